@@ -1,0 +1,23 @@
+"""B200-native fbfft: batched R2C/C2R FFTs and Fourier-domain convolution.
+
+The product is the C-ABI shared library ``lib/libfbfft_b200.so`` (declared in
+``include/fbfft_b200.h``); this package is a thin ctypes mirror of the
+reference's host entry points for Python callers and for the tests.
+"""
+from .api import (  # noqa: F401
+    ErrorCode,
+    FbfftError,
+    FFTIteratedConvolution,
+    TiledDeviceTensor,
+    fbfft1D,
+    fbfft2D,
+    fbfft2D_c2c,
+    fbifft1D,
+    fbifft2D,
+    fbifft2D_c2c,
+    fft2d_c2r,
+    fft2d_r2c,
+    last_error,
+    lib,
+    transposeMM,
+)

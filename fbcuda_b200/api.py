@@ -1,0 +1,199 @@
+"""ctypes mirror of the reference's fbfft host interface over libfbfft_b200.so.
+
+Function names, argument order and error behaviour follow the reference's
+templates in ``namespace facebook::cuda::fbfft`` (fbfft/FBFFT.cuh:11-56),
+``transposeMM`` (MM.cuh:11-17) and ``FFTIteratedConvolution``
+(fbfft/FFTIteratedConvolution.cuh:624-632).  Tensors are CUDA ``torch.Tensor``
+objects used purely as device-memory handles: only ``data_ptr()``, ``shape`` and
+``stride()`` are read, exactly the three fields of the reference's DeviceTensor.
+Nothing here computes; a missing or unloadable library raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "lib", "libfbfft_b200.so")
+_lib = None
+
+
+class ErrorCode(enum.IntEnum):
+    """FBFFTParameters::ErrorCode (fbfft/FBFFTParameters.h:9-14)."""
+    Success = 0
+    UnsupportedSize = 1
+    UnsupportedDimension = 2
+    CudaError = 3
+
+
+class FbfftError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{ErrorCode(code).name}: {msg}")
+        self.code = ErrorCode(code)
+
+
+class _Tiled(ctypes.Structure):
+    """fbfft_tiled_tensor4 == TiledDeviceTensor<float, 4>
+    (fbfft/FFTIteratedConvolution.cuh:70-88)."""
+    _fields_ = [("padL", ctypes.c_int), ("padU", ctypes.c_int), ("data", ctypes.c_void_p),
+                ("stride", ctypes.c_int * 4), ("size", ctypes.c_int * 4)]
+
+
+_ip = ctypes.POINTER(ctypes.c_int)
+_vp = ctypes.c_void_p
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the CUDA library; there is no fallback of any kind."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise ImportError(f"{_LIB_PATH} is missing: run `python -m fbcuda_b200.build`")
+        L = ctypes.CDLL(_LIB_PATH)
+        L.fbfft_b200_version.restype = ctypes.c_int
+        L.fbfft_b200_last_error.restype = ctypes.c_char_p
+        t4 = [_vp, _ip, _ip]
+        L.fbfft_b200_fbfft1d.argtypes = t4 + t4 + [ctypes.c_int, _vp]
+        L.fbfft_b200_fbifft1d.argtypes = t4 + t4 + [ctypes.c_int, _vp]
+        L.fbfft_b200_fbfft2d.argtypes = t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
+        L.fbfft_b200_fbfft2d_c2c.argtypes = t4 + t4 + [_vp]
+        L.fbfft_b200_fbifft2d_c2c.argtypes = t4 + t4 + [_vp]
+        L.fbfft_b200_fbifft2d.argtypes = t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
+        L.fbfft_b200_fft2d_r2c.argtypes = [ctypes.c_int] + t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
+        L.fbfft_b200_fft2d_c2r.argtypes = [ctypes.c_int] + t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
+        L.fbfft_b200_transpose_mm.argtypes = [ctypes.c_int] * 4 + t4 * 3 + [ctypes.c_float, _vp]
+        L.fbfft_b200_iterated_convolution.argtypes = [ctypes.c_int, _vp, _vp, _vp, _ip, _ip, ctypes.c_int,
+                                                      ctypes.c_float, ctypes.c_int, ctypes.c_size_t, _vp]
+        for name in ("fbfft1d", "fbifft1d", "fbfft2d", "fbfft2d_c2c", "fbifft2d_c2c", "fbifft2d", "fft2d_r2c",
+                     "fft2d_c2r", "transpose_mm", "iterated_convolution"):
+            getattr(L, "fbfft_b200_" + name).restype = ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().fbfft_b200_last_error().decode()
+
+
+def _ints(vals):
+    return (ctypes.c_int * len(vals))(*[int(v) for v in vals])
+
+
+def _t(t):
+    """(pointer, sizes, strides) of a CUDA tensor."""
+    if not t.is_cuda:
+        raise ValueError("fbfft operates on device memory: pass CUDA tensors")
+    return _vp(t.data_ptr()), _ints(t.shape), _ints(t.stride())
+
+
+def _t_complex(t):
+    """A float tensor [..., 2] seen as the reference's DeviceTensor<Complex, Dim-1>:
+    sizes without the trailing 2, strides counted in complex elements."""
+    if not t.is_cuda:
+        raise ValueError("fbfft operates on device memory: pass CUDA tensors")
+    if t.shape[-1] != 2 or t.stride(-1) != 1 or any(s % 2 for s in t.stride()[:-1]):
+        raise ValueError("not viewable as a complex tensor")
+    return _vp(t.data_ptr()), _ints(t.shape[:-1]), _ints([s // 2 for s in t.stride()[:-1]])
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+        return _vp(torch.cuda.current_stream().cuda_stream)
+    if isinstance(stream, int):
+        return _vp(stream)
+    return _vp(stream.cuda_stream)
+
+
+def _check(code: int) -> ErrorCode:
+    if code != 0:
+        raise FbfftError(code, last_error())
+    return ErrorCode.Success
+
+
+def fbfft1D(real, complex, padL: int = 0, stream=None) -> ErrorCode:
+    """fbfft1D<1>: real [B][N] -> complex [B][N/2+1][2] (fbfft/FBFFT.cuh:11-16)."""
+    return _check(lib().fbfft_b200_fbfft1d(*_t(real), *_t(complex), padL, _stream(stream)))
+
+
+def fbifft1D(real, complex, padL: int = 0, stream=None) -> ErrorCode:
+    """fbifft1D<1>: complex [B][N/2+1][2] -> real [B][N], unnormalised (fbfft/FBFFT.cuh:18-23)."""
+    return _check(lib().fbfft_b200_fbifft1d(*_t(real), *_t(complex), padL, _stream(stream)))
+
+
+def fbfft2D(real, complex, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """fbfft2D<1>(real, complexAsFloat): finished transform for N <= 32, row pass
+    into the [B][N][N/2+1][2] buffer for N >= 64 (fbfft/FBFFT.cuh:30-36)."""
+    return _check(lib().fbfft_b200_fbfft2d(*_t(real), *_t(complex), padL, padU, _stream(stream)))
+
+
+def fbfft2D_c2c(src, dst, stream=None) -> ErrorCode:
+    """fbfft2D<1>(Complex src, Complex dst): column pass for N >= 64; src and dst are
+    float tensors [B][N][N/2+1][2] and [B][N/2+1][N][2] (fbfft/FBFFT.cuh:38-43)."""
+    return _check(lib().fbfft_b200_fbfft2d_c2c(*_t_complex(src), *_t_complex(dst), _stream(stream)))
+
+
+def fbifft2D_c2c(src, dst, stream=None) -> ErrorCode:
+    """fbifft2D<1>(float4 src, float4 dst): first inverse pass for N >= 64 (fbfft/FBFFT.cuh:45-49)."""
+    return _check(lib().fbfft_b200_fbifft2d_c2c(*_t(src), *_t(dst), _stream(stream)))
+
+
+def fbifft2D(complexSrc, realDst, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """fbifft2D<1>(Complex src, real dst): full inverse for N <= 32, second inverse
+    pass for N >= 64; complexSrc is a float tensor [..., 2] (fbfft/FBFFT.cuh:50-56)."""
+    return _check(lib().fbfft_b200_fbifft2d(*_t_complex(complexSrc), *_t(realDst), padL, padU, _stream(stream)))
+
+
+def fft2d_r2c(n: int, real, complex, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """Single-call forward transform for any N in {8..256} (no reference counterpart for N >= 64)."""
+    return _check(lib().fbfft_b200_fft2d_r2c(n, *_t(real), *_t(complex), padL, padU, _stream(stream)))
+
+
+def fft2d_c2r(n: int, complex, real, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """Single-call inverse transform for any N in {8..256}."""
+    return _check(lib().fbfft_b200_fft2d_c2r(n, *_t(complex), *_t(real), padL, padU, _stream(stream)))
+
+
+def transposeMM(A, B, C, invNorm: float, conjugateTransposeA: bool, conjugateTransposeB: bool,
+                accumulate: bool = False, stream=None) -> ErrorCode:
+    """transposeMM<Dim, CTA, CTB, Acc>(A, B, C, invNorm) (MM.cuh:11-17)."""
+    return _check(lib().fbfft_b200_transpose_mm(A.dim(), int(conjugateTransposeA), int(conjugateTransposeB),
+                                                int(accumulate), *_t(A), *_t(B), *_t(C), float(invNorm),
+                                                _stream(stream)))
+
+
+class TiledDeviceTensor:
+    """Host-side builder for a device array of TiledDeviceTensor<float, 4>
+    descriptors (fbfft/FFTIteratedConvolution.cuh:70-88)."""
+
+    def __init__(self, tiles):
+        """tiles: list of (tensor [B][planes][h][w], padL, padU)."""
+        import torch
+        self.tiles = tiles
+        arr = (_Tiled * len(tiles))()
+        for i, (t, pad_l, pad_u) in enumerate(tiles):
+            if not t.is_cuda or t.dim() != 4:
+                raise ValueError("tiles are 4-d CUDA tensors")
+            arr[i].padL, arr[i].padU, arr[i].data = int(pad_l), int(pad_u), t.data_ptr()
+            for d in range(4):
+                arr[i].stride[d] = t.stride(d)
+                arr[i].size[d] = t.shape[d]
+        raw = bytes(arr)
+        host = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+        self.device_array = host.to(tiles[0][0].device)
+        self.count = len(tiles)
+
+    @property
+    def ptr(self):
+        return _vp(self.device_array.data_ptr())
+
+
+def FFTIteratedConvolution(fftSize: int, ins: TiledDeviceTensor, outs: TiledDeviceTensor, weight, conv_pass: int,
+                           scale: float, batchSize: int, stream=None) -> bool:
+    """FFTIteratedConvolution<FFTSize>(ins, outs, weight, pass, scale, batchSize,
+    numTiles, s); returns what the reference returns (true when launched)."""
+    w_ptr, w_size, w_stride = _t(weight)
+    return bool(lib().fbfft_b200_iterated_convolution(fftSize, ins.ptr, outs.ptr, w_ptr, w_size, w_stride,
+                                                      int(conv_pass), float(scale), int(batchSize), ins.count,
+                                                      _stream(stream)))

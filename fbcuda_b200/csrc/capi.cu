@@ -1,0 +1,268 @@
+// C ABI: argument validation and dispatch to the kernels.  Mirrors the host
+// dispatch of the reference (fbfft/FBFFT-inl.cuh:19-150, fbfft/FBFFT2D-inl.cuh:450-669,
+// fbfft/FBIFFT2D-inl.cuh:529-742, MM-inl.cuh:515-814,
+// fbfft/FFTIteratedConvolution.cuh:624-755) but reports violated preconditions as
+// error codes instead of aborting.
+#include "../../include/fbfft_b200.h"
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+thread_local char g_last_error[256] = "";
+}
+
+void set_last_error(const char* msg) {
+  std::strncpy(g_last_error, msg, sizeof(g_last_error) - 1);
+  g_last_error[sizeof(g_last_error) - 1] = 0;
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64];
+  static bool have[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!have[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+    have[dev] = true;
+  }
+  return cached[dev];
+}
+
+namespace {
+
+int fail(int code, const char* msg) {
+  set_last_error(msg);
+  return code;
+}
+
+bool is_pow2(int n) { return n > 0 && (n & (n - 1)) == 0; }
+bool small_size(int n) { return n == 8 || n == 16 || n == 32; }
+bool large_size(int n) { return n == 64 || n == 128 || n == 256; }
+
+RealView real_view(const float* p, const int* size, const int* stride) {
+  RealView v;
+  v.p = const_cast<float*>(p);
+  v.sb = stride[0];
+  v.sy = stride[1];
+  v.sx = stride[2];
+  v.h = size[1];
+  v.w = size[2];
+  return v;
+}
+
+// float tensor [B][rows][cols][2]
+CplxView cplx_view_f4(const float* p, const int* stride) {
+  CplxView v;
+  v.p = const_cast<float*>(p);
+  v.sb = stride[0];
+  v.sr = stride[1];
+  v.sc = stride[2];
+  v.sz = stride[3];
+  return v;
+}
+
+// Complex tensor [B][rows][cols], strides in complex elements
+CplxView cplx_view_c3(const float* p, const int* stride) {
+  CplxView v;
+  v.p = const_cast<float*>(p);
+  v.sb = 2LL * stride[0];
+  v.sr = 2 * stride[1];
+  v.sc = 2 * stride[2];
+  v.sz = 1;
+  return v;
+}
+
+int check_ptrs(const void* a, const void* b) {
+  if (!a || !b) return fail(kUnsupportedDimension, "null tensor pointer");
+  return kSuccess;
+}
+
+}  // namespace
+}  // namespace fbfft_b200
+
+using namespace fbfft_b200;
+
+extern "C" {
+
+int fbfft_b200_version(void) { return 100; }
+
+const char* fbfft_b200_last_error(void) { return g_last_error; }
+
+int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const int* real_stride, float* cplx,
+                         const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream) {
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = real_size[0];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(real, cplx)) return kUnsupportedDimension;
+  if (!small_size(n) && !large_size(n)) return fail(kUnsupportedSize, "fft2d_r2c: N must be 8, 16, 32, 64, 128 or 256");
+  if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != n || cplx_size[3] != 2)
+    return fail(kUnsupportedDimension, "fft2d_r2c: complex tensor must be [B][N/2+1][N][2]");
+  if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fft2d_r2c: negative padding");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RealView in = real_view(real, real_size, real_stride);
+  CplxView out = cplx_view_f4(cplx, cplx_stride);
+  if (small_size(n)) return fft2d_small_forward(n, in, out, B, padL, padU, s);
+  return fft2d_large_forward(n, in, out, B, padL, padU, s);
+}
+
+int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const int* cplx_stride, float* real,
+                         const int* real_size, const int* real_stride, int padL, int padU, void* stream) {
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = real_size[0];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(real, cplx)) return kUnsupportedDimension;
+  if (!small_size(n) && !large_size(n)) return fail(kUnsupportedSize, "fft2d_c2r: N must be 8, 16, 32, 64, 128 or 256");
+  if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != n || cplx_size[3] != 2)
+    return fail(kUnsupportedDimension, "fft2d_c2r: complex tensor must be [B][N/2+1][N][2]");
+  if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fft2d_c2r: negative padding");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CplxView in = cplx_view_f4(cplx, cplx_stride);
+  RealView out = real_view(real, real_size, real_stride);
+  if (small_size(n)) return fft2d_small_inverse(n, in, out, B, padL, padU, s);
+  return fft2d_large_inverse(n, in, out, B, padL, padU, s);
+}
+
+int fbfft_b200_fbfft2d(const float* real, const int* real_size, const int* real_stride, float* cplx,
+                       const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream) {
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return fail(kUnsupportedDimension, "null size/stride");
+  // Size class by the shape of the complex tensor, as the reference does
+  // (fbfft/FBFFT2D-inl.cuh:479,511,543 test dimension 2; :599-616 dimension 1).
+  const int d1 = cplx_size[1], d2 = cplx_size[2];
+  if (d1 > 256 || d2 > 256) return fail(kUnsupportedSize, "fbfft2d: transform size above 256");
+  if (small_size(d2) && d1 == d2 / 2 + 1) {
+    return fbfft_b200_fft2d_r2c(d2, real, real_size, real_stride, cplx, cplx_size, cplx_stride, padL, padU, stream);
+  }
+  if (large_size(d1) && d2 == d1 / 2 + 1) {
+    const int B = real_size[0];
+    if (B == 0) return kSuccess;
+    if (check_ptrs(real, cplx)) return kUnsupportedDimension;
+    if (cplx_size[0] != B || cplx_size[3] != 2) return fail(kUnsupportedDimension, "fbfft2d: buffer must be [B][N][N/2+1][2]");
+    if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fbfft2d: negative padding");
+    return fft2d_large_rows_forward(d1, real_view(real, real_size, real_stride), cplx_view_f4(cplx, cplx_stride), B,
+                                    padL, padU, static_cast<cudaStream_t>(stream));
+  }
+  return fail(kUnsupportedSize, "fbfft2d: complex tensor is neither [B][N/2+1][N][2] (N<=32) nor [B][N][N/2+1][2] (N>=64)");
+}
+
+int fbfft_b200_fbfft2d_c2c(const float* src, const int* src_size, const int* src_stride, float* dst,
+                           const int* dst_size, const int* dst_stride, void* stream) {
+  if (!src_size || !src_stride || !dst_size || !dst_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = src_size[0], n = src_size[1];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(src, dst)) return kUnsupportedDimension;
+  if (!large_size(n)) return fail(kUnsupportedSize, "fbfft2d_c2c: N must be 64, 128 or 256");
+  if (src_size[2] != n / 2 + 1) return fail(kUnsupportedDimension, "fbfft2d_c2c: src must be [B][N][N/2+1]");
+  if (dst_size[0] != B || dst_size[1] != n / 2 + 1 || dst_size[2] != n)
+    return fail(kUnsupportedDimension, "fbfft2d_c2c: dst must be [B][N/2+1][N]");
+  if (src == dst) return fail(kUnsupportedDimension, "fbfft2d_c2c: src and dst must differ");
+  return fft2d_large_cols_forward(n, cplx_view_c3(src, src_stride), cplx_view_c3(dst, dst_stride), B,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_fbifft2d_c2c(const float* src, const int* src_size, const int* src_stride, float* dst,
+                            const int* dst_size, const int* dst_stride, void* stream) {
+  if (!src_size || !src_stride || !dst_size || !dst_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = src_size[0], n = src_size[2];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(src, dst)) return kUnsupportedDimension;
+  if (!large_size(n)) return fail(kUnsupportedSize, "fbifft2d_c2c: N must be 64, 128 or 256");
+  if (src_size[1] != n / 2 + 1 || src_size[3] != 2) return fail(kUnsupportedDimension, "fbifft2d_c2c: src must be [B][N/2+1][N][2]");
+  if (dst_size[0] != B || dst_size[1] != n || dst_size[2] != n || dst_size[3] != 2)
+    return fail(kUnsupportedDimension, "fbifft2d_c2c: dst must be [B][N][N][2]");
+  if (src == dst) return fail(kUnsupportedDimension, "fbifft2d_c2c: src and dst must differ");
+  return fft2d_large_rows_inverse(n, cplx_view_f4(src, src_stride), cplx_view_f4(dst, dst_stride), B,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_fbifft2d(const float* src, const int* src_size, const int* src_stride, float* real,
+                        const int* real_size, const int* real_stride, int padL, int padU, void* stream) {
+  if (!src_size || !src_stride || !real_size || !real_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int d1 = src_size[1], d2 = src_size[2];
+  if (d1 > 256 || d2 > 256) return fail(kUnsupportedSize, "fbifft2d: transform size above 256");
+  const int B = real_size[0];
+  if (small_size(d2) && d1 == d2 / 2 + 1) {
+    if (B == 0) return kSuccess;
+    if (check_ptrs(src, real)) return kUnsupportedDimension;
+    if (src_size[0] != B) return fail(kUnsupportedDimension, "fbifft2d: batch sizes differ");
+    if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fbifft2d: negative padding");
+    return fft2d_small_inverse(d2, cplx_view_c3(src, src_stride), real_view(real, real_size, real_stride), B, padL,
+                               padU, static_cast<cudaStream_t>(stream));
+  }
+  if (large_size(d1) && d2 == d1) {
+    if (B == 0) return kSuccess;
+    if (check_ptrs(src, real)) return kUnsupportedDimension;
+    if (src_size[0] != B) return fail(kUnsupportedDimension, "fbifft2d: batch sizes differ");
+    if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fbifft2d: negative padding");
+    return fft2d_large_cols_inverse(d1, cplx_view_c3(src, src_stride), real_view(real, real_size, real_stride), B,
+                                    padL, padU, static_cast<cudaStream_t>(stream));
+  }
+  return fail(kUnsupportedSize, "fbifft2d: src is neither [B][N/2+1][N] (N<=32) nor [B][N][N] (N>=64)");
+}
+
+int fbfft_b200_fbfft1d(const float* real, const int* real_size, const int* real_stride, float* cplx,
+                       const int* cplx_size, const int* cplx_stride, int padL, void* stream) {
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = real_size[0], n = real_size[1];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(real, cplx)) return kUnsupportedDimension;
+  if (!is_pow2(n) || n < 8 || n > 256) return fail(kUnsupportedSize, "fbfft1d: N must be a power of two in [8, 256]");
+  if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != 2)
+    return fail(kUnsupportedDimension, "fbfft1d: complex tensor must be [B][N/2+1][2]");
+  if (padL < 0) return fail(kUnsupportedDimension, "fbfft1d: negative padding");
+  return fft1d_forward(n, real, real_stride[0], real_stride[1], cplx, cplx_stride[0], cplx_stride[1], cplx_stride[2],
+                       B, padL, static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_fbifft1d(float* real, const int* real_size, const int* real_stride, const float* cplx,
+                        const int* cplx_size, const int* cplx_stride, int padL, void* stream) {
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return fail(kUnsupportedDimension, "null size/stride");
+  const int B = real_size[0], n = real_size[1];
+  if (B == 0) return kSuccess;
+  if (check_ptrs(real, cplx)) return kUnsupportedDimension;
+  if (!is_pow2(n) || n < 8 || n > 256) return fail(kUnsupportedSize, "fbifft1d: N must be a power of two in [8, 256]");
+  if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != 2)
+    return fail(kUnsupportedDimension, "fbifft1d: complex tensor must be [B][N/2+1][2]");
+  if (padL < 0) return fail(kUnsupportedDimension, "fbifft1d: negative padding");
+  return fft1d_inverse(n, cplx, cplx_stride[0], cplx_stride[1], cplx_stride[2], real, real_stride[0], real_stride[1],
+                       B, padL, static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_transpose_mm(int dim, int conj_transpose_a, int conj_transpose_b, int accumulate, const float* a,
+                            const int* a_size, const int* a_stride, const float* b, const int* b_size,
+                            const int* b_stride, float* c, const int* c_size, const int* c_stride, float inv_norm,
+                            void* stream) {
+  if (!a_size || !a_stride || !b_size || !b_stride || !c_size || !c_stride)
+    return fail(kUnsupportedDimension, "null size/stride");
+  if (dim < 4 || dim > 6) return fail(kUnsupportedDimension, "transpose_mm: dim must be 4, 5 or 6");
+  if (!a || !b || !c) return fail(kUnsupportedDimension, "null tensor pointer");
+  return transpose_mm(dim, conj_transpose_a != 0, conj_transpose_b != 0, accumulate != 0, a, a_size, a_stride, b,
+                      b_size, b_stride, c, c_size, c_stride, inv_norm, static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs,
+                                    float* weight, const int* weight_size, const int* weight_stride, int pass,
+                                    float scale, int batch_size, size_t num_tiles, void* stream) {
+  if (!small_size(fft_size)) {
+    set_last_error("iterated_convolution: FFT size must be 8, 16 or 32");
+    return 0;
+  }
+  if (pass < 0 || pass > 2 || !ins || !outs || !weight || !weight_size || !weight_stride) {
+    set_last_error("iterated_convolution: unknown pass or null argument");
+    return 0;
+  }
+  return iterated_convolution(fft_size, ins, outs, weight, weight_size, weight_stride, pass, scale, batch_size,
+                              num_tiles, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

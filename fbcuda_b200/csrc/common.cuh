@@ -1,0 +1,42 @@
+// Shared host/device definitions for the fbfft kernels.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace fbfft_b200 {
+
+// Numeric values of the reference's FBFFTParameters::ErrorCode
+// (fbfft/FBFFTParameters.h:9-14).
+enum ErrorCode : int {
+  kSuccess = 0,
+  kUnsupportedSize = 1,
+  kUnsupportedDimension = 2,
+  kCudaError = 3,
+};
+
+// A batch of real images: element (b, y, x) at p[b*sb + y*sy + x*sx].
+struct RealView {
+  float* p;
+  long long sb;
+  int sy, sx;
+  int h, w;
+};
+
+// A batch of complex matrices stored as floats: element (b, r, c, z) at
+// p[b*sb + r*sr + c*sc + z*sz], z = 0 (re) or 1 (im).
+struct CplxView {
+  float* p;
+  long long sb;
+  int sr, sc, sz;
+};
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Number of SMs of the current device, cached per device (the reference caches
+// cudaDeviceProp for its grid sizing, util/CachedDeviceProperties.cpp:45-64).
+int sm_count();
+
+void set_last_error(const char* msg);
+
+}  // namespace fbfft_b200

@@ -1,0 +1,43 @@
+// Internal entry points behind the C ABI (one per kernel family).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+#include "../../include/fbfft_b200.h"
+#include "common.cuh"
+
+namespace fbfft_b200 {
+
+// N in {8, 16, 32}: [B][N/2+1][N] layout (fft2d_small.cu)
+int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
+int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
+
+// N in {64, 128, 256}: transposed [B][N/2+1 (kx)][N (ky)] layout (fft2d_large.cu)
+int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
+int fft2d_large_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
+// the reference's two-call protocol for N >= 64 (fft_lines.cu)
+int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, int B, int padL, int padU,
+                             cudaStream_t s);
+int fft2d_large_cols_forward(int n, const CplxView& buffer, const CplxView& dst, int B, cudaStream_t s);
+int fft2d_large_rows_inverse(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s);
+int fft2d_large_cols_inverse(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU,
+                             cudaStream_t s);
+
+// 1-D (fft_lines.cu)
+int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,
+                  cudaStream_t s);
+int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* real, int rs0, int rs1, int B, int padL,
+                  cudaStream_t s);
+
+// per-bin complex contraction (cgemm_bins.cu)
+int transpose_mm(int dim, bool conjA, bool conjB, bool accumulate, const float* a, const int* a_size,
+                 const int* a_stride, const float* b, const int* b_size, const int* b_stride, float* c,
+                 const int* c_size, const int* c_stride, float inv_norm, cudaStream_t s);
+
+// tiled convolution passes (conv_iterated.cu)
+int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs, float* weight,
+                         const int* weight_size, const int* weight_stride, int pass, float scale, int batch_size,
+                         size_t num_tiles, cudaStream_t s);
+
+}  // namespace fbfft_b200

@@ -1,0 +1,136 @@
+/* C ABI of the B200 fbfft library (libfbfft_b200.so).
+ *
+ * Every function is a drop-in for one host entry point of the reference's fbfft
+ * path; the comment above each declaration names the reference interface it
+ * replaces (paths relative to the reference tree).  Tensors cross the boundary
+ * as the three fields of the reference's DeviceTensor<T, Dim> POD
+ * (DeviceTensor.cuh:237-245): a device pointer, `Dim` sizes and `Dim` strides,
+ * both in elements of T.  All pointers are device pointers unless stated; work
+ * is enqueued on `stream` (a cudaStream_t) and nothing synchronises.  The caller
+ * owns every buffer; the library allocates no device memory.
+ *
+ * Return values are those of FBFFTParameters::ErrorCode
+ * (fbfft/FBFFTParameters.h:9-14).  Conditions the reference checks with
+ * assert()/CHECK_*() and aborts on are reported as FBFFT_UNSUPPORTED_DIMENSION
+ * instead; fbfft_b200_last_error() returns a description.
+ */
+#ifndef FBFFT_B200_H_
+#define FBFFT_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FBFFT_SUCCESS = 0,
+  FBFFT_UNSUPPORTED_SIZE = 1,
+  FBFFT_UNSUPPORTED_DIMENSION = 2,
+  FBFFT_CUDA_ERROR = 3
+};
+
+/* Layout of the reference's TiledDeviceTensor<float, 4>
+ * (fbfft/FFTIteratedConvolution.cuh:70-88): two pads, then the DeviceTensor POD. */
+typedef struct fbfft_tiled_tensor4 {
+  int padL;
+  int padU;
+  float* data;
+  int stride[4];
+  int size[4];
+} fbfft_tiled_tensor4;
+
+/* Library version (major * 100 + minor). */
+int fbfft_b200_version(void);
+
+/* Text describing the last non-success return on the calling thread. */
+const char* fbfft_b200_last_error(void);
+
+/* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
+ * -- fbfft/FBFFT.cuh:11-16, fbfft/FBFFT-inl.cuh:19-87.
+ * real [B][N], N = real_size[1] in {8..256}; complex [B][N/2+1][2].
+ * complex[b][k] = sum_n p[n] exp(-2 pi i k n / N), p[n] = real[b][n - padL] for
+ * padL <= n < N, else 0. */
+int fbfft_b200_fbfft1d(const float* real, const int* real_size, const int* real_stride, float* cplx,
+                       const int* cplx_size, const int* cplx_stride, int padL, void* stream);
+
+/* fbifft1D<1>(real, complex, padL, s) -- fbfft/FBFFT.cuh:18-23,
+ * fbfft/FBFFT-inl.cuh:89-150.  Unnormalised: real[b][x - padL] = N * p[x]. */
+int fbfft_b200_fbifft1d(float* real, const int* real_size, const int* real_stride, const float* cplx,
+                        const int* cplx_size, const int* cplx_stride, int padL, void* stream);
+
+/* fbfft2D<1>(DeviceTensor<float,3>& real, DeviceTensor<float,4>& complexAsFloat,
+ * padL, padU, s) -- fbfft/FBFFT.cuh:30-36, fbfft/FBFFT2D-inl.cuh:450-623.
+ * real [B][h][w] is placed at (padU, padL) of an N x N canvas of zeros.
+ *  - cplx_size = {B, N/2+1, N, 2}, N in {8,16,32}: the finished transform,
+ *    cplx[b][ky][kx] = F[ky][kx].
+ *  - cplx_size = {B, N, N/2+1, 2}, N in {64,128,256}: the first half of the
+ *    reference's two-call protocol, row transforms only:
+ *    cplx[b][y][kx] = sum_x P[y][x] exp(-2 pi i kx x / N). */
+int fbfft_b200_fbfft2d(const float* real, const int* real_size, const int* real_stride, float* cplx,
+                       const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream);
+
+/* fbfft2D<1>(DeviceTensor<Complex,3>& src, DeviceTensor<Complex,3>& dst, s)
+ * -- fbfft/FBFFT.cuh:38-43, fbfft/FBFFT2D-inl.cuh:627-669.  Second half for
+ * N >= 64: src [B][N][N/2+1] -> dst [B][N/2+1][N],
+ * dst[b][kx][ky] = sum_y src[b][y][kx] exp(-2 pi i ky y / N).  Sizes and strides
+ * count complex elements; src and dst must not overlap. */
+int fbfft_b200_fbfft2d_c2c(const float* src, const int* src_size, const int* src_stride, float* dst,
+                           const int* dst_size, const int* dst_stride, void* stream);
+
+/* fbifft2D<1>(DeviceTensor<float,4>& src, DeviceTensor<float,4>& dst, s)
+ * -- fbfft/FBFFT.cuh:45-49, fbfft/FBIFFT2D-inl.cuh:529-563.  First half of the
+ * inverse for N >= 64: src [B][N/2+1][N][2] -> dst [B][N][N][2]; images b and
+ * b + ceil(B/2) are combined as X_b + i X_{b+ceil(B/2)}, the spectrum is extended
+ * to all N values of kx by Hermitian symmetry and inverse transformed along ky;
+ * only the first ceil(B/2) slices of dst are written. */
+int fbfft_b200_fbifft2d_c2c(const float* src, const int* src_size, const int* src_stride, float* dst,
+                            const int* dst_size, const int* dst_stride, void* stream);
+
+/* fbifft2D<1>(DeviceTensor<Complex,3>& src, DeviceTensor<float,3>& real, padL,
+ * padU, s) -- fbfft/FBFFT.cuh:50-56, fbfft/FBIFFT2D-inl.cuh:567-742.
+ *  - src_size = {B, N/2+1, N}, N in {8,16,32}: full inverse of the [ky][kx]
+ *    layout, real[b][y-padU][x-padL] = N*N * P[y][x] for in-bounds (y, x).
+ *  - src_size = {B, N, N}, N in {64,128,256}: second half of the two-call
+ *    inverse; src is the buffer written by fbfft_b200_fbifft2d_c2c.
+ * Sizes and strides of src count complex elements. */
+int fbfft_b200_fbifft2d(const float* src, const int* src_size, const int* src_stride, float* real,
+                        const int* real_size, const int* real_stride, int padL, int padU, void* stream);
+
+/* Single-call 2-D transforms for every N in {8,...,256}; no counterpart in the
+ * reference for N >= 64, where it needs two calls and a caller-owned buffer
+ * (fbfft/FBFFT2D-inl.cuh:597-617 then :627-669).  cplx is [B][N/2+1][N][2] in the
+ * reference's final layout for the size class: [ky][kx] for N <= 32, transposed
+ * [kx][ky] for N >= 64.  n is the transform size. */
+int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const int* real_stride, float* cplx,
+                         const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream);
+int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const int* cplx_stride, float* real,
+                         const int* real_size, const int* real_stride, int padL, int padU, void* stream);
+
+/* transposeMM<Dim, ConjugateTransposeA, ConjugateTransposeB, Accumulate>(A, B, C,
+ * invNorm, s) -- MM.cuh:11-17, MM-inl.cuh:515-814.  A, B, C are float tensors of
+ * `dim` dimensions whose last dimension is 2 (re, im) and whose dimensions
+ * 2..dim-2 are the frequency bins:
+ *   C[i][j][bin] (+)= invNorm * sum_k op(A)[i][k][bin] * op(B)[k][j][bin],
+ * where a conjugate-transposed operand has its two leading indices swapped and
+ * its value conjugated (MM-inl.cuh:121-131,150-163). */
+int fbfft_b200_transpose_mm(int dim, int conj_transpose_a, int conj_transpose_b, int accumulate, const float* a,
+                            const int* a_size, const int* a_stride, const float* b, const int* b_size,
+                            const int* b_stride, float* c, const int* c_size, const int* c_stride, float inv_norm,
+                            void* stream);
+
+/* FFTIteratedConvolution<FFTSize>(ins, outs, weight, pass, scale, batchSize,
+ * numTiles, s) -- fbfft/FFTIteratedConvolution.cuh:624-755.  ins / outs are
+ * DEVICE arrays of numTiles descriptors (the reference dereferences them on the
+ * device, :113-114).  pass: 0 updateOutput (writes outs), 1 updateGradInput
+ * (writes ins), 2 accGradParameters (overwrites weight with scale * gradient).
+ * Returns 1 (true) when the pass was launched, 0 (false) otherwise, as the
+ * reference does.  fft_size in {8, 16, 32}. */
+int fbfft_b200_iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs,
+                                    float* weight, const int* weight_size, const int* weight_stride, int pass,
+                                    float scale, int batch_size, size_t num_tiles, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBFFT_B200_H_ */
