@@ -25,7 +25,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
-    "-DFBFFT_B200_BUILD",
+    "--expt-relaxed-constexpr", "-DFBFFT_B200_BUILD",
 ]
 
 

@@ -24,6 +24,9 @@ int fft2d_large_rows_inverse(int n, const CplxView& src, const CplxView& buffer,
 int fft2d_large_cols_inverse(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU,
                              cudaStream_t s);
 
+// in-place transform of `lines` contiguous-or-strided lines per batch of a [B][lines][N] complex tensor
+int fft_lines_inplace(int n, const CplxView& t, int B, int lines, bool inverse, cudaStream_t s);
+
 // 1-D (fft_lines.cu)
 int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,
                   cudaStream_t s);

@@ -1,14 +1,6 @@
 #include "kernels.h"
 namespace fbfft_b200 {
 #define NI { set_last_error("not implemented"); return kUnsupportedSize; }
-int fft2d_large_forward(int, const RealView&, const CplxView&, int, int, int, cudaStream_t) NI
-int fft2d_large_inverse(int, const CplxView&, const RealView&, int, int, int, cudaStream_t) NI
-int fft2d_large_rows_forward(int, const RealView&, const CplxView&, int, int, int, cudaStream_t) NI
-int fft2d_large_cols_forward(int, const CplxView&, const CplxView&, int, cudaStream_t) NI
-int fft2d_large_rows_inverse(int, const CplxView&, const CplxView&, int, cudaStream_t) NI
-int fft2d_large_cols_inverse(int, const CplxView&, const RealView&, int, int, int, cudaStream_t) NI
-int fft1d_forward(int, const float*, int, int, float*, int, int, int, int, int, cudaStream_t) NI
-int fft1d_inverse(int, const float*, int, int, int, float*, int, int, int, int, cudaStream_t) NI
 int transpose_mm(int, bool, bool, bool, const float*, const int*, const int*, const float*, const int*, const int*, float*, const int*, const int*, float, cudaStream_t) NI
 int iterated_convolution(int, const fbfft_tiled_tensor4*, const fbfft_tiled_tensor4*, float*, const int*, const int*, int, float, int, size_t, cudaStream_t) { return 0; }
 }

@@ -1,0 +1,67 @@
+"""GPU parity of fbfft1D / fbifft1D against the float64 oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import fbcuda_b200 as fb
+from oracle import fbfft_oracle as orc
+from tests.util_gpu import FFT_TOL, canary_alloc, check_canary, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [8, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("b", [1, 2, 3, 5, 64, 4096])
+def test_fbfft1d_roundtrip(n, b):
+    rng = np.random.default_rng(1000 * n + b)
+    x = rng.uniform(-1, 1, (b, n)).astype(np.float32)
+    for pad in (0, 3):
+        raw, out = canary_alloc((b, n // 2 + 1, 2))
+        assert fb.fbfft1D(dev(x), out, pad) == fb.ErrorCode.Success
+        torch.cuda.synchronize()
+        check_canary(raw, out.numel())
+        want = orc.fbfft1d(x, pad)
+        assert orc.rel_l2(host(out), want) < FFT_TOL, (n, b, pad)
+        raw2, back = canary_alloc((b, n))
+        back.fill_(7.0)
+        assert fb.fbifft1D(back, out, pad) == fb.ErrorCode.Success
+        torch.cuda.synchronize()
+        check_canary(raw2, back.numel())
+        want_back = orc.fbifft1d(want, n, pad)
+        got = host(back)
+        assert orc.rel_l2(got[:, : n - pad], want_back[:, : n - pad]) < FFT_TOL, (n, b, pad)
+        if pad:
+            assert np.all(got[:, n - pad:] == 7.0)   # columns the shifted window never reaches are untouched
+
+
+def test_config1_signals():
+    """4096 signals of length 32, uniform[-1,1) from seed 0 -> 4096 x 17 bins, plus the inverse round trip."""
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, (4096, 32)).astype(np.float32)
+    out = torch.empty((4096, 17, 2), device="cuda")
+    fb.fbfft1D(dev(x), out)
+    assert orc.rel_l2(host(out), orc.fbfft1d(x)) < FFT_TOL
+    back = torch.empty((4096, 32), device="cuda")
+    fb.fbifft1D(back, out)
+    assert orc.rel_l2(host(back) / 32.0, x) < FFT_TOL
+
+
+def test_strided_1d():
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1, 1, (10, 64)).astype(np.float32)
+    big = torch.zeros((10, 80), device="cuda")
+    big[:, 5:69] = dev(x)
+    out_big = torch.zeros((10, 40, 2), device="cuda")
+    fb.fbfft1D(big[:, 5:69], out_big[:, :33])
+    assert orc.rel_l2(host(out_big[:, :33]), orc.fbfft1d(x)) < FFT_TOL
+    assert float(out_big[:, 33:].abs().max()) == 0.0
+
+
+def test_1d_errors():
+    with pytest.raises(fb.FbfftError) as e:
+        fb.fbfft1D(torch.zeros((2, 512), device="cuda"), torch.zeros((2, 257, 2), device="cuda"))
+    assert e.value.code == fb.ErrorCode.UnsupportedSize
+    with pytest.raises(fb.FbfftError) as e:
+        fb.fbfft1D(torch.zeros((2, 32), device="cuda"), torch.zeros((2, 16, 2), device="cuda"))
+    assert e.value.code == fb.ErrorCode.UnsupportedDimension
+    assert fb.fbfft1D(torch.zeros((0, 32), device="cuda"), torch.zeros((0, 17, 2), device="cuda")) == fb.ErrorCode.Success

@@ -1,0 +1,47 @@
+"""The reference's two-call protocol for N >= 64 (row pass into a caller-owned
+buffer, then column pass), forward and inverse, against the float64 oracle."""
+import numpy as np
+import pytest
+import torch
+
+import fbcuda_b200 as fb
+from oracle import fbfft_oracle as orc
+from tests.util_gpu import FFT_TOL, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [64, 128, 256])
+@pytest.mark.parametrize("b", [1, 2, 5])
+def test_two_call_forward_and_inverse(n, b):
+    rng = np.random.default_rng(n + b)
+    h, w, pl, pu = n - 3, n - 7, 1, 2
+    x = rng.uniform(-1, 1, (b, h, w)).astype(np.float32)
+    xd = dev(x)
+    buf = torch.zeros((b, n, n // 2 + 1, 2), device="cuda")
+    assert fb.fbfft2D(xd, buf, pl, pu) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(buf), orc.fbfft2d_rows(x, n, pl, pu)) < FFT_TOL
+    spec = torch.zeros((b, n // 2 + 1, n, 2), device="cuda")
+    assert fb.fbfft2D_c2c(buf, spec) == fb.ErrorCode.Success
+    want = orc.fbfft2d(x, n, pl, pu)
+    assert orc.rel_l2(host(spec), want) < FFT_TOL
+
+    mid = torch.zeros((b, n, n, 2), device="cuda")
+    assert fb.fbifft2D_c2c(spec, mid) == fb.ErrorCode.Success
+    g = (b + 1) // 2
+    want_mid = orc.fbifft2d_rows(want, n)
+    assert orc.rel_l2(host(mid)[:g], want_mid[:g]) < FFT_TOL
+    assert float(mid[g:].abs().max()) == 0.0 if g < b else True   # only ceil(B/2) slices are written
+    back = torch.full((b, h, w), 7.0, device="cuda")
+    assert fb.fbifft2D(mid, back, pl, pu) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(back), n * n * x.astype(np.float64)) < FFT_TOL
+
+
+def test_two_call_errors():
+    with pytest.raises(fb.FbfftError):
+        # src and dst must differ
+        t = torch.zeros((1, 64, 33, 2), device="cuda")
+        fb.fbfft2D_c2c(t, t.view(1, 33, 64, 2))
+    with pytest.raises(fb.FbfftError) as e:
+        fb.fbfft2D_c2c(torch.zeros((1, 64, 33, 2), device="cuda"), torch.zeros((1, 32, 64, 2), device="cuda"))
+    assert e.value.code == fb.ErrorCode.UnsupportedDimension
