@@ -20,4 +20,10 @@ from .api import (  # noqa: F401
     last_error,
     lib,
     transposeMM,
+    conv_workspace_bytes,
+    conv_workspace_region,
+    conv_update_output,
+    conv_update_grad_input,
+    conv_acc_grad_parameters,
 )
+from . import api  # noqa: F401,E402

@@ -65,6 +65,18 @@ def lib() -> ctypes.CDLL:
         L.fbfft_b200_transpose_mm.argtypes = [ctypes.c_int] * 4 + t4 * 3 + [ctypes.c_float, _vp]
         L.fbfft_b200_iterated_convolution.argtypes = [ctypes.c_int, _vp, _vp, _vp, _ip, _ip, ctypes.c_int,
                                                       ctypes.c_float, ctypes.c_int, ctypes.c_size_t, _vp]
+        sz = ctypes.c_size_t
+        L.fbfft_b200_conv_workspace_bytes.argtypes = [ctypes.c_int] * 4
+        L.fbfft_b200_conv_workspace_bytes.restype = sz
+        L.fbfft_b200_conv_workspace_region.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(sz), ctypes.POINTER(sz)]
+        L.fbfft_b200_conv_workspace_region.restype = ctypes.c_int
+        tp = t4 + [ctypes.c_int, ctypes.c_int]
+        L.fbfft_b200_conv_update_output.argtypes = [ctypes.c_int] + tp + t4 + tp + [_vp, sz, ctypes.c_int, _vp]
+        L.fbfft_b200_conv_update_grad_input.argtypes = [ctypes.c_int] + tp + t4 + tp + [_vp, sz, ctypes.c_int, _vp]
+        L.fbfft_b200_conv_acc_grad_parameters.argtypes = ([ctypes.c_int] + tp + t4 + tp +
+                                                          [ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
+        for name in ("conv_update_output", "conv_update_grad_input", "conv_acc_grad_parameters"):
+            getattr(L, "fbfft_b200_" + name).restype = ctypes.c_int
         for name in ("fbfft1d", "fbifft1d", "fbfft2d", "fbfft2d_c2c", "fbifft2d_c2c", "fbifft2d", "fft2d_r2c",
                      "fft2d_c2r", "transpose_mm", "iterated_convolution"):
             getattr(L, "fbfft_b200_" + name).restype = ctypes.c_int
@@ -197,3 +209,51 @@ def FFTIteratedConvolution(fftSize: int, ins: TiledDeviceTensor, outs: TiledDevi
     return bool(lib().fbfft_b200_iterated_convolution(fftSize, ins.ptr, outs.ptr, w_ptr, w_size, w_stride,
                                                       int(conv_pass), float(scale), int(batchSize), ins.count,
                                                       _stream(stream)))
+
+
+# ---- convolution passes over a caller-owned workspace ---------------------------
+REUSE_INPUT_SPECTRUM = 1
+REUSE_OUTPUT_SPECTRUM = 2
+REUSE_WEIGHT_SPECTRUM = 4
+STOP_AFTER_CONTRACTION = 8
+START_FROM_SPECTRUM = 16
+REGION_INPUT, REGION_OUTPUT, REGION_WEIGHT, REGION_RESULT = 0, 1, 2, 3
+
+
+def conv_workspace_bytes(fftSize: int, batch: int, inPlanes: int, outPlanes: int) -> int:
+    return int(lib().fbfft_b200_conv_workspace_bytes(fftSize, batch, inPlanes, outPlanes))
+
+
+def conv_workspace_region(fftSize: int, batch: int, inPlanes: int, outPlanes: int, which: int):
+    """(offset_bytes, size_bytes) of a spectrum region of the workspace."""
+    off, size = ctypes.c_size_t(), ctypes.c_size_t()
+    _check(lib().fbfft_b200_conv_workspace_region(fftSize, batch, inPlanes, outPlanes, which, ctypes.byref(off),
+                                                  ctypes.byref(size)))
+    return off.value, size.value
+
+
+def _ws(workspace):
+    if not workspace.is_cuda:
+        raise ValueError("workspace must be device memory")
+    return _vp(workspace.data_ptr()), ctypes.c_size_t(workspace.numel() * workspace.element_size())
+
+
+def conv_update_output(fftSize, input, weight, output, workspace, inPad=(0, 0), outPad=(0, 0), flags=0, stream=None):
+    """updateOutput on one tile; pads are (padL, padU)."""
+    return _check(lib().fbfft_b200_conv_update_output(fftSize, *_t(input), inPad[0], inPad[1], *_t(weight),
+                                                      *_t(output), outPad[0], outPad[1], *_ws(workspace), flags,
+                                                      _stream(stream)))
+
+
+def conv_update_grad_input(fftSize, gradInput, weight, gradOutput, workspace, inPad=(0, 0), outPad=(0, 0), flags=0,
+                           stream=None):
+    return _check(lib().fbfft_b200_conv_update_grad_input(fftSize, *_t(gradInput), inPad[0], inPad[1], *_t(weight),
+                                                          *_t(gradOutput), outPad[0], outPad[1], *_ws(workspace),
+                                                          flags, _stream(stream)))
+
+
+def conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, scale=1.0, inPad=(0, 0),
+                             outPad=(0, 0), flags=0, stream=None):
+    return _check(lib().fbfft_b200_conv_acc_grad_parameters(fftSize, *_t(input), inPad[0], inPad[1],
+                                                            *_t(gradWeight), *_t(gradOutput), outPad[0], outPad[1],
+                                                            float(scale), *_ws(workspace), flags, _stream(stream)))

@@ -1,0 +1,254 @@
+// Fourier-domain convolution passes (updateOutput / updateGradInput /
+// accGradParameters) for every supported transform size, as transform ->
+// per-bin contraction -> inverse transform over a caller-owned workspace.
+//
+// The reference ships this chain only as building blocks (fbfft2D, transposeMM,
+// fbifft2D; the host code that chained them lived in its caller) plus a fused
+// prototype for N <= 32 (fbfft/FFTIteratedConvolution.cuh).  The math of each
+// pass is that prototype's (:161-186, :316-341, :482-523) with the contraction
+// roles of MM-inl.cuh:194-196:
+//   updateOutput       outF[b][o] = sum_c inF[b][c] * conj(wF[o][c])
+//   updateGradInput    inF [b][c] = sum_o outF[b][o] * wF[o][c]
+//   accGradParameters  wF  [o][c] = sum_b conj(outF[b][o]) * inF[b][c]
+// every result scaled by 1/N^2 (accGradParameters also by `scale`) and cropped at
+// the tensor's (padU, padL) offset inside the N x N canvas; weights sit at (0, 0).
+#include "../../include/fbfft_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+struct Tensor4 {
+  float* p;
+  int size[4];
+  int stride[4];
+};
+
+long long bins_of(int n) { return (long long)(n / 2 + 1) * n; }
+
+struct Regions {
+  long long in_off, out_off, w_off, res_off, total;  // in floats
+};
+
+Regions regions(int n, long long B, long long C, long long O) {
+  const long long per = bins_of(n) * 2;
+  Regions r;
+  r.in_off = 0;
+  r.out_off = r.in_off + B * C * per;
+  r.w_off = r.out_off + B * O * per;
+  r.res_off = r.w_off + O * C * per;
+  long long m = B * C;
+  if (B * O > m) m = B * O;
+  if (O * C > m) m = O * C;
+  r.total = r.res_off + m * per;
+  return r;
+}
+
+bool fail(const char* msg) {
+  set_last_error(msg);
+  return false;
+}
+
+// [d0][d1][h][w] -> batch of d0*d1 images; the two leading dimensions must collapse
+bool as_images(const Tensor4& t, RealView* v, int* count) {
+  if (t.size[0] > 1 && t.stride[0] != t.size[1] * t.stride[1]) return fail("leading dimensions must be collapsible");
+  v->p = t.p;
+  v->sb = t.stride[1];
+  v->sy = t.stride[2];
+  v->sx = t.stride[3];
+  v->h = t.size[2];
+  v->w = t.size[3];
+  *count = t.size[0] * t.size[1];
+  return true;
+}
+
+CplxView spectrum_view(float* p, int n) {
+  CplxView v;
+  v.p = p;
+  v.sb = bins_of(n) * 2;
+  v.sr = 2 * n;
+  v.sc = 2;
+  v.sz = 1;
+  return v;
+}
+
+int forward(int n, const Tensor4& t, int padL, int padU, float* spec, cudaStream_t s) {
+  RealView v;
+  int count;
+  if (!as_images(t, &v, &count)) return kUnsupportedDimension;
+  if (n <= 32) return fft2d_small_forward(n, v, spectrum_view(spec, n), count, padL, padU, s);
+  return fft2d_large_forward(n, v, spectrum_view(spec, n), count, padL, padU, s);
+}
+
+int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, cudaStream_t s) {
+  RealView v;
+  int count;
+  if (!as_images(t, &v, &count)) return kUnsupportedDimension;
+  if (n <= 32) return fft2d_small_inverse(n, spectrum_view(spec, n), v, count, padL, padU, s);
+  return fft2d_large_inverse(n, spectrum_view(spec, n), v, count, padL, padU, s);
+}
+
+Tensor4 make_tensor(const float* p, const int* size, const int* stride) {
+  Tensor4 t;
+  t.p = const_cast<float*>(p);
+  for (int d = 0; d < 4; ++d) {
+    t.size[d] = size[d];
+    t.stride[d] = stride[d];
+  }
+  return t;
+}
+
+int check_common(int n, const Tensor4& in, const Tensor4& w, const Tensor4& out, void* ws, size_t ws_bytes) {
+  if (!(n == 8 || n == 16 || n == 32 || n == 64 || n == 128)) {
+    set_last_error("convolution: transform size must be 8, 16, 32, 64 or 128");
+    return kUnsupportedSize;
+  }
+  if (in.size[0] != out.size[0] || in.size[1] != w.size[1] || out.size[1] != w.size[0]) {
+    set_last_error("convolution: batch / plane counts of input, weight and output do not agree");
+    return kUnsupportedDimension;
+  }
+  const Regions r = regions(n, in.size[0], in.size[1], out.size[1]);
+  if (!ws || ws_bytes < (size_t)r.total * sizeof(float)) {
+    set_last_error("convolution: workspace too small (see fbfft_b200_conv_workspace_bytes)");
+    return kUnsupportedDimension;
+  }
+  if (reinterpret_cast<uintptr_t>(ws) & 15u) {
+    set_last_error("convolution: workspace must be 16-byte aligned");
+    return kUnsupportedDimension;
+  }
+  return kSuccess;
+}
+
+}  // namespace
+}  // namespace fbfft_b200
+
+using namespace fbfft_b200;
+
+extern "C" {
+
+size_t fbfft_b200_conv_workspace_bytes(int fft_size, int batch, int in_planes, int out_planes) {
+  return (size_t)regions(fft_size, batch, in_planes, out_planes).total * sizeof(float);
+}
+
+int fbfft_b200_conv_workspace_region(int fft_size, int batch, int in_planes, int out_planes, int which,
+                                     size_t* offset_bytes, size_t* size_bytes) {
+  const Regions r = regions(fft_size, batch, in_planes, out_planes);
+  const long long per = bins_of(fft_size) * 2;
+  long long off, sz;
+  switch (which) {
+    case FBFFT_CONV_REGION_INPUT:
+      off = r.in_off, sz = (long long)batch * in_planes * per;
+      break;
+    case FBFFT_CONV_REGION_OUTPUT:
+      off = r.out_off, sz = (long long)batch * out_planes * per;
+      break;
+    case FBFFT_CONV_REGION_WEIGHT:
+      off = r.w_off, sz = (long long)out_planes * in_planes * per;
+      break;
+    case FBFFT_CONV_REGION_RESULT:
+      off = r.res_off, sz = r.total - r.res_off;
+      break;
+    default:
+      set_last_error("conv_workspace_region: unknown region");
+      return kUnsupportedDimension;
+  }
+  if (offset_bytes) *offset_bytes = (size_t)off * sizeof(float);
+  if (size_bytes) *size_bytes = (size_t)sz * sizeof(float);
+  return kSuccess;
+}
+
+int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_size, const int* in_stride, int in_padL,
+                                  int in_padU, const float* weight, const int* w_size, const int* w_stride, float* out,
+                                  const int* out_size, const int* out_stride, int out_padL, int out_padU,
+                                  void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  if (!in || !weight || !out || !in_size || !w_size || !out_size) {
+    set_last_error("null argument");
+    return kUnsupportedDimension;
+  }
+  const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(weight, w_size, w_stride),
+                to = make_tensor(out, out_size, out_stride);
+  int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
+  if (rc) return rc;
+  const int n = fft_size, B = ti.size[0], C = ti.size[1], O = to.size[1];
+  if (B == 0) return kSuccess;
+  const Regions r = regions(n, B, C, O);
+  float* ws = static_cast<float*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long X = bins_of(n);
+  if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, s))) return rc;
+  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, s))) return rc;
+  // res[b][o] = sum_c in[b][c] conj(w[o][c]) / N^2
+  rc = cgemm_bins(false, true, false, ws + r.in_off, C * X, X, ws + r.w_off, C * X, X, ws + r.res_off, O * X, X, B, O, C,
+                  (int)X, 1.0f / ((float)n * (float)n), s);
+  if (rc) return rc;
+  return inverse(n, ws + r.res_off, to, out_padL, out_padU, s);
+}
+
+int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* in_size, const int* in_stride,
+                                      int in_padL, int in_padU, const float* weight, const int* w_size,
+                                      const int* w_stride, const float* grad_out, const int* out_size,
+                                      const int* out_stride, int out_padL, int out_padU, void* workspace,
+                                      size_t workspace_bytes, int flags, void* stream) {
+  if (!grad_in || !weight || !grad_out || !in_size || !w_size || !out_size) {
+    set_last_error("null argument");
+    return kUnsupportedDimension;
+  }
+  const Tensor4 ti = make_tensor(grad_in, in_size, in_stride), tw = make_tensor(weight, w_size, w_stride),
+                to = make_tensor(grad_out, out_size, out_stride);
+  int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
+  if (rc) return rc;
+  const int n = fft_size, B = ti.size[0], C = ti.size[1], O = to.size[1];
+  if (B == 0) return kSuccess;
+  const Regions r = regions(n, B, C, O);
+  float* ws = static_cast<float*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long X = bins_of(n);
+  if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, s)))
+    return rc;
+  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, s))) return rc;
+  // res[b][c] = sum_o out[b][o] w[o][c] / N^2
+  rc = cgemm_bins(false, false, false, ws + r.out_off, O * X, X, ws + r.w_off, C * X, X, ws + r.res_off, C * X, X, B, C,
+                  O, (int)X, 1.0f / ((float)n * (float)n), s);
+  if (rc) return rc;
+  return inverse(n, ws + r.res_off, ti, in_padL, in_padU, s);
+}
+
+int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int* in_size, const int* in_stride,
+                                        int in_padL, int in_padU, float* grad_weight, const int* w_size,
+                                        const int* w_stride, const float* grad_out, const int* out_size,
+                                        const int* out_stride, int out_padL, int out_padU, float scale,
+                                        void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  if (!in || !grad_weight || !grad_out || !in_size || !w_size || !out_size) {
+    set_last_error("null argument");
+    return kUnsupportedDimension;
+  }
+  const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(grad_weight, w_size, w_stride),
+                to = make_tensor(grad_out, out_size, out_stride);
+  int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
+  if (rc) return rc;
+  const int n = fft_size, B = ti.size[0], C = ti.size[1], O = to.size[1];
+  const Regions r = regions(n, B, C, O);
+  float* ws = static_cast<float*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long X = bins_of(n);
+  if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
+    if (B == 0) {
+      if (cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
+    } else {
+      if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, s)))
+        return rc;
+      if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, s)))
+        return rc;
+      // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]
+      rc = cgemm_bins(true, false, false, ws + r.out_off, O * X, X, ws + r.in_off, C * X, X, ws + r.res_off, C * X, X, O,
+                      C, B, (int)X, scale / ((float)n * (float)n), s);
+      if (rc) return rc;
+    }
+  }
+  if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
+  return inverse(n, ws + r.res_off, tw, 0, 0, s);
+}
+
+}  // extern "C"

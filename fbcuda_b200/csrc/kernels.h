@@ -38,6 +38,11 @@ int transpose_mm(int dim, bool conjA, bool conjB, bool accumulate, const float* 
                  const int* a_stride, const float* b, const int* b_size, const int* b_stride, float* c,
                  const int* c_size, const int* c_stride, float inv_norm, cudaStream_t s);
 
+// the same contraction on complex views [d0][d1][X] with strides in complex elements
+int cgemm_bins(bool conjA, bool conjB, bool accumulate, const float* a, long long as0, long long as1, const float* b,
+               long long bs0, long long bs1, float* c, long long cs0, long long cs1, int I, int J, int K, int X,
+               float inv_norm, cudaStream_t s);
+
 // tiled convolution passes (conv_iterated.cu)
 int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs, float* weight,
                          const int* weight_size, const int* weight_stride, int pass, float scale, int batch_size,

@@ -1,6 +1,5 @@
 #include "kernels.h"
 namespace fbfft_b200 {
 #define NI { set_last_error("not implemented"); return kUnsupportedSize; }
-int transpose_mm(int, bool, bool, bool, const float*, const int*, const int*, const float*, const int*, const int*, float*, const int*, const int*, float, cudaStream_t) NI
 int iterated_convolution(int, const fbfft_tiled_tensor4*, const fbfft_tiled_tensor4*, float*, const int*, const int*, int, float, int, size_t, cudaStream_t) { return 0; }
 }

@@ -130,6 +130,70 @@ int fbfft_b200_iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins
                                     float* weight, const int* weight_size, const int* weight_stride, int pass,
                                     float scale, int batch_size, size_t num_tiles, void* stream);
 
+/* ---- Convolution passes over a caller-owned workspace ------------------------
+ * The transform -> per-bin contraction -> inverse transform chain for one tile of
+ * any transform size in {8, 16, 32, 64, 128}.  The reference ships the chain only
+ * as its building blocks (fbfft2D, transposeMM, fbifft2D: MM-inl.cuh:188-196; the
+ * code chaining them lived in its caller) and, for N <= 32, as the fused
+ * FFTIteratedConvolution prototype whose math these follow
+ * (fbfft/FFTIteratedConvolution.cuh:161-186,316-341,482-523).
+ *
+ * in / grad_in   [B][C][ih][iw] placed at (in_padU, in_padL) of the N x N canvas
+ * out / grad_out [B][O][oh][ow] placed at (out_padU, out_padL)
+ * weight         [O][C][kh][kw] placed at (0, 0)
+ * The two leading dimensions of each tensor must be collapsible
+ * (stride[0] == size[1] * stride[1]).
+ *
+ * The workspace holds four spectrum regions (input, output, weight, result); a
+ * pass can skip a forward transform whose spectrum an earlier pass left in the
+ * workspace (REUSE flags), and accGradParameters can stop after the contraction
+ * and resume from the result region so that a caller can all-reduce the
+ * frequency-domain weight gradient across GPUs in between. */
+enum {
+  FBFFT_CONV_REUSE_INPUT_SPECTRUM = 1,
+  FBFFT_CONV_REUSE_OUTPUT_SPECTRUM = 2,
+  FBFFT_CONV_REUSE_WEIGHT_SPECTRUM = 4,
+  FBFFT_CONV_STOP_AFTER_CONTRACTION = 8,
+  FBFFT_CONV_START_FROM_SPECTRUM = 16
+};
+enum {
+  FBFFT_CONV_REGION_INPUT = 0,
+  FBFFT_CONV_REGION_OUTPUT = 1,
+  FBFFT_CONV_REGION_WEIGHT = 2,
+  FBFFT_CONV_REGION_RESULT = 3
+};
+
+size_t fbfft_b200_conv_workspace_bytes(int fft_size, int batch, int in_planes, int out_planes);
+
+/* Byte offset and size of one spectrum region inside the workspace.  Spectra are
+ * [planes...][N/2+1][N][2] floats in the layout of the size class. */
+int fbfft_b200_conv_workspace_region(int fft_size, int batch, int in_planes, int out_planes, int which,
+                                     size_t* offset_bytes, size_t* size_bytes);
+
+/* out[b][o][y][x] = sum_c sum_ij in_canvas[b][c][y+i][x+j] w[o][c][i][j]
+ * (updateOutputIteratedKernel, fbfft/FFTIteratedConvolution.cuh:97-207). */
+int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_size, const int* in_stride, int in_padL,
+                                  int in_padU, const float* weight, const int* w_size, const int* w_stride, float* out,
+                                  const int* out_size, const int* out_stride, int out_padL, int out_padU,
+                                  void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* grad_in[b][c] = sum_o (grad_out_canvas[b][o] circularly convolved with w[o][c])
+ * (updateGradInputIteratedKernel, fbfft/FFTIteratedConvolution.cuh:254-363). */
+int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* in_size, const int* in_stride,
+                                      int in_padL, int in_padU, const float* weight, const int* w_size,
+                                      const int* w_stride, const float* grad_out, const int* out_size,
+                                      const int* out_stride, int out_padL, int out_padU, void* workspace,
+                                      size_t workspace_bytes, int flags, void* stream);
+
+/* grad_weight[o][c][i][j] = scale * sum_b sum_yx in_canvas[b][c][y+i][x+j] grad_out_canvas[b][o][y][x];
+ * overwrites grad_weight (accGradParametersIteratedKernel,
+ * fbfft/FFTIteratedConvolution.cuh:409-524). */
+int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int* in_size, const int* in_stride,
+                                        int in_padL, int in_padU, float* grad_weight, const int* w_size,
+                                        const int* w_stride, const float* grad_out, const int* out_size,
+                                        const int* out_stride, int out_padL, int out_padU, float scale,
+                                        void* workspace, size_t workspace_bytes, int flags, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

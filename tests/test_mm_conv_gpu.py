@@ -1,0 +1,135 @@
+"""GPU parity of the per-bin contraction (transposeMM) and of the three
+convolution passes against float64 (direct convolution for small shapes, the
+float64 FFT convolution -- itself checked against the direct form on CPU -- for
+the BASELINE shapes)."""
+import numpy as np
+import pytest
+import torch
+
+import fbcuda_b200 as fb
+from fbcuda_b200 import api
+from oracle import fbfft_oracle as orc
+from tests.util_gpu import CONV_TOL, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("conj_a,conj_b", [(False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("shape", [(3, 4, 5, 5, 8), (17, 9, 21, 17, 32), (16, 16, 16, 9, 16), (1, 1, 1, 33, 64)])
+def test_transpose_mm(conj_a, conj_b, shape):
+    bsz, p, f, rows, cols = shape
+    rng = np.random.default_rng(sum(shape))
+    if (conj_a, conj_b) == (False, True):
+        a = rng.normal(size=(bsz, p, rows, cols, 2)); b = rng.normal(size=(f, p, rows, cols, 2))
+    elif (conj_a, conj_b) == (True, False):
+        a = rng.normal(size=(bsz, f, rows, cols, 2)); b = rng.normal(size=(bsz, p, rows, cols, 2))
+    else:
+        a = rng.normal(size=(bsz, f, rows, cols, 2)); b = rng.normal(size=(f, p, rows, cols, 2))
+    a, b = a.astype(np.float32), b.astype(np.float32)
+    want = orc.transpose_mm(a, b, None, conj_a, conj_b, False, 0.25)
+    c = torch.full(want.shape, 3.0, device="cuda")
+    assert fb.transposeMM(dev(a), dev(b), c, 0.25, conj_a, conj_b, False) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(c), want) < 1e-5
+    fb.transposeMM(dev(a), dev(b), c, 0.25, conj_a, conj_b, True)   # accumulate
+    assert orc.rel_l2(host(c), 2 * want) < 1e-5
+
+
+def test_transpose_mm_errors():
+    a = torch.zeros((2, 3, 5, 8, 2), device="cuda")
+    with pytest.raises(fb.FbfftError):
+        fb.transposeMM(a, torch.zeros((4, 4, 5, 8, 2), device="cuda"), torch.zeros((2, 4, 5, 8, 2), device="cuda"),
+                       1.0, False, True)
+
+
+def run_passes(n, x, w, go, pad, scale=0.5):
+    b, c, h, _ = x.shape
+    o = w.shape[0]
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    xd, wd, god = dev(x), dev(w), dev(go)
+    out = torch.full(go.shape, 7.0, device="cuda")
+    fb.conv_update_output(n, xd, wd, out, ws, inPad=(pad, pad))
+    gi = torch.full(x.shape, 7.0, device="cuda")
+    fb.conv_update_grad_input(n, gi, wd, god, ws, inPad=(pad, pad))
+    gw = torch.full(w.shape, 7.0, device="cuda")
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, scale=scale, inPad=(pad, pad))
+    torch.cuda.synchronize()
+    return host(out), host(gi), host(gw)
+
+
+@pytest.mark.parametrize("n,hw,k,pad", [(8, 6, 3, 0), (8, 6, 3, 1), (16, 12, 5, 0), (16, 14, 1, 0), (32, 27, 5, 0),
+                                        (32, 30, 3, 1), (64, 40, 3, 1), (64, 58, 7, 0), (128, 100, 13, 0)])
+@pytest.mark.parametrize("bco", [(1, 1, 1), (3, 5, 4), (2, 3, 17)])
+def test_conv_passes_small_shapes_vs_direct(n, hw, k, pad, bco):
+    b, c, o = bco
+    rng = np.random.default_rng(n + hw + k + b)
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    oh = hw + 2 * pad - k + 1
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    out, gi, gw = run_passes(n, x, w, go, pad)
+    assert orc.rel_l2(out, orc.conv_update_output(x, w, pad)) < CONV_TOL
+    assert orc.rel_l2(gi, orc.conv_update_grad_input(go, w, hw, hw, pad)) < CONV_TOL
+    assert orc.rel_l2(gw, orc.conv_acc_grad_parameters(x, go, k, k, pad, 0.5)) < CONV_TOL
+
+
+def test_conv_reuse_flags_and_split_acc_grad():
+    """REUSE flags skip transforms whose spectra are already in the workspace;
+    accGradParameters can stop after the contraction and resume from the result region."""
+    n, b, c, o, hw, k, pad = 32, 4, 6, 5, 27, 5, 0
+    rng = np.random.default_rng(11)
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    oh = hw - k + 1
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    xd, wd, god = dev(x), dev(w), dev(go)
+    out = torch.empty(go.shape, device="cuda")
+    fb.conv_update_output(n, xd, wd, out, ws)
+    gi = torch.empty(x.shape, device="cuda")
+    fb.conv_update_grad_input(n, gi, wd, god, ws, flags=api.REUSE_WEIGHT_SPECTRUM)
+    gw = torch.empty(w.shape, device="cuda")
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM |
+                                api.STOP_AFTER_CONTRACTION)
+    off, size = fb.conv_workspace_region(n, b, c, o, api.REGION_RESULT)
+    spec = ws[off // 4: off // 4 + o * c * 17 * 32 * 2]
+    spec.mul_(2.0)     # what an all-reduce over two identical ranks would leave
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, flags=api.START_FROM_SPECTRUM)
+    assert orc.rel_l2(host(out), orc.conv_update_output(x, w)) < CONV_TOL
+    assert orc.rel_l2(host(gi), orc.conv_update_grad_input(go, w, hw, hw)) < CONV_TOL
+    assert orc.rel_l2(host(gw), 2 * orc.conv_acc_grad_parameters(x, go, k, k)) < CONV_TOL
+
+
+def test_conv_config3_forward():
+    """B=128 C=64 27x27, O=128 5x5, FFT 32 (seeds 2, 3) against the float64 FFT convolution."""
+    x = np.random.default_rng(2).normal(size=(128, 64, 27, 27)).astype(np.float32)
+    w = (np.random.default_rng(3).normal(size=(128, 64, 5, 5)) / np.sqrt(64 * 25)).astype(np.float32)
+    ws = torch.empty(fb.conv_workspace_bytes(32, 128, 64, 128) // 4, device="cuda")
+    out = torch.empty((128, 128, 23, 23), device="cuda")
+    fb.conv_update_output(32, dev(x), dev(w), out, ws)
+    sub = slice(0, 16)
+    want = orc.fftconv_update_output(x[sub], w, 32)
+    assert orc.rel_l2(host(out[sub]), want) < CONV_TOL
+
+
+def test_conv_config4_reduced_batch():
+    """C=128 O=128 56x56 k3 pad1 FFT 64 (config 4 at batch 4) fwd + both gradients."""
+    b = 4
+    x = np.random.default_rng(4).normal(size=(b, 128, 56, 56)).astype(np.float32)
+    w = (np.random.default_rng(5).normal(size=(128, 128, 3, 3)) * np.sqrt(2.0 / (128 * 9))).astype(np.float32)
+    go = np.random.default_rng(6).normal(size=(b, 128, 56, 56)).astype(np.float32)
+    out, gi, gw = run_passes(64, x, w, go, 1, scale=1.0)
+    assert orc.rel_l2(out, orc.fftconv_update_output(x, w, 64, 1)) < CONV_TOL
+    assert orc.rel_l2(gi, orc.fftconv_update_grad_input(go, w, 64, 56, 56, 1)) < CONV_TOL
+    assert orc.rel_l2(gw, orc.fftconv_acc_grad_parameters(x, go, 64, 3, 3, 1)) < CONV_TOL
+
+
+def test_conv_config5_reduced_batch():
+    """C=96 O=96 128x128 k13 FFT 128 (config 5 at batch 2) fwd + both gradients."""
+    b = 2
+    x = np.random.default_rng(7).normal(size=(b, 96, 128, 128)).astype(np.float32)
+    w = (np.random.default_rng(8).normal(size=(96, 96, 13, 13)) / np.sqrt(96 * 169)).astype(np.float32)
+    go = np.random.default_rng(9).normal(size=(b, 96, 116, 116)).astype(np.float32)
+    out, gi, gw = run_passes(128, x, w, go, 0, scale=1.0)
+    assert orc.rel_l2(out, orc.fftconv_update_output(x, w, 128)) < CONV_TOL
+    assert orc.rel_l2(gi, orc.fftconv_update_grad_input(go, w, 128, 128, 128)) < CONV_TOL
+    assert orc.rel_l2(gw, orc.fftconv_acc_grad_parameters(x, go, 128, 13, 13)) < CONV_TOL
