@@ -1,0 +1,459 @@
+#!/usr/bin/env python
+"""Benchmark of the fbfft hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload fft2d|conv] [--fft-size 32] [--extras 0|1]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one
+batch of synthetic input:
+
+* workload "fft2d" (default): one batched fbfft2D call over 1 GiB of fp32 images
+  per GPU (the N = 32 point of the BASELINE size sweep; other points with
+  --fft-size).  Metric: algorithmic GB/s, (4*h*w + 8*N*(N/2+1)) bytes per image.
+  The batch shards over GPUs with no communication (weak scaling).
+* workload "conv": updateOutput + updateGradInput + accGradParameters of the
+  FFT-64 layer (B=64, C=O=128, 56x56, 3x3, pad 1), batch sharded over GPUs,
+  frequency-domain weight gradient all-reduced with NCCL.  Metric: images/s.
+
+--impl reference times the reference path's CPU restatement (the reference has no
+CPU implementation and is GPU-only code that does not build for sm_100 unmodified)
+on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GIB = 1 << 30
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the
+# ncu capture summarised in profiles/ (captured on 65536 images, scaled by images per launch)
+NCU_TRAFFIC_BYTES_PER_IMAGE = {}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        rows = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or \
+               [r for (_, r) in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        reasons = set()
+        for r in rows:
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(rows), "power_w_max": max(float(r[3]) for r in rows)}
+
+
+def fft_bytes_per_image(n, h, w):
+    return 4 * h * w + 8 * n * (n // 2 + 1)
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_fft2d_sample(n, seconds_target=12.0):
+    """Times the scalar restatement of the reference algorithm on all host cores on a
+    bounded sample of the workload; returns (GB/s, cores, description)."""
+    import numpy as np
+    from oracle import cpuref
+    cores = max(1, cpuref.hardware_threads())
+    rng = np.random.default_rng(1)
+    b = max(cores * 64, 4096 * 32 * 32 // (n * n))
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    out = np.zeros((b, n // 2 + 1, n, 2), np.float32)
+    cpuref.fbfft2d(x, n, threads=cores, out=out)       # warm-up, page faults
+    times = []
+    t_all = time.time()
+    while len(times) < 5 or (time.time() - t_all < seconds_target and len(times) < 50):
+        t0 = time.perf_counter()
+        cpuref.fbfft2d(x, n, threads=cores, out=out)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    gbs = b * fft_bytes_per_image(n, n, n) / med / 1e9
+    return gbs, cores, f"fbfft2D N={n} over {b} images of {n}x{n} (median of {len(times)} runs, {med*1e3:.1f} ms each)", med
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    n = args.fft_size
+    if args.workload == "conv":
+        import numpy as np
+        from oracle import cpuref
+        cores = max(1, cpuref.hardware_threads())
+        b, c, o, hw, k, pad, nn = 2, 128, 128, 56, 3, 1, 64
+        rng = np.random.default_rng(4)
+        x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+        w = rng.normal(size=(o, c, k, k)).astype(np.float32)
+        go = rng.normal(size=(b, o, hw, hw)).astype(np.float32)
+        times = []
+        for it in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            for p in range(3):
+                cpuref.conv_pass(p, x, go, w, nn, in_pad=(pad, pad), threads=cores)
+            if it >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        ms = statistics.mean(times) * 1e3
+        val = b / (ms / 1e3)
+        line = {"impl": "reference", "metric": "FFT-conv layer fwd+bwd images/s", "value": val, "unit": "images/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "conv fwd+bwd B=64 C=128 O=128 56x56 k3 pad1 FFT64", "sample": f"batch {b} of 64"},
+                "cpu_baseline": {"value": val, "unit": "images/s", "cores": cores, "kind": "port",
+                                 "sample": f"batch {b} of 64 per step"},
+                "e2e": {"value": val, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+    import numpy as np
+    from oracle import cpuref
+    cores = max(1, cpuref.hardware_threads())
+    b = max(cores * 64, 8192 * 32 * 32 // (n * n))
+    rng = np.random.default_rng(1)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    out = np.zeros((b, n // 2 + 1, n, 2), np.float32)
+    times = []
+    for it in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        cpuref.fbfft2d(x, n, threads=cores, out=out)
+        if it >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    ms = statistics.mean(times) * 1e3
+    gbs = b * fft_bytes_per_image(n, n, n) / (ms / 1e3) / 1e9
+    line = {"impl": "reference", "metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"fbfft2D N={n}, 1 GiB fp32 input per GPU ([{GIB // (4 * n * n)}][{n}][{n}])",
+                       "sample": f"{b} images per step on {cores} host threads"},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                             "sample": f"{b} images of {n}x{n} per step"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def dist_setup(args):
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier_sync(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world):
+    import torch
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(fn, steps, warmup, world):
+    """W untimed steps, then exactly K steps between CUDA events on the current
+    stream, bracketed by barrier + synchronize; returns max-over-ranks ms per step."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    barrier_sync(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier_sync(world)
+    return max_over_ranks(e0.elapsed_time(e1) / steps, world)
+
+
+def run_fft2d(args, world, rank, local):
+    import torch
+    import fbcuda_b200 as fb
+    n = args.fft_size
+    b = GIB // (4 * n * n)
+    if args.profile_case:
+        # small case for an ncu capture: 256 MiB of input (still larger than L2), the
+        # timed launches only
+        b //= 4
+    gen = torch.Generator(device="cuda").manual_seed(1 + rank)
+    x = torch.rand((b, n, n), device="cuda", generator=gen) * 2 - 1
+    spec = torch.empty((b, n // 2 + 1, n, 2), device="cuda")
+    per_image = fft_bytes_per_image(n, n, n)
+
+    def step():
+        fb.fft2d_r2c(n, x, spec)
+
+    if args.profile_case and args.inverse:
+        back = torch.empty_like(x)
+        fb.fft2d_r2c(n, x, spec)
+
+        def step():  # noqa: F811
+            fb.fft2d_c2r(n, spec, back)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t0 = time.time()
+    ms = time_steps(step, args.steps, max(3, args.warmup), world)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    gbs = world * b * per_image / (ms / 1e3) / 1e9
+    if args.profile_case:
+        return {"metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
+                "config": {"workload": f"profile case: fbfft2D N={n} over {b} images"}, "clocks": clocks}
+
+    # end to end through the public call with HOST buffers: H2D of the images, the
+    # transform, D2H of the spectrum, every step
+    xh = torch.empty((b, n, n), dtype=torch.float32).pin_memory()
+    xh.copy_(x.cpu())
+    sh = torch.empty((b, n // 2 + 1, n, 2), dtype=torch.float32).pin_memory()
+
+    def step_e2e():
+        x.copy_(xh, non_blocking=True)
+        fb.fft2d_r2c(n, x, spec)
+        sh.copy_(spec, non_blocking=True)
+
+    ms_e2e = time_steps(step_e2e, max(2, args.steps // 4), 3, world)
+    e2e = {"value": world * b * per_image / (ms_e2e / 1e3) / 1e9, "unit": "GB/s",
+           "h2d_bytes_per_step": b * n * n * 4, "d2h_bytes_per_step": b * (n // 2 + 1) * n * 8,
+           "ms_per_step": ms_e2e}
+    del xh, sh
+
+    peak, how = measured_peak_gbs()
+    achieved = b * per_image / (ms / 1e3) / 1e9      # per GPU; one launch per step
+    traffic = NCU_TRAFFIC_BYTES_PER_IMAGE.get(n)
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": f"of {how}", "frac_of_8TBs": achieved / 8000.0,
+                "traffic": traffic * b if traffic else None, "algorithmic_bytes_per_launch": b * per_image,
+                "kernel": "fft2d_small_fwd_kernel" if n <= 32 else "fft2d_large_fwd_kernel"}
+    extra = {}
+    if args.extras and rank == 0 and world == 1:
+        extra = run_extras(args, x, spec, n)
+    line = {"metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"fbfft2D N={n}, 1 GiB fp32 input per GPU ([{b}][{n}][{n}] -> [{b}][{n // 2 + 1}][{n}] complex)",
+                       "l2": "inputs (1 GiB) and outputs exceed the 126 MB L2, no flush needed",
+                       "parallelism": f"batch sharded over {world} GPU(s), no collective"},
+            "e2e": e2e, "gpu_launches": args.steps, "roofline": roofline, "clocks": clocks}
+    if rank == 0 and world == 1:
+        gb, cores, sample, _ = cpu_fft2d_sample(n)
+        line["cpu_baseline"] = {"value": gb, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+    if extra:
+        line["extra"] = extra
+    return line
+
+
+def run_extras(args, x, spec, n0):
+    """Size sweep forward + inverse (1 GiB input each) on one GPU, for the record."""
+    import torch
+    import fbcuda_b200 as fb
+    del x, spec
+    torch.cuda.empty_cache()
+    peak, _ = measured_peak_gbs()
+    sweep = {}
+    for n in (8, 16, 32, 64, 128, 256):
+        b = GIB // (4 * n * n)
+        x = torch.rand((b, n, n), device="cuda") * 2 - 1
+        spec = torch.empty((b, n // 2 + 1, n, 2), device="cuda")
+        back = torch.empty_like(x)
+        ms_f = time_steps(lambda: fb.fft2d_r2c(n, x, spec), 10, 3, 1)
+        entry = {"fwd_us": ms_f * 1e3, "fwd_gbs": b * fft_bytes_per_image(n, n, n) / ms_f / 1e6}
+        entry["fwd_frac_of_measured"] = entry["fwd_gbs"] / peak
+        if n <= 128:
+            ms_i = time_steps(lambda: fb.fft2d_c2r(n, spec, back), 10, 3, 1)
+            entry["inv_us"] = ms_i * 1e3
+            entry["inv_gbs"] = b * fft_bytes_per_image(n, n, n) / ms_i / 1e6
+            entry["inv_frac_of_measured"] = entry["inv_gbs"] / peak
+        sweep[str(n)] = entry
+        del x, spec, back
+        torch.cuda.empty_cache()
+    return {"sweep_1GiB": sweep}
+
+
+def run_conv(args, world, rank, local):
+    """FFT-64 layer (B=64, C=O=128, 56x56, k3, pad 1): fwd + gradInput + gradWeight
+    with the batch sharded over the GPUs and the frequency-domain weight gradient
+    all-reduced (sum) over NCCL between the contraction and its inverse transform."""
+    import torch
+    import fbcuda_b200 as fb
+    from fbcuda_b200 import api
+    cfg = {"conv4": (64, 128, 128, 56, 3, 1, 64), "conv5": (32, 96, 96, 128, 13, 0, 128),
+           "conv3": (128, 64, 128, 27, 5, 0, 32)}[args.conv_config]
+    bg, c, o, hw, k, pad, n = cfg
+    if bg % world:
+        raise SystemExit(f"batch {bg} does not shard over {world} GPUs")
+    b = bg // world
+    oh = hw + 2 * pad - k + 1
+    gen = torch.Generator(device="cuda").manual_seed(4 + rank)
+    x = torch.randn((b, c, hw, hw), device="cuda", generator=gen)
+    w = torch.randn((o, c, k, k), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)) * \
+        (2.0 / (c * k * k)) ** 0.5
+    go = torch.randn((b, o, oh, oh), device="cuda", generator=gen)
+    out = torch.empty_like(go)
+    gi = torch.empty_like(x)
+    gw = torch.empty_like(w)
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    off, _ = fb.conv_workspace_region(n, b, c, o, api.REGION_RESULT)
+    wspec = ws[off // 4: off // 4 + o * c * (n // 2 + 1) * n * 2]
+    ip = (pad, pad)
+
+    def step():
+        fb.conv_update_output(n, x, w, out, ws, inPad=ip)
+        fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
+        if world > 1 and args.dw_mode == "frequency":
+            import torch.distributed as dist
+            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.REUSE_INPUT_SPECTRUM |
+                                        api.REUSE_OUTPUT_SPECTRUM | api.STOP_AFTER_CONTRACTION)
+            dist.all_reduce(wspec)
+            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.START_FROM_SPECTRUM)
+        else:
+            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip,
+                                        flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
+            if world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(gw)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    t0 = time.time()
+    ms = time_steps(step, args.steps, max(3, args.warmup), world)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    ips = bg / (ms / 1e3)
+
+    xh, goh = x.cpu().pin_memory(), go.cpu().pin_memory()
+    gwh = torch.empty(gw.shape).pin_memory()
+
+    def step_e2e():
+        x.copy_(xh, non_blocking=True)
+        go.copy_(goh, non_blocking=True)
+        step()
+        gwh.copy_(gw, non_blocking=True)
+
+    ms_e2e = time_steps(step_e2e, max(2, args.steps // 2), 3, world)
+    bins = (n // 2 + 1) * n
+    flops = 3 * 8.0 * bg * c * o * bins
+    line = {"metric": "FFT-conv layer fwd+bwd images/s", "value": ips, "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"conv fwd+gradInput+gradWeight B={bg} C={c} O={o} {hw}x{hw} k{k} pad{pad} FFT{n}",
+                       "parallelism": f"batch sharded over {world} GPU(s), weights replicated, dW all-reduce in the {args.dw_mode} domain",
+                       "l2": "spectra (hundreds of MB) exceed the 126 MB L2"},
+            "e2e": {"value": bg / (ms_e2e / 1e3), "unit": "images/s",
+                    "h2d_bytes_per_step": (x.numel() + go.numel()) * 4, "d2h_bytes_per_step": gw.numel() * 4,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": args.steps * 9, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": None, "peak": measured_peak_gbs()[0], "unit": "GB/s", "frac": None,
+                         "traffic": None, "contraction_tflops": flops / world / (ms / 1e3) / 1e12,
+                         "note": "per-step time covers 6 transform batches and 3 contractions; see profiles/"}}
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fft2d", choices=["fft2d", "conv"])
+    ap.add_argument("--conv-config", default="conv4", choices=["conv3", "conv4", "conv5"])
+    ap.add_argument("--dw-mode", default="frequency", choices=["frequency", "spatial"])
+    ap.add_argument("--fft-size", type=int, default=32)
+    ap.add_argument("--extras", type=int, default=1)
+    ap.add_argument("--profile-case", action="store_true", help="small fft2d case for profiler captures")
+    ap.add_argument("--inverse", action="store_true", help="profile case: time fbifft2D instead of fbfft2D")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    world, rank, local = dist_setup(args)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+    line = run_fft2d(args, world, rank, local) if args.workload == "fft2d" else run_conv(args, world, rank, local)
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
