@@ -194,6 +194,31 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
                                         const int* out_stride, int out_padL, int out_padU, float scale,
                                         void* workspace, size_t workspace_bytes, int flags, void* stream);
 
+/* updateOutput without any device allocation, for callers that must not allocate:
+ * a plugin invoked while its host holds the allocator, a loop with a
+ * no-allocation rule after start-up, a process whose device memory is already
+ * fully handed out.  Has no counterpart in the reference.
+ *
+ * Same arguments and result as fbfft_b200_conv_update_output without workspace and
+ * flags: the spectra live in a fixed scratch area of
+ * FBFFT_B200_NOALLOC_SCRATCH_BYTES that is part of the library image, so every GPU
+ * that loads the library carries that much extra memory until the process exits.
+ * Layers whose fbfft_b200_conv_workspace_bytes() exceeds it are refused with
+ * FBFFT_UNSUPPORTED_SIZE.  The function calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ *
+ * The first call on each device looks up the device address of the scratch area
+ * (with that device current); make that first call outside any stream capture.
+ * All calls on a device share the one scratch area and it keeps whatever the last
+ * call left in it: nothing in it needs clearing between calls, but two calls that
+ * overlap on the GPU (different streams, or graphs replayed concurrently) race on
+ * it -- serialise them. */
+#define FBFFT_B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+int fbfft_b200_conv_update_output_noalloc(int fft_size, const float* in, const int* in_size, const int* in_stride,
+                                          int in_padL, int in_padU, const float* weight, const int* w_size,
+                                          const int* w_stride, float* out, const int* out_size,
+                                          const int* out_stride, int out_padL, int out_padU, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
