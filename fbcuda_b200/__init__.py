@@ -18,6 +18,7 @@ from .api import (  # noqa: F401
     fft2d_c2r,
     fft2d_r2c,
     last_error,
+    device_status,
     lib,
     transposeMM,
     conv_workspace_bytes,

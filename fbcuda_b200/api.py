@@ -84,6 +84,11 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+def device_status() -> int:
+    """0 when no kernel recorded a device-side error (synchronises)."""
+    return int(lib().fbfft_b200_device_status())
+
+
 def last_error() -> str:
     return lib().fbfft_b200_last_error().decode()
 

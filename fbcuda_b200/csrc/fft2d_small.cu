@@ -4,138 +4,143 @@
 // kernels (fbfft/FFT2D32.cuh:361-533, dispatched from fbfft/FBFFT2D-inl.cuh:476-570
 // and fbfft/FBIFFT2D-inl.cuh:591-682).  Output layout is the reference's for this
 // size class: [B][ky in 0..N/2][kx in 0..N) complex, Hermitian half along the ROW
-// frequency; inverse is unnormalised (returns N*N*x) and crops at (padU, padL).
+// frequency; the inverse is unnormalised (returns N*N*x) and crops at (padU, padL).
 //
 // Design: a warp owns 32/(N/2) images at a time and never synchronises with any
 // other warp.  Both passes are length-N complex FFTs held entirely in one
-// thread's registers:
-//   pass A  thread (image, l) loads columns l and l+N/2 as re/im of one complex
-//           line (coalesced 4-byte loads, zero padding by predicate), transforms
-//           it and separates the two real-input spectra; rows 0 and N/2 are real
-//           and travel packed as one complex row;
+// thread's registers (fft2d_small.cuh):
+//   pass A  thread (image, l) takes columns l and l+N/2 as re/im of one complex
+//           line, transforms it and separates the two real-input spectra; rows 0
+//           and N/2 are real and travel packed as one complex row;
 //   pass B  after a transpose through padded shared memory, thread (image, r)
-//           transforms packed row r; row 0 is then unpacked into rows 0 and N/2;
-//   store   the finished (N/2+1) x N block is copied out with 16-byte stores.
-// The inverse runs the same passes backwards.  No twiddle is ever shuffled or
-// read from memory.
-#include "common.cuh"
-#include "fft_regs.cuh"
+//           transforms packed row r; row 0 is then unpacked into rows 0 and N/2.
+// Data movement on the fast path (contiguous, 16-byte aligned tensors) is
+// asynchronous: the raw images of the NEXT task are fetched with cp.async.bulk into
+// a per-warp staging slot while the current task computes (completion on a
+// per-warp mbarrier), and finished rows leave through bulk stores; neither costs
+// issue slots or registers.  Strided or unaligned tensors take plain loads/stores
+// with the same arithmetic.  No twiddle is ever shuffled or read from memory.
+#include "fft2d_small.cuh"
+#include "kernels.h"
 
 namespace fbfft_b200 {
 
 namespace {
 
-// Shared-memory pitches in float2 units: RS between rows of an image, IS between
-// images of a warp.  Chosen by exhaustive search so that the 8-byte column writes
-// of pass A, the 16-byte row reads of pass B and the 16-byte copy-out are free of
-// bank conflicts (N = 8 keeps a 2-way conflict on the row reads).
-template <int N>
-struct SmallCfg;
-template <>
-struct SmallCfg<8> {
-  static constexpr int RS = 8, IS = 44;
-};
-template <>
-struct SmallCfg<16> {
-  static constexpr int RS = 18, IS = 168;
-};
-template <>
-struct SmallCfg<32> {
-  static constexpr int RS = 34, IS = 578;
-};
-
 constexpr int kSmallThreads = 128;
+constexpr int kWarps = kSmallThreads / 32;
 
-template <int N>
-__device__ __forceinline__ void load_row(const float2* row, float2 (&v)[N]) {
-#pragma unroll
-  for (int c = 0; c < N; c += 2) {
-    float4 t = *reinterpret_cast<const float4*>(row + c);
-    v[c] = make_float2(t.x, t.y);
-    v[c + 1] = make_float2(t.z, t.w);
-  }
-}
+enum : int { kErrFwdWait = 101, kErrInvWait = 102 };
 
 // ------------------------------------------------------------------ forward
-template <int N, bool VEC>
-__global__ void __launch_bounds__(kSmallThreads, 4) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
-                                                                       int padU, int ntasks) {
+// IN_BULK : real input is contiguous [B][h][w] with a 16-byte aligned base
+// OUT_BULK: complex output is contiguous [B][N/2+1][N][2] with a 16-byte aligned base
+template <int N, bool IN_BULK, bool OUT_BULK>
+__global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
+                                                                          int padU, int ntasks, int slot_floats) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
   constexpr int RS = SmallCfg<N>::RS, IS = SmallCfg<N>::IS;
   extern __shared__ __align__(16) float2 smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wpc = blockDim.x >> 5;
   float2* buf = smem + warp * (IPW * IS);
   const int li = lane / T, l = lane % T;
   float2* ib = buf + li * IS;
+  // staging slots (IN_BULK) follow the work buffers; mbarriers follow the slots
+  float* slot = reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) + warp * slot_floats;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) +
+                                                                   kWarps * slot_floats);
+  const unsigned bar = smem_u32(bars + warp);
+  const long long img_floats = (long long)in.h * in.w;
+  const long long total_bytes = (long long)B * img_floats * 4;
 
-  for (int task = blockIdx.x * wpc + warp; task < ntasks; task += gridDim.x * wpc) {
+  const int first = blockIdx.x * kWarps + warp, stride = gridDim.x * kWarps;
+  // bytes [lo, hi) of the 16-byte aligned window around the images of `task`;
+  // returns false when the window would reach past the end of the tensor
+  auto window = [&](int task, long long* lo, unsigned* bytes) {
+    const long long g0 = (long long)task * IPW * img_floats * 4;
+    long long g1 = g0 + IPW * img_floats * 4;
+    if (g1 > total_bytes) g1 = total_bytes;
+    *lo = g0 & ~15LL;
+    const long long hi = (g1 + 15) & ~15LL;
+    *bytes = (unsigned)(hi - *lo);
+    return hi <= total_bytes || (total_bytes & 15) == 0;
+  };
+  unsigned phase = 0;
+  bool staged = false;  // the slot holds (or will hold) the current task
+  if (IN_BULK) {
+    if (lane == 0) mbar_init(bar, 1);
+    __syncwarp();
+    if (first < ntasks) {
+      long long lo;
+      unsigned bytes;
+      staged = window(first, &lo, &bytes);
+      if (staged && lane == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(smem_u32(slot), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
+      }
+    }
+  }
+
+  for (int task = first; task < ntasks; task += stride) {
     const int b = task * IPW + li;
     const bool valid = b < B;
     {
-      // ---- pass A: columns l and l+T of image b as one complex line
+      // ---- pass A
       float2 a[N];
-      const float* src = in.p + (long long)(valid ? b : 0) * in.sb;
-      const unsigned x0 = (unsigned)(l - padL), x1 = (unsigned)(l + T - padL);
-      const bool ok0 = valid && x0 < (unsigned)in.w, ok1 = valid && x1 < (unsigned)in.w;
-#pragma unroll
-      for (int y = 0; y < N; ++y) {
-        const unsigned yy = (unsigned)(y - padU);
-        const bool oky = yy < (unsigned)in.h;
-        a[y].x = (oky && ok0) ? __ldg(src + (long long)yy * in.sy + (long long)x0 * in.sx) : 0.f;
-        a[y].y = (oky && ok1) ? __ldg(src + (long long)yy * in.sy + (long long)x1 * in.sx) : 0.f;
+      if (IN_BULK && staged) {
+        if (!mbar_wait(bar, phase, kErrFwdWait)) return;
+        phase ^= 1;
+        const long long g0 = (long long)task * IPW * img_floats * 4;
+        const int off0 = (int)((g0 & 15) >> 2);
+        load_columns<N>(slot + off0 + li * img_floats, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
+      } else {
+        load_columns<N>(in.p + (long long)(valid ? b : 0) * in.sb, in.sy, in.sx, in.h, in.w, padL, padU, valid, l, a);
       }
-      fft_bitrev<N, false>(a);
-      // separate: A = (Z[r] + conj Z[N-r]) / 2 (column l), Bc = (Z[r] - conj Z[N-r]) / 2i (column l+T)
-      {
-        const float2 z0 = a[0], zh = a[brev(N / 2, N)];
-        ib[l] = make_float2(z0.x, zh.x);
-        ib[l + T] = make_float2(z0.y, zh.y);
-      }
-      static_for<T - 1>([&](auto rc) {
-        constexpr int r = decltype(rc)::value + 1;
-        const float2 zr = a[brev(r, N)], zm = a[brev(N - r, N)];
-        ib[r * RS + l] = make_float2(0.5f * (zr.x + zm.x), 0.5f * (zr.y - zm.y));
-        ib[r * RS + l + T] = make_float2(0.5f * (zr.y + zm.y), 0.5f * (zm.x - zr.x));
-      });
-    }
-    __syncwarp();
-    {
-      // ---- pass B: packed row l of image li
-      float2 v[N];
-      load_row<N>(ib + l * RS, v);
-      fft_bitrev<N, false>(v);
-      static_for<N / 2>([&](auto cc) {
-        constexpr int c = decltype(cc)::value * 2;
-        const float2 p = v[brev(c, N)], q = v[brev(c + 1, N)];
-        *reinterpret_cast<float4*>(ib + l * RS + c) = make_float4(p.x, p.y, q.x, q.y);
-      });
-    }
-    __syncwarp();
-    {
-      // ---- unpack row 0 = F[0] + i F[N/2]: lane l owns the pair (kx, N-kx), kx = l
-      // (lane 0 owns the self-paired kx = 0 and kx = N/2)
-      const int k0 = (l == 0) ? 0 : l, k1 = (l == 0) ? T : N - l;
-      const float2 va = ib[k0], vb = ib[k1];
-      const float2 ma = (l == 0) ? va : vb;  // V[(N-k0)%N]
-      const float2 mb = (l == 0) ? vb : va;  // V[(N-k1)%N]
-      ib[k0] = make_float2(0.5f * (va.x + ma.x), 0.5f * (va.y - ma.y));
-      ib[T * RS + k0] = make_float2(0.5f * (va.y + ma.y), 0.5f * (ma.x - va.x));
-      ib[k1] = make_float2(0.5f * (vb.x + mb.x), 0.5f * (vb.y - mb.y));
-      ib[T * RS + k1] = make_float2(0.5f * (vb.y + mb.y), 0.5f * (mb.x - vb.x));
-    }
-    __syncwarp();
-    // ---- copy out IPW images x ROWS x N complex
-    if (VEC) {
-      constexpr int PER = ROWS * (N / 2);  // float4 per image
-      for (int e = lane; e < IPW * PER; e += 32) {
-        const int img = e / PER, rem = e % PER, row = rem / (N / 2), c4 = rem % (N / 2);
-        const int bb = task * IPW + img;
-        if (bb < B) {
-          const float4 t = *reinterpret_cast<const float4*>(buf + img * IS + row * RS + c4 * 2);
-          *reinterpret_cast<float4*>(out.p + (long long)bb * out.sb + (long long)rem * 4) = t;
+      if (IN_BULK) {
+        // everything of this task is in registers: fetch the next task into the slot
+        __syncwarp();
+        const int next = task + stride;
+        staged = false;
+        if (next < ntasks) {
+          long long lo;
+          unsigned bytes;
+          staged = window(next, &lo, &bytes);
+          if (staged && lane == 0) {
+            fence_async_smem();
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(smem_u32(slot), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
+          }
         }
       }
+      fft_bitrev<N, false>(a);
+      if (OUT_BULK) {
+        // rows of the previous task may still be leaving the work buffer
+        bulk_wait_read();
+        __syncwarp();
+      }
+      fwd_separate_store<N>(a, ib, l);
+    }
+    __syncwarp();
+    fwd_rows_unpack<N>(ib, l);
+    // ---- store IPW images x ROWS rows x N complex
+    if (OUT_BULK) {
+      fence_async_smem();
+      __syncwarp();
+      if (RS == N) {
+        // rows are contiguous in shared memory: one copy per image
+        if (lane < IPW && task * IPW + lane < B)
+          bulk_s2g(out.p + (long long)(task * IPW + lane) * out.sb, smem_u32(buf + lane * IS), ROWS * N * 8);
+      } else {
+        for (int r = lane; r < IPW * ROWS; r += 32) {
+          const int img = r / ROWS, row = r % ROWS;
+          const int bb = task * IPW + img;
+          if (bb < B)
+            bulk_s2g(out.p + (long long)bb * out.sb + (long long)row * (2 * N), smem_u32(buf + img * IS + row * RS),
+                     N * 8);
+        }
+      }
+      bulk_commit();
     } else {
       constexpr int PER = ROWS * N;
       for (int e = lane; e < IPW * PER; e += 32) {
@@ -148,35 +153,69 @@ __global__ void __launch_bounds__(kSmallThreads, 4) fft2d_small_fwd_kernel(RealV
           dst[out.sz] = t.y;
         }
       }
+      __syncwarp();
     }
-    __syncwarp();
   }
+  if (OUT_BULK) bulk_wait_read();
 }
 
 // ------------------------------------------------------------------ inverse
-template <int N, bool VEC>
-__global__ void __launch_bounds__(kSmallThreads, 4) fft2d_small_inv_kernel(CplxView in, RealView out, int B, int padL,
-                                                                       int padU, int ntasks) {
+// IN_BULK: complex input contiguous and 16-byte aligned; rows are fetched with bulk
+// copies one task ahead into the second of two work buffers.
+template <int N, bool IN_BULK>
+__global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxView in, RealView out, int B, int padL,
+                                                                          int padU, int ntasks) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
   constexpr int RS = SmallCfg<N>::RS, IS = SmallCfg<N>::IS;
+  constexpr int NBUF = IN_BULK ? 2 : 1;
   extern __shared__ __align__(16) float2 smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wpc = blockDim.x >> 5;
-  float2* buf = smem + warp * (IPW * IS);
+  float2* wbuf = smem + warp * (NBUF * IPW * IS);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kWarps * (NBUF * IPW * IS));
   const int li = lane / T, l = lane % T;
-  float2* ib = buf + li * IS;
+  const int first = blockIdx.x * kWarps + warp, stride = gridDim.x * kWarps;
 
-  for (int task = blockIdx.x * wpc + warp; task < ntasks; task += gridDim.x * wpc) {
-    // ---- copy in
-    if (VEC) {
-      constexpr int PER = ROWS * (N / 2);
-      for (int e = lane; e < IPW * PER; e += 32) {
-        const int img = e / PER, rem = e % PER, row = rem / (N / 2), c4 = rem % (N / 2);
-        const int bb = task * IPW + img;
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (bb < B) t = __ldg(reinterpret_cast<const float4*>(in.p + (long long)bb * in.sb + (long long)rem * 4));
-        *reinterpret_cast<float4*>(buf + img * IS + row * RS + c4 * 2) = t;
+  // issue the row copies of `task` into buffer `which`; completion on that buffer's barrier
+  auto fetch = [&](int task, int which) {
+    float2* dstbuf = wbuf + which * (IPW * IS);
+    const unsigned bar = smem_u32(bars + warp * 2 + which);
+    int imgs = B - task * IPW;
+    if (imgs > IPW) imgs = IPW;
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_expect_tx(bar, (unsigned)(imgs * ROWS * N * 8));
+    __syncwarp();
+    if (RS == N) {
+      // rows are contiguous in shared memory: one copy per image
+      if (lane < imgs)
+        bulk_g2s(smem_u32(dstbuf + lane * IS), in.p + (long long)(task * IPW + lane) * in.sb, ROWS * N * 8, bar);
+    } else {
+      for (int r = lane; r < imgs * ROWS; r += 32) {
+        const int img = r / ROWS, row = r % ROWS;
+        bulk_g2s(smem_u32(dstbuf + img * IS + row * RS),
+                 in.p + (long long)(task * IPW + img) * in.sb + (long long)row * (2 * N), N * 8, bar);
       }
+    }
+  };
+
+  unsigned phase[2] = {0, 0};
+  int cur = 0;
+  if (IN_BULK) {
+    if (lane == 0) {
+      mbar_init(smem_u32(bars + warp * 2), 1);
+      mbar_init(smem_u32(bars + warp * 2 + 1), 1);
+    }
+    __syncwarp();
+    if (first < ntasks) fetch(first, 0);
+  }
+
+  for (int task = first; task < ntasks; task += stride) {
+    float2* buf = wbuf + cur * (IPW * IS);
+    float2* ib = buf + li * IS;
+    if (IN_BULK) {
+      if (task + stride < ntasks) fetch(task + stride, cur ^ 1);
+      if (!mbar_wait(smem_u32(bars + warp * 2 + cur), phase[cur], kErrInvWait)) return;
+      phase[cur] ^= 1;
     } else {
       constexpr int PER = ROWS * N;
       for (int e = lane; e < IPW * PER; e += 32) {
@@ -189,87 +228,70 @@ __global__ void __launch_bounds__(kSmallThreads, 4) fft2d_small_inv_kernel(CplxV
         }
         buf[img * IS + row * RS + c] = t;
       }
+      __syncwarp();
     }
-    __syncwarp();
+    inv_pack_rows<N>(ib, l);
     {
-      // ---- pack rows 0 and N/2 into row 0: P = F[0] + i F[N/2]; the imaginary
-      // parts of F[0][0] and F[N/2][0] carry no information and are dropped
-      // (fbfft/FFT2D32.cuh:313-315)
-      const int k0 = l, k1 = l + T;
-      const float2 a0 = ib[k0], h0 = ib[T * RS + k0], a1 = ib[k1], h1 = ib[T * RS + k1];
-      ib[k0] = (l == 0) ? make_float2(a0.x, h0.x) : make_float2(a0.x - h0.y, a0.y + h0.x);
-      ib[k1] = make_float2(a1.x - h1.y, a1.y + h1.x);
-    }
-    __syncwarp();
-    {
-      // ---- pass B^-1: inverse transform of packed row l along kx
-      float2 v[N];
-      load_row<N>(ib + l * RS, v);
-      fft_bitrev<N, true>(v);
-      static_for<N / 2>([&](auto cc) {
-        constexpr int c = decltype(cc)::value * 2;
-        const float2 p = v[brev(c, N)], q = v[brev(c + 1, N)];
-        *reinterpret_cast<float4*>(ib + l * RS + c) = make_float4(p.x, p.y, q.x, q.y);
-      });
-    }
-    __syncwarp();
-    {
-      // ---- pass A^-1: columns l and l+T; Z[r] = G_l[r] + i G_{l+T}[r] with the
-      // Hermitian extension G[N-r] = conj G[r]
       float2 z[N];
-      {
-        const float2 g0 = ib[l], g1 = ib[l + T];
-        z[0] = make_float2(g0.x, g1.x);
-        z[N / 2] = make_float2(g0.y, g1.y);
-      }
-      static_for<T - 1>([&](auto rc) {
-        constexpr int r = decltype(rc)::value + 1;
-        const float2 g0 = ib[r * RS + l], g1 = ib[r * RS + l + T];
-        z[r] = make_float2(g0.x - g1.y, g0.y + g1.x);
-        z[N - r] = make_float2(g0.x + g1.y, g1.x - g0.y);
-      });
-      fft_bitrev<N, true>(z);
+      inv_columns<N>(ib, l, z);
       const int b = task * IPW + li;
-      if (b < B) {
-        float* dst = out.p + (long long)b * out.sb;
-        const unsigned x0 = (unsigned)(l - padL), x1 = (unsigned)(l + T - padL);
-        const bool ok0 = x0 < (unsigned)out.w, ok1 = x1 < (unsigned)out.w;
-        static_for<N>([&](auto yc) {
-          constexpr int y = decltype(yc)::value;
-          const unsigned yy = (unsigned)(y - padU);
-          if (yy < (unsigned)out.h) {
-            const float2 t = z[brev(y, N)];
-            if (ok0) dst[(long long)yy * out.sy + (long long)x0 * out.sx] = t.x;
-            if (ok1) dst[(long long)yy * out.sy + (long long)x1 * out.sx] = t.y;
-          }
-        });
-      }
+      if (b < B) store_columns<N>(out.p + (long long)b * out.sb, out.sy, out.sx, out.h, out.w, padL, padU, l, z, 1.0f);
     }
     __syncwarp();
+    cur ^= IN_BULK ? 1 : 0;
   }
 }
 
 template <int N>
-constexpr int small_smem_bytes() {
-  return (kSmallThreads / 32) * (32 / (N / 2)) * SmallCfg<N>::IS * (int)sizeof(float2);
+constexpr int work_floats() {
+  return kWarps * (32 / (N / 2)) * SmallCfg<N>::IS * 2;
 }
 
-bool cplx_is_vectorizable(const CplxView& c, int rows, int cols) {
+bool cplx_is_contiguous16(const CplxView& c, int cols) {
   return c.sz == 1 && c.sc == 2 && c.sr == 2 * cols && (c.sb % 4) == 0 && aligned16(c.p);
+}
+bool real_is_contiguous16(const RealView& r, int B) {
+  return r.sx == 1 && r.sy == r.w && (B <= 1 || r.sb == (long long)r.h * r.w) && aligned16(r.p);
+}
+
+int grid_for(int ntasks, int per_sm) {
+  const int want = (ntasks + kWarps - 1) / kWarps;
+  const int cap = sm_count() * per_sm;
+  return want < cap ? want : cap;
+}
+
+template <typename K>
+void allow_smem(K kernel, int bytes) {
+  if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
 template <int N>
 int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
   constexpr int IPW = 32 / (N / 2);
   const int ntasks = (B + IPW - 1) / IPW;
-  const int wpc = kSmallThreads / 32;
-  const int want = (ntasks + wpc - 1) / wpc;
-  const int grid = want < sm_count() * 8 ? want : sm_count() * 8;
-  const int smem = small_smem_bytes<N>();
-  if (cplx_is_vectorizable(out, N / 2 + 1, N)) {
-    fft2d_small_fwd_kernel<N, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+  const bool out_bulk = cplx_is_contiguous16(out, N);
+  const int hw = in.h * in.w;
+  // staging slot per warp: the raw images of one task plus alignment slack
+  const int slot_floats = ((IPW * hw + 8 + 3) / 4) * 4;
+  const bool in_bulk = real_is_contiguous16(in, B) && in.h <= N && in.w <= N;
+  const int base = work_floats<N>() * 4;
+  if (in_bulk) {
+    const int smem = base + kWarps * slot_floats * 4 + kWarps * 8;
+    const int grid = grid_for(ntasks, 3);
+    if (out_bulk) {
+      allow_smem(fft2d_small_fwd_kernel<N, true, true>, smem);
+      fft2d_small_fwd_kernel<N, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats);
+    } else {
+      allow_smem(fft2d_small_fwd_kernel<N, true, false>, smem);
+      fft2d_small_fwd_kernel<N, true, false><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats);
+    }
   } else {
-    fft2d_small_fwd_kernel<N, false><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    const int grid = grid_for(ntasks, 4);
+    if (out_bulk) {
+      fft2d_small_fwd_kernel<N, false, true><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0);
+    } else {
+      fft2d_small_fwd_kernel<N, false, false><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0);
+    }
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -278,14 +300,13 @@ template <int N>
 int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
   constexpr int IPW = 32 / (N / 2);
   const int ntasks = (B + IPW - 1) / IPW;
-  const int wpc = kSmallThreads / 32;
-  const int want = (ntasks + wpc - 1) / wpc;
-  const int grid = want < sm_count() * 8 ? want : sm_count() * 8;
-  const int smem = small_smem_bytes<N>();
-  if (cplx_is_vectorizable(in, N / 2 + 1, N)) {
-    fft2d_small_inv_kernel<N, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+  const int base = work_floats<N>() * 4;
+  if (cplx_is_contiguous16(in, N)) {
+    const int smem = 2 * base + kWarps * 16;
+    allow_smem(fft2d_small_inv_kernel<N, true>, smem);
+    fft2d_small_inv_kernel<N, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
   } else {
-    fft2d_small_inv_kernel<N, false><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    fft2d_small_inv_kernel<N, false><<<grid_for(ntasks, 4), kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks);
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -318,6 +339,12 @@ int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, i
     default:
       return kUnsupportedSize;
   }
+}
+
+int read_device_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
 }
 
 }  // namespace fbfft_b200

@@ -48,4 +48,7 @@ int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbf
                          const int* weight_size, const int* weight_stride, int pass, float scale, int batch_size,
                          size_t num_tiles, cudaStream_t s);
 
+// value of the device-side error word (0 = none; set when a bounded wait inside a kernel ran out)
+int read_device_error();
+
 }  // namespace fbfft_b200

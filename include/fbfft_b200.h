@@ -46,6 +46,12 @@ int fbfft_b200_version(void);
 /* Text describing the last non-success return on the calling thread. */
 const char* fbfft_b200_last_error(void);
 
+/* Synchronising health check (no counterpart in the reference): returns 0 when no
+ * kernel of this library has recorded a device-side error on the current device,
+ * else the code it recorded (a bounded wait on an asynchronous copy that ran out:
+ * 101 forward, 102 inverse 2-D transform), or -1 if the status cannot be read. */
+int fbfft_b200_device_status(void);
+
 /* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
  * -- fbfft/FBFFT.cuh:11-16, fbfft/FBFFT-inl.cuh:19-87.
  * real [B][N], N = real_size[1] in {8..256}; complex [B][N/2+1][2].

@@ -148,3 +148,8 @@ def test_config2_shapes_roundtrip():
     sub = slice(0, 512)
     assert orc.rel_l2(host(spec[sub]), orc.fbfft2d(x[sub], 32)) < FFT_TOL
     assert orc.rel_l2(host(back) / 1024.0, x) < FFT_TOL
+
+
+def test_no_device_error_recorded():
+    """Bounded waits inside the kernels record an error instead of hanging; none may have fired."""
+    assert fb.device_status() == 0

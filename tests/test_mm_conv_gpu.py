@@ -133,3 +133,67 @@ def test_conv_config5_reduced_batch():
     assert orc.rel_l2(out, orc.fftconv_update_output(x, w, 128)) < CONV_TOL
     assert orc.rel_l2(gi, orc.fftconv_update_grad_input(go, w, 128, 128, 128)) < CONV_TOL
     assert orc.rel_l2(gw, orc.fftconv_acc_grad_parameters(x, go, 128, 13, 13)) < CONV_TOL
+
+
+def _tiles(arrs_pads):
+    return fb.TiledDeviceTensor([(t, pl, pu) for (t, pl, pu) in arrs_pads])
+
+
+@pytest.mark.parametrize("n,hw,k,pad", [(8, 6, 3, 0), (16, 12, 3, 1), (16, 14, 5, 0), (32, 27, 5, 0), (32, 30, 3, 1)])
+@pytest.mark.parametrize("bco", [(1, 1, 1), (3, 5, 4), (2, 3, 7)])
+def test_iterated_convolution_single_tile(n, hw, k, pad, bco):
+    """FFTIteratedConvolution<N> with the reference's tile descriptors (one tile)."""
+    b, c, o = bco
+    rng = np.random.default_rng(n * 7 + hw + b)
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    oh = hw + 2 * pad - k + 1
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    xd, wd, god = dev(x), dev(w), dev(go)
+    out = torch.full(go.shape, 7.0, device="cuda")
+    assert fb.FFTIteratedConvolution(n, _tiles([(xd, pad, pad)]), _tiles([(out, 0, 0)]), wd, 0, 1.0, b) is True
+    assert orc.rel_l2(host(out), orc.conv_update_output(x, w, pad)) < CONV_TOL
+    gi = torch.full(x.shape, 7.0, device="cuda")
+    assert fb.FFTIteratedConvolution(n, _tiles([(gi, pad, pad)]), _tiles([(god, 0, 0)]), wd, 1, 1.0, b) is True
+    assert orc.rel_l2(host(gi), orc.conv_update_grad_input(go, w, hw, hw, pad)) < CONV_TOL
+    gw = torch.full(w.shape, 7.0, device="cuda")
+    assert fb.FFTIteratedConvolution(n, _tiles([(xd, pad, pad)]), _tiles([(god, 0, 0)]), gw, 2, 0.5, b) is True
+    assert orc.rel_l2(host(gw), orc.conv_acc_grad_parameters(x, go, k, k, pad, 0.5)) < CONV_TOL
+    assert fb.device_status() == 0
+
+
+def test_iterated_convolution_tiled_input():
+    """A 20x20 input convolved with 3x3 through four overlapping 16x16 tiles (overlap-save):
+    every tile is a strided view of the big tensors with its own pads, as the reference's
+    caller builds them; accGradParameters sums over tiles."""
+    n, k, b, c, o = 16, 3, 2, 3, 4
+    big, step = 28, 14            # each tile yields 14x14 outputs from a 16x16 input window
+    rng = np.random.default_rng(99)
+    x = rng.normal(size=(b, c, big + k - 1, big + k - 1)).astype(np.float32)
+    w = rng.normal(size=(o, c, k, k)).astype(np.float32)
+    go = rng.normal(size=(b, o, big, big)).astype(np.float32)
+    xd, wd, god = dev(x), dev(w), dev(go)
+    out = torch.zeros((b, o, big, big), device="cuda")
+    ins, outs, gouts = [], [], []
+    for ty in range(0, big, step):
+        for tx in range(0, big, step):
+            ins.append((xd[:, :, ty:ty + n, tx:tx + n], 0, 0))
+            outs.append((out[:, :, ty:ty + step, tx:tx + step], 0, 0))
+            gouts.append((god[:, :, ty:ty + step, tx:tx + step], 0, 0))
+    assert fb.FFTIteratedConvolution(n, _tiles(ins), _tiles(outs), wd, 0, 1.0, b)
+    assert orc.rel_l2(host(out), orc.conv_update_output(x, w)) < CONV_TOL
+    gw = torch.zeros_like(wd)
+    assert fb.FFTIteratedConvolution(n, _tiles(ins), _tiles(gouts), gw, 2, 1.0, b)
+    assert orc.rel_l2(host(gw), orc.conv_acc_grad_parameters(x, go, k, k)) < CONV_TOL
+    # the float64 definition of the tiled entry point agrees tile by tile
+    want_tiles = orc.iterated_convolution(n, [(host(t), 0, 0) for (t, _, _) in ins],
+                                          [(np.zeros((b, o, step, step)), 0, 0) for _ in outs], w, 0)
+    for (t, _, _), want in zip(outs, want_tiles):
+        assert orc.rel_l2(host(t), want) < CONV_TOL
+
+
+def test_iterated_convolution_rejects_unknown():
+    x = torch.zeros((1, 1, 8, 8), device="cuda")
+    t = _tiles([(x, 0, 0)])
+    assert fb.FFTIteratedConvolution(64, t, t, torch.zeros((1, 1, 3, 3), device="cuda"), 0, 1.0, 1) is False
+    assert fb.FFTIteratedConvolution(8, t, t, torch.zeros((1, 1, 3, 3), device="cuda"), 3, 1.0, 1) is False
