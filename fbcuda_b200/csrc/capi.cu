@@ -99,7 +99,10 @@ int fbfft_b200_version(void) { return 100; }
 
 const char* fbfft_b200_last_error(void) { return g_last_error; }
 
-int fbfft_b200_device_status(void) { return read_device_error(); }
+int fbfft_b200_device_status(void) {
+  const int a = read_device_error(), b = read_device_error_coop();
+  return a != 0 ? a : b;
+}
 
 int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const int* real_stride, float* cplx,
                          const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream) {

@@ -1,0 +1,413 @@
+// Single-call batched 2-D real-to-complex / complex-to-real FFTs for N = 64 and
+// N = 128 on contiguous tensors, in the reference's layout for this size class:
+// transposed spectrum [B][kx in 0..N/2][ky in 0..N) (what its two calls,
+// fbfft/FBFFT2D-inl.cuh:597-617 then :627-669, leave behind), unnormalised inverse
+// with crop at (padU, padL) (fbfft/FBIFFT2D-inl.cuh:529-742).
+//
+// One block owns one image, which never leaves the SM between the two passes (the
+// reference round-trips a [B][N][N/2+1] buffer through HBM).  Every 1-D transform
+// is a length-N complex FFT shared by Q = N/32 neighbouring lanes: a radix-Q
+// decimation-in-frequency step on each lane's own data, one exchange between the Q
+// lanes with __shfl_xor_sync, then an independent 32-point FFT held in each lane's
+// registers with compile-time twiddles (fft_regs.cuh).
+//   forward  pass A: lanes (q, p) take columns p and p+N/2 as re/im of one complex
+//            line (coalesced global loads, zero padding by predicate) and transform
+//            along y; all N bins of the line go to shared memory, mid[ky][p];
+//            pass B: lanes (q, ky) rebuild row ky of the two real-input spectra from
+//            mid[ky][*] and mid[N-ky][*] while loading, transform along x and scatter
+//            the result (and its Hermitian mirror) into the transposed output tile;
+//            rows ky = 0 and N/2 are real and travel as one complex row.
+//            The finished tile leaves through cp.async.bulk row stores.
+//   inverse  the same two passes backwards; the spectrum rows arrive through
+//            cp.async.bulk copies completing on an mbarrier (bounded wait).
+#include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+enum : int { kErrCoopInvWait = 103 };
+
+template <int N>
+struct CoopCfg;
+// R: length of the FFT one lane holds in registers; Q = N/R lanes share a line.
+template <>
+struct CoopCfg<64> {
+  static constexpr int R = 64, Q = 1, PM = 34, PO = 66, BLOCKS_PER_SM = 12, MIN_BLOCKS = 10;
+};
+template <>
+struct CoopCfg<128> {
+  static constexpr int R = 64, Q = 2, PM = 66, PO = 130, BLOCKS_PER_SM = 3, MIN_BLOCKS = 3;
+};
+
+// Length-N = R*Q complex FFT shared by Q lanes (lane index bits above log2(32/Q)
+// select q; Q = 1 is a plain in-register FFT).  In: a[m*P + jl] = x[jl + P*q + R*m],
+// P = R/Q.  Out: a[brev(k, R)] = X[Q*k + q].  lf[qq] = exp(-+2*pi*i*q*qq/(Q*Q)) is
+// the part of the twiddle that depends on the lane.
+template <int N, int R, int Q, bool INV>
+__device__ __forceinline__ void coop_fft(float2 (&a)[R], int q, const float2 (&lf)[Q]) {
+  if constexpr (Q == 1) {
+    fft_bitrev<R, INV>(a);
+  } else {
+    constexpr int P = R / Q;
+    constexpr int LP = 32 / Q;  // lanes per q group
+    constexpr int LOGQ = ilog2c(Q);
+    // radix-Q step over m for every jl: output qq lands at a[brev(qq, Q)*P + jl]
+    static_for<P>([&](auto jc) {
+      constexpr int jl = decltype(jc)::value;
+      Dif<Q, jl, P, INV, R>::run(a);
+    });
+    float2 c[R];
+    static_for<Q>([&](auto qc) {
+      constexpr int qq = decltype(qc)::value;
+      static_for<P>([&](auto jc) {
+        constexpr int jl = decltype(jc)::value;
+        float2 v = mul_tw<jl * qq, N, INV>(a[brev(qq, Q) * P + jl]);
+        if (qq > 0) v = cmul(v, lf[qq]);
+        c[qq * P + jl] = v;
+      });
+    });
+    // all-to-all between the Q lanes: block qq goes to lane qq; afterwards block i holds
+    // what lane i sent, i.e. c[i*P + jl] is element j = jl + P*i of this lane's R-point input
+    static_for<LOGQ>([&](auto tc) {
+      constexpr int t = decltype(tc)::value;
+      const bool mybit = (q >> t) & 1;
+      static_for<Q / 2>([&](auto ic) {
+        constexpr int idx = decltype(ic)::value;
+        constexpr int i0 = ((idx >> t) << (t + 1)) | (idx & ((1 << t) - 1));
+        constexpr int i1 = i0 | (1 << t);
+        static_for<P>([&](auto jc) {
+          constexpr int jl = decltype(jc)::value;
+          const float2 lo = c[i0 * P + jl], hi = c[i1 * P + jl];
+          const float sx = mybit ? lo.x : hi.x, sy = mybit ? lo.y : hi.y;
+          const float rx = __shfl_xor_sync(0xffffffffu, sx, LP << t);
+          const float ry = __shfl_xor_sync(0xffffffffu, sy, LP << t);
+          c[i0 * P + jl] = mybit ? make_float2(rx, ry) : lo;
+          c[i1 * P + jl] = mybit ? hi : make_float2(rx, ry);
+        });
+      });
+    });
+    fft_bitrev<R, INV>(c);
+#pragma unroll
+    for (int i = 0; i < R; ++i) a[i] = c[i];
+  }
+}
+
+// block-wide barrier; a one-warp block only needs the warp to reconverge
+template <int THREADS>
+__device__ __forceinline__ void block_sync() {
+  if constexpr (THREADS <= 32) {
+    __syncwarp();
+  } else {
+    __syncthreads();
+  }
+}
+
+template <int Q, bool INV>
+__device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
+#pragma unroll
+  for (int qq = 0; qq < Q; ++qq) {
+    float s, c;
+    sincospif((INV ? 2.0f : -2.0f) * (float)(q * qq) / (float)(Q * Q), &s, &c);
+    lf[qq] = make_float2(c, s);
+  }
+}
+
+// ------------------------------------------------------------------ forward
+template <int N>
+__global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
+                                                                                long long out_sb, int B, int padL,
+                                                                                int padU) {
+  constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
+  constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
+  constexpr int H = N / 2, T = H * Q;
+  extern __shared__ __align__(16) float2 smem[];
+  float2* mid = smem;   // [N][PM]        pass A -> pass B
+  float2* tile = smem;  // [H+1][PO] + packed row [N]   pass B -> bulk stores (aliases mid)
+  float2* vs = smem + (H + 1) * PO;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP, item = warp * LP + (lane % LP);  // item: column pair p (pass A), row r (pass B)
+  float2 lf[Q];
+  lane_factors<Q, false>(q, lf);
+
+  for (int b = blockIdx.x; b < B; b += gridDim.x) {
+    float2 a[R];
+    {
+      // ---- pass A: columns item and item+H, rows y = jl + P*q + R*m
+      const float* src = in.p + (long long)b * in.sb;
+      const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
+      const bool ok0 = x0 < (unsigned)in.w, ok1 = x1 < (unsigned)in.w;
+      const float* p0 = src + (long long)x0 * in.sx + (long long)(P * q - padU) * in.sy;
+      const float* p1 = src + (long long)x1 * in.sx + (long long)(P * q - padU) * in.sy;
+      const int ybase = P * q - padU;
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) {
+          const int yo = jl + R * m;
+          const bool oky = (unsigned)(ybase + yo) < (unsigned)in.h;
+          a[m * P + jl].x = (oky && ok0) ? __ldg(p0 + (long long)yo * in.sy) : 0.f;
+          a[m * P + jl].y = (oky && ok1) ? __ldg(p1 + (long long)yo * in.sy) : 0.f;
+        }
+      }
+      coop_fft<N, R, Q, false>(a, q, lf);
+      // the previous image's rows may still be leaving the tile that mid aliases
+      bulk_wait_read();
+      block_sync<T>();
+      static_for<R>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        mid[(Q * k + q) * PM + item] = a[brev(k, R)];
+      });
+    }
+    block_sync<T>();
+    {
+      // ---- pass B: row item (0 = packed rows 0 and N/2).  The lane needs x = jl + P*q + R*m;
+      // x < H comes from the first column of pair p = x, x >= H from the second of p = x - H
+      const int r = item;
+      const float2* row1 = mid + r * PM;
+      const float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
+      auto take = [&](float4 u, float4 v, float2& a0, float2& a1, float2& b0, float2& b1) {
+        if (r == 0) {
+          a0 = make_float2(u.x, v.x), b0 = make_float2(u.y, v.y);
+          a1 = make_float2(u.z, v.z), b1 = make_float2(u.w, v.w);
+        } else {
+          a0 = make_float2(0.5f * (u.x + v.x), 0.5f * (u.y - v.y)), b0 = make_float2(0.5f * (u.y + v.y), 0.5f * (v.x - u.x));
+          a1 = make_float2(0.5f * (u.z + v.z), 0.5f * (u.w - v.w)), b1 = make_float2(0.5f * (u.w + v.w), 0.5f * (v.z - u.z));
+        }
+      };
+      if constexpr (Q == 1) {
+#pragma unroll
+        for (int p = 0; p < H; p += 2) {
+          const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
+          take(u, v, a[p], a[p + 1], a[p + H], a[p + H + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < Q / 2; ++m) {
+#pragma unroll
+          for (int jl = 0; jl < P; jl += 2) {
+            const int p = jl + P * q + R * m;
+            const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
+            take(u, v, a[m * P + jl], a[m * P + jl + 1], a[(m + Q / 2) * P + jl], a[(m + Q / 2) * P + jl + 1]);
+          }
+        }
+      }
+      coop_fft<N, R, Q, false>(a, q, lf);
+      block_sync<T>();  // every lane has read its part of mid: the tile may overwrite it
+      if (r == 0) {
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          vs[Q * k + q] = a[brev(k, R)];
+        });
+      } else {
+        float2* direct = tile + r;                 // tile[kx][ky = r]
+        float2* mirror = tile + (N - r);           // tile[(N-kx)%N][N - r], conjugated
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          const int kx = Q * k + q;
+          const float2 v = a[brev(k, R)];
+          if (Q * k + Q - 1 <= H || kx <= H) {
+            if (kx <= H) direct[kx * PO] = v;
+          }
+          if (Q * k >= H - (Q - 1) || k == 0) {
+            if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
+          }
+        });
+      }
+    }
+    block_sync<T>();
+    // rows ky = 0 and N/2 from the packed row: V = F[0] + i F[N/2]
+    for (int kx = threadIdx.x; kx <= H; kx += T) {
+      const float2 v = vs[kx], m = vs[(N - kx) & (N - 1)];
+      tile[kx * PO] = make_float2(0.5f * (v.x + m.x), 0.5f * (v.y - m.y));
+      tile[kx * PO + H] = make_float2(0.5f * (v.y + m.y), 0.5f * (m.x - v.x));
+    }
+    fence_async_smem();
+    block_sync<T>();
+    float* dst = out + (long long)b * out_sb;
+    for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
+    bulk_commit();
+  }
+  bulk_wait_read();
+}
+
+// ------------------------------------------------------------------ inverse
+template <int N>
+__global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
+                                                                                long long in_sb, RealView out, int B,
+                                                                                int padL, int padU) {
+  constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
+  constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
+  constexpr int H = N / 2, T = H * Q;
+  extern __shared__ __align__(16) float2 smem[];
+  constexpr int REGION = (H + 1) * PO > N * PM ? (H + 1) * PO : N * PM;
+  float2* tile = smem;  // [H+1][PO]   spectrum rows as stored: tile[kx][ky]
+  float2* mid = smem;   // [N][PM]     aliases the tile (consumed before mid is written)
+  unsigned long long* bar_mem = reinterpret_cast<unsigned long long*>(smem + REGION);
+  const unsigned bar = smem_u32(bar_mem);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP, item = warp * LP + (lane % LP);
+  float2 lf[Q];
+  lane_factors<Q, true>(q, lf);
+  if (threadIdx.x == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  block_sync<T>();
+  unsigned phase = 0;
+  auto fetch = [&](int b) {
+    // all threads: earlier reads of the tile are done (caller synchronised)
+    fence_async_smem();
+    if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)((H + 1) * N * 8));
+    block_sync<T>();
+    const float* src = in + (long long)b * in_sb;
+    for (int kx = threadIdx.x; kx <= H; kx += T) bulk_g2s(smem_u32(tile + kx * PO), src + (long long)kx * (2 * N), N * 8, bar);
+  };
+  if (blockIdx.x < B) fetch(blockIdx.x);
+
+  for (int b = blockIdx.x; b < B; b += gridDim.x) {
+    float2 a[R];
+    if (!mbar_wait(bar, phase, kErrCoopInvWait)) return;
+    phase ^= 1;
+    {
+      // ---- pass B^-1: row item along kx = jl + P*q + R*m; row 0 packs ky = 0 and N/2.
+      // F[ky][kx] = tile[kx][ky] for kx <= H, else conj(tile[N-kx][(N-ky)%N]).
+      const int r = item;
+      const float2* c1 = tile + r;                       // tile[kx][r]
+      const float2* c2 = tile + ((N - r) & (N - 1));     // tile[N-kx][(N-r)%N]
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) {
+          const int kx = jl + P * q + R * m;
+          if (r == 0) {
+            // the imaginary parts of F[0][0] and F[N/2][0] carry nothing (both rows are
+            // transforms of real sequences) and are dropped
+            float2 f0, fh;
+            if (kx <= H) {
+              f0 = tile[kx * PO], fh = tile[kx * PO + H];
+            } else {
+              f0 = tile[(N - kx) * PO], fh = tile[(N - kx) * PO + H];
+              f0.y = -f0.y, fh.y = -fh.y;
+            }
+            a[m * P + jl] = (kx == 0) ? make_float2(f0.x, fh.x) : make_float2(f0.x - fh.y, f0.y + fh.x);
+          } else if (kx <= H) {
+            a[m * P + jl] = c1[kx * PO];
+          } else {
+            const float2 t = c2[(N - kx) * PO];
+            a[m * P + jl] = make_float2(t.x, -t.y);
+          }
+        }
+      }
+    }
+    block_sync<T>();  // the tile is consumed: mid may overwrite it
+    coop_fft<N, R, Q, true>(a, q, lf);
+    {
+      // lane holds G[ky][x] at x = Q*k + q; columns x and x+H share a complex line:
+      // Z_p[ky] = G_p[ky] + i G_{p+H}[ky], Z_p[N-ky] = conj(G_p[ky]) + i conj(G_{p+H}[ky]).
+      // x + H = Q*(k + R/2) + q sits in the same lane.
+      const int r = item;
+      static_for<R / 2>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        const int p = Q * k + q;
+        const float2 g0 = a[brev(k, R)], g1 = a[brev(k + R / 2, R)];
+        if (r == 0) {
+          mid[p] = make_float2(g0.x, g1.x);
+          mid[H * PM + p] = make_float2(g0.y, g1.y);
+        } else {
+          mid[r * PM + p] = make_float2(g0.x - g1.y, g0.y + g1.x);
+          mid[(N - r) * PM + p] = make_float2(g0.x + g1.y, g1.x - g0.y);
+        }
+      });
+    }
+    block_sync<T>();
+    {
+      // ---- pass A^-1: column pair item along ky = jl + P*q + R*m
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) a[m * P + jl] = mid[(jl + P * q + R * m) * PM + item];
+      }
+      block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
+      if (b + gridDim.x < B) fetch(b + gridDim.x);
+      coop_fft<N, R, Q, true>(a, q, lf);
+      float* dst = out.p + (long long)b * out.sb;
+      const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
+      const bool ok0 = x0 < (unsigned)out.w, ok1 = x1 < (unsigned)out.w;
+      float* p0 = dst + (long long)x0 * out.sx + (long long)(q - padU) * out.sy;
+      float* p1 = dst + (long long)x1 * out.sx + (long long)(q - padU) * out.sy;
+      static_for<R>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        if ((unsigned)(Q * k + q - padU) < (unsigned)out.h) {
+          const float2 t = a[brev(k, R)];
+          if (ok0) p0[(long long)(Q * k) * out.sy] = t.x;
+          if (ok1) p1[(long long)(Q * k) * out.sy] = t.y;
+        }
+      });
+    }
+  }
+}
+
+template <int N>
+constexpr int fwd_smem() {
+  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO + N;
+  return (mid > tile ? mid : tile) * (int)sizeof(float2);
+}
+template <int N>
+constexpr int inv_smem() {
+  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO;
+  return (mid > tile ? mid : tile) * (int)sizeof(float2) + 16;
+}
+
+template <int N>
+int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    configured[dev] = true;
+  }
+  const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
+  fft2d_coop_fwd_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+template <int N>
+int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    configured[dev] = true;
+  }
+  const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
+  fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+}  // namespace
+
+bool fft2d_coop_supported(int n, const CplxView& c) {
+  return (n == 64 || n == 128) && c.sz == 1 && c.sc == 2 && c.sr == 2 * n && (c.sb % 4) == 0 && aligned16(c.p);
+}
+
+int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (n == 64) return launch_fwd<64>(in, out, B, padL, padU, s);
+  return launch_fwd<128>(in, out, B, padL, padU, s);
+}
+
+int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (n == 64) return launch_inv<64>(in, out, B, padL, padU, s);
+  return launch_inv<128>(in, out, B, padL, padU, s);
+}
+
+int read_device_error_coop() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace fbfft_b200

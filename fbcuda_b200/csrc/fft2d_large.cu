@@ -184,6 +184,7 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
 }  // namespace
 
 int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (fft2d_coop_supported(n, out)) return fft2d_coop_forward(n, in, out, B, padL, padU, s);
   if (n == 64) return launch_fwd<64>(in, out, B, padL, padU, s);
   if (n == 128) return launch_fwd<128>(in, out, B, padL, padU, s);
   if (n == 256) {
@@ -200,6 +201,7 @@ int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, i
 }
 
 int fft2d_large_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (fft2d_coop_supported(n, in)) return fft2d_coop_inverse(n, in, out, B, padL, padU, s);
   if (n == 64) return launch_inv<64>(in, out, B, padL, padU, s);
   if (n == 128) return launch_inv<128>(in, out, B, padL, padU, s);
   set_last_error("single-call inverse is available for N <= 128; use the two-call protocol for N = 256");

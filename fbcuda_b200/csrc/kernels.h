@@ -16,6 +16,11 @@ int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, i
 // N in {64, 128, 256}: transposed [B][N/2+1 (kx)][N (ky)] layout (fft2d_large.cu)
 int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_large_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
+// contiguous fast path for N in {64, 128} (fft2d_coop.cu)
+bool fft2d_coop_supported(int n, const CplxView& c);
+int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
+int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
+int read_device_error_coop();
 // the reference's two-call protocol for N >= 64 (fft_lines.cu)
 int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, int B, int padL, int padU,
                              cudaStream_t s);

@@ -49,7 +49,7 @@ const char* fbfft_b200_last_error(void);
 /* Synchronising health check (no counterpart in the reference): returns 0 when no
  * kernel of this library has recorded a device-side error on the current device,
  * else the code it recorded (a bounded wait on an asynchronous copy that ran out:
- * 101 forward, 102 inverse 2-D transform), or -1 if the status cannot be read. */
+ * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128), or -1 if the status cannot be read. */
 int fbfft_b200_device_status(void);
 
 /* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
