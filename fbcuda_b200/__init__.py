@@ -19,6 +19,7 @@ from .api import (  # noqa: F401
     fft2d_r2c,
     last_error,
     device_status,
+    set_contraction_mode,
     lib,
     transposeMM,
     conv_workspace_bytes,

@@ -89,6 +89,11 @@ def device_status() -> int:
     return int(lib().fbfft_b200_device_status())
 
 
+def set_contraction_mode(mode: int) -> None:
+    """0: tensor cores (3xTF32) when the operands qualify; 1: FP32 CUDA cores only."""
+    _check(lib().fbfft_b200_set_contraction_mode(int(mode)))
+
+
 def last_error() -> str:
     return lib().fbfft_b200_last_error().decode()
 

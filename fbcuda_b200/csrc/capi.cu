@@ -100,8 +100,14 @@ int fbfft_b200_version(void) { return 100; }
 const char* fbfft_b200_last_error(void) { return g_last_error; }
 
 int fbfft_b200_device_status(void) {
-  const int a = read_device_error(), b = read_device_error_coop();
-  return a != 0 ? a : b;
+  const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc();
+  return a != 0 ? a : (b != 0 ? b : c);
+}
+
+int fbfft_b200_set_contraction_mode(int mode) {
+  if (mode != 0 && mode != 1) return fail(kUnsupportedDimension, "set_contraction_mode: 0 (tensor cores) or 1 (FP32 cores)");
+  set_contraction_mode(mode);
+  return kSuccess;
 }
 
 int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const int* real_stride, float* cplx,

@@ -145,6 +145,23 @@ int cgemm_bins(bool conjA, bool conjB, bool accumulate, const float* a, long lon
                long long bs0, long long bs1, float* c, long long cs0, long long cs1, int I, int J, int K, int X,
                float inv_norm, cudaStream_t s) {
   if (I == 0 || J == 0 || X == 0) return kSuccess;
+  if (conjA && conjB) {
+    set_last_error("transpose_mm: both operands conjugate-transposed is not a convolution pass");
+    return kUnsupportedDimension;
+  }
+  if (K > 0) {
+    // tensor-core path: the larger of I and J becomes the 128-row MMA dimension
+    // (complex multiplication commutes, so C = op(A) op(B) = (op(B)^T op(A)^T)^T)
+    const long long a_rs = conjA ? as1 : as0, a_ks = conjA ? as0 : as1;   // op(A)[i][k]
+    const long long b_rs = conjB ? bs0 : bs1, b_ks = conjB ? bs1 : bs0;   // op(B)[k][j] seen as rows j
+    if (J >= I) {
+      if (cgemm_tc_supported(b, b_rs, b_ks, a, a_rs, a_ks, c, cs1, cs0, J, I, K, X))
+        return cgemm_tc(b, b_rs, b_ks, conjB, a, a_rs, a_ks, conjA, c, cs1, cs0, J, I, K, X, inv_norm, accumulate, s);
+    } else {
+      if (cgemm_tc_supported(a, a_rs, a_ks, b, b_rs, b_ks, c, cs0, cs1, I, J, K, X))
+        return cgemm_tc(a, a_rs, a_ks, conjA, b, b_rs, b_ks, conjB, c, cs0, cs1, I, J, K, X, inv_norm, accumulate, s);
+    }
+  }
   const float2* A = reinterpret_cast<const float2*>(a);
   const float2* B = reinterpret_cast<const float2*>(b);
   float2* C = reinterpret_cast<float2*>(c);

@@ -48,6 +48,17 @@ int cgemm_bins(bool conjA, bool conjB, bool accumulate, const float* a, long lon
                long long bs0, long long bs1, float* c, long long cs0, long long cs1, int I, int J, int K, int X,
                float inv_norm, cudaStream_t s);
 
+// tensor-core (tcgen05, 3xTF32) version of the contraction (cgemm_tc.cu):
+// D[m][n][x] (+)= inv_norm * sum_k opA(A[m][k][x]) opB(B[n][k][x]), strides in complex elements
+bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const float* b, long long b_rs, long long b_ks,
+                        const float* d, long long d_ms, long long d_ns, int M, int N, int K, int X);
+int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
+             bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
+             bool accumulate, cudaStream_t s);
+void set_contraction_mode(int mode);  // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only
+int contraction_mode();
+int read_device_error_tc();
+
 // tiled convolution passes (conv_iterated.cu)
 int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs, float* weight,
                          const int* weight_size, const int* weight_stride, int pass, float scale, int batch_size,

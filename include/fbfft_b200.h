@@ -49,8 +49,16 @@ const char* fbfft_b200_last_error(void);
 /* Synchronising health check (no counterpart in the reference): returns 0 when no
  * kernel of this library has recorded a device-side error on the current device,
  * else the code it recorded (a bounded wait on an asynchronous copy that ran out:
- * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128), or -1 if the status cannot be read. */
+ * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128, 201 / 202 tensor-core contraction), or -1 if the status cannot be read. */
 int fbfft_b200_device_status(void);
+
+/* How fbfft_b200_transpose_mm and the convolution passes contract (process-wide; no
+ * counterpart in the reference, whose transposeMM is FP32 CUDA-core code only):
+ * 0 (default) tensor cores -- tcgen05 MMAs on a 3xTF32 split of the fp32 operands,
+ * accumulating in fp32 -- whenever the operands qualify (bin count a multiple of 4,
+ * 16-byte aligned bases, even strides), FP32 CUDA cores otherwise; 1 FP32 CUDA cores
+ * always. */
+int fbfft_b200_set_contraction_mode(int mode);
 
 /* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
  * -- fbfft/FBFFT.cuh:11-16, fbfft/FBFFT-inl.cuh:19-87.

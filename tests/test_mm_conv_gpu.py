@@ -197,3 +197,47 @@ def test_iterated_convolution_rejects_unknown():
     t = _tiles([(x, 0, 0)])
     assert fb.FFTIteratedConvolution(64, t, t, torch.zeros((1, 1, 3, 3), device="cuda"), 0, 1.0, 1) is False
     assert fb.FFTIteratedConvolution(8, t, t, torch.zeros((1, 1, 3, 3), device="cuda"), 3, 1.0, 1) is False
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("conj_a,conj_b", [(False, True), (True, False), (False, False)])
+@pytest.mark.parametrize("ikj", [(64, 128, 128), (8, 96, 96), (130, 20, 70), (96, 5, 40)])
+def test_transpose_mm_both_contraction_modes(mode, conj_a, conj_b, ikj):
+    """Tensor-core (3xTF32, mode 0) and FP32 CUDA-core (mode 1) contractions against float64,
+    on shapes that need row, column and k padding of the MMA tiles."""
+    i, k, j = ikj
+    rows, cols = 3, 8
+    rng = np.random.default_rng(i + 7 * k + 13 * j)
+    a_shape = (k, i) if conj_a else (i, k)
+    b_shape = (j, k) if conj_b else (k, j)
+    a = rng.normal(size=a_shape + (rows, cols, 2)).astype(np.float32)
+    b = rng.normal(size=b_shape + (rows, cols, 2)).astype(np.float32)
+    want = orc.transpose_mm(a, b, None, conj_a, conj_b, False, 0.5)
+    fb.set_contraction_mode(mode)
+    try:
+        c = torch.full(want.shape, 3.0, device="cuda")
+        fb.transposeMM(dev(a), dev(b), c, 0.5, conj_a, conj_b, False)
+        err = orc.rel_l2(host(c), want)
+        fb.transposeMM(dev(a), dev(b), c, 0.5, conj_a, conj_b, True)
+        err2 = orc.rel_l2(host(c), 2 * want)
+    finally:
+        fb.set_contraction_mode(0)
+    assert err < 5e-6 and err2 < 5e-6, (err, err2)
+    assert fb.device_status() == 0
+
+
+def test_conv_passes_fp32_mode_matches():
+    """The convolution passes give the same answer with the FP32 CUDA-core contraction."""
+    n, b, c, o, hw, k, pad = 32, 4, 6, 5, 27, 5, 0
+    rng = np.random.default_rng(12)
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    go = rng.normal(size=(b, o, hw - k + 1, hw - k + 1)).astype(np.float32)
+    fb.set_contraction_mode(1)
+    try:
+        out, gi, gw = run_passes(n, x, w, go, pad)
+    finally:
+        fb.set_contraction_mode(0)
+    assert orc.rel_l2(out, orc.conv_update_output(x, w, pad)) < CONV_TOL
+    assert orc.rel_l2(gi, orc.conv_update_grad_input(go, w, hw, hw, pad)) < CONV_TOL
+    assert orc.rel_l2(gw, orc.conv_acc_grad_parameters(x, go, k, k, pad, 0.5)) < CONV_TOL
