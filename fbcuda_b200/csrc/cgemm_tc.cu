@@ -33,7 +33,8 @@ namespace fbfft_b200 {
 
 namespace {
 
-constexpr int kTcThreads = 256;
+constexpr int kProducers = 256;           // gather / split / epilogue threads (8 warps)
+constexpr int kTcThreads = kProducers + 32;  // plus one warp that only issues MMAs
 constexpr int BM = 128;   // rows of m per block
 constexpr int XB = 4;     // bins per block
 constexpr int KS = 8;     // k per stage (one tf32 MMA)
@@ -112,15 +113,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   constexpr int TMEM_COLS = 512;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* stage_mem = smem_raw;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 2 * STAGE);  // [0],[1] stage free, [2] done
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 3);
+  // [0],[1] stage filled (256 producer arrivals), [2],[3] stage free (MMA commit), [4] all MMAs done
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 2 * STAGE);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 5);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int x0 = blockIdx.x * XB, m0 = blockIdx.y * BM, n0 = blockIdx.z * BN;
 
   if (tid == 0) {
-    mbar_init(smem_u32(bars + 0), 1);
-    mbar_init(smem_u32(bars + 1), 1);
+    mbar_init(smem_u32(bars + 0), kProducers);
+    mbar_init(smem_u32(bars + 1), kProducers);
     mbar_init(smem_u32(bars + 2), 1);
+    mbar_init(smem_u32(bars + 3), 1);
+    mbar_init(smem_u32(bars + 4), 1);
     fence_async_smem();
   }
   if (warp == 0) {
@@ -134,7 +138,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   const unsigned tmem_base = *tmem_slot;
 
   // ---- gather roles: every thread owns one (row, k-quad) unit of A; threads < 2*BN also one of B
-  const int a_row = tid % BM, a_kq = tid / BM;           // kq in {0, 1}
+  const int a_row = tid % BM, a_kq = (tid / BM) & 1;     // kq in {0, 1}
   const bool has_b = tid < 2 * BN;
   const int b_row = tid % BN, b_kq = tid / BN;
   const bool a_row_ok = m0 + a_row < g.M, b_row_ok = has_b && (n0 + b_row < g.N);
@@ -193,89 +197,107 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
 
   const int nsteps = (g.K + KS - 1) / KS;
   bool ok = true;
-  unsigned free_phase[2] = {0, 0};
-  gather(0);
-  for (int s = 0; s < nsteps; ++s) {
-    const int buf = s & 1;
-    unsigned char* st = stage_mem + buf * STAGE;
-    if (s >= 2 && ok) {
-      // the MMAs that read this stage two steps ago must have finished
-      if (!mbar_wait(smem_u32(bars + buf), free_phase[buf], kErrTcStageWait)) ok = false;
-      free_phase[buf] ^= 1;
-    }
-    scatter(st);
-    if (s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while this step's MMAs run
-    fence_async_smem();                        // generic-proxy writes -> visible to the tensor core
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (tid == 0) {
-      const unsigned sa = smem_u32(st), sb = sa + A_STAGE;
+  if (warp == kProducers / 32) {
+    // ---- MMA warp: one lane issues; it never touches operands, only descriptors
+    if (lane == 0) {
+      const unsigned long long a_desc0 = smem_desc(smem_u32(stage_mem), A_LBO, SBO);
+      const unsigned long long b_desc0 = smem_desc(smem_u32(stage_mem) + A_STAGE, B_LBO, SBO);
+      const unsigned idesc_pos = instr_desc(BN, false, false), idesc_neg = instr_desc(BN, true, false);
+      // (A part, B part, target): Re D = Ar*Br -/+ Ai*Bi, Im D = +/- Ar*Bi +/- Ai*Br;
+      // conj(A) flips the sign of Ai, conj(B) of Bi
+      const unsigned id1 = !(g.conjA ^ g.conjB) ? idesc_neg : idesc_pos;  // Ai*Bi
+      const unsigned id2 = g.conjB ? idesc_neg : idesc_pos;               // Ar*Bi
+      const unsigned id3 = g.conjA ? idesc_neg : idesc_pos;               // Ai*Br
+      unsigned full_phase[2] = {0, 0};
+      for (int s = 0; s < nsteps && ok; ++s) {
+        const int buf = s & 1;
+        if (!mbar_wait(smem_u32(bars + buf), full_phase[buf], kErrTcStageWait)) {
+          ok = false;
+          break;
+        }
+        full_phase[buf] ^= 1;
+        tc_fence_after();
+        const unsigned long long da0 = a_desc0 + (unsigned long long)((buf * STAGE) >> 4);
+        const unsigned long long db0 = b_desc0 + (unsigned long long)((buf * STAGE) >> 4);
 #pragma unroll
-      for (int bin = 0; bin < XB; ++bin) {
-        const unsigned d_re = tmem_base + bin * (2 * BN), d_im = d_re + BN;
-        // (A part, B part, target, negate): Re D = Ar*Br - s*Ai*Bi, Im D = sB*Ar*Bi + sA*Ai*Br
-        // with conj(A): Ai -> -Ai, conj(B): Bi -> -Bi
+        for (int bin = 0; bin < XB; ++bin) {
+          const unsigned d_re = tmem_base + bin * (2 * BN), d_im = d_re + BN;
 #pragma unroll
-        for (int term = 0; term < 4; ++term) {
-          const int pa = (term == 1 || term == 3) ? 1 : 0;   // 0 = re, 1 = im
-          const int pb = (term == 1 || term == 2) ? 1 : 0;
-          const unsigned d = (term < 2) ? d_re : d_im;
-          bool neg = false;
-          if (term == 1) neg = !(g.conjA ^ g.conjB);   // Ai*Bi: minus unless exactly one is conjugated
-          if (term == 2) neg = g.conjB;                // Ar*Bi
-          if (term == 3) neg = g.conjA;                // Ai*Br
-          const unsigned idesc = instr_desc(BN, neg, false);
+          for (int term = 0; term < 4; ++term) {
+            const int pa = (term == 1 || term == 3) ? 1 : 0;   // 0 = re, 1 = im
+            const int pb = (term == 1 || term == 2) ? 1 : 0;
+            const unsigned d = (term < 2) ? d_re : d_im;
+            const unsigned idesc = term == 0 ? idesc_pos : (term == 1 ? id1 : (term == 2 ? id2 : id3));
 #pragma unroll
-          for (int sp = 0; sp < 3; ++sp) {
-            const int sa_split = (sp == 2) ? 1 : 0, sb_split = (sp == 1) ? 1 : 0;  // hi*hi, hi*lo, lo*hi
-            const unsigned long long da = smem_desc(sa + ((bin * 2 + pa) * 2 + sa_split) * A_TILE, A_LBO, SBO);
-            const unsigned long long db = smem_desc(sb + ((bin * 2 + pb) * 2 + sb_split) * B_TILE, B_LBO, SBO);
-            const unsigned acc = (s > 0 || (term & 1) || sp > 0) ? 1u : 0u;  // first product into each accumulator overwrites
-            mma_tf32(d, da, db, idesc, acc);
+            for (int sp = 0; sp < 3; ++sp) {
+              const int sa_split = (sp == 2) ? 1 : 0, sb_split = (sp == 1) ? 1 : 0;  // hi*hi, hi*lo, lo*hi
+              const unsigned long long da = da0 + (unsigned long long)((((bin * 2 + pa) * 2 + sa_split) * A_TILE) >> 4);
+              const unsigned long long db = db0 + (unsigned long long)((((bin * 2 + pb) * 2 + sb_split) * B_TILE) >> 4);
+              // the first product into each accumulator overwrites it
+              const unsigned acc = (s > 0 || (term & 1) || sp > 0) ? 1u : 0u;
+              mma_tf32(d, da, db, idesc, acc);
+            }
           }
         }
+        mma_commit(smem_u32(bars + 2 + buf));                 // frees the stage when these MMAs retire
+        if (s == nsteps - 1) mma_commit(smem_u32(bars + 4));  // and, after the last step, releases the epilogue
       }
-      mma_commit(smem_u32(bars + buf));
-      if (s == nsteps - 1) mma_commit(smem_u32(bars + 2));
     }
-  }
-  // ---- epilogue: all MMAs done -> tensor memory -> global
-  if (ok && !mbar_wait(smem_u32(bars + 2), 0, kErrTcFinalWait)) ok = false;
-  tc_fence_after();
-  if (ok) {
-    const int lq = warp & 3, ch = warp >> 2;            // lane quarter of tensor memory, column half
-    const int m = m0 + lq * 32 + lane;
-    constexpr int CHUNKS = BN / 16;                     // 8-column chunks per column half
-#pragma unroll 1
-    for (int cc = 0; cc < CHUNKS; ++cc) {
-      const int col = ch * (BN / 2) + cc * 8;
-      float v[XB][2][8];
-#pragma unroll
-      for (int bin = 0; bin < XB; ++bin) {
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (2 * BN) + part * BN + col, v[bin][part]);
-        }
+    __syncwarp();
+  } else {
+    // ---- producers
+    unsigned free_phase[2] = {0, 0};
+    gather(0);
+    for (int s = 0; s < nsteps; ++s) {
+      const int buf = s & 1;
+      unsigned char* st = stage_mem + buf * STAGE;
+      if (s >= 2 && ok) {
+        // the MMAs that read this stage two steps ago must have retired
+        if (!mbar_wait(smem_u32(bars + 2 + buf), free_phase[buf], kErrTcStageWait)) ok = false;
+        free_phase[buf] ^= 1;
       }
-      tmem_ld_wait();
-      if (m < g.M) {
+      scatter(st);
+      if (s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while this step's MMAs run
+      fence_async_smem();                        // generic-proxy writes -> visible to the tensor core
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bars + buf)) : "memory");
+    }
+    // ---- epilogue: all MMAs done -> tensor memory -> global
+    if (ok && !mbar_wait(smem_u32(bars + 4), 0, kErrTcFinalWait)) ok = false;
+    tc_fence_after();
+    if (ok) {
+      const int lq = warp & 3, ch = warp >> 2;            // lane quarter of tensor memory, column half
+      const int m = m0 + lq * 32 + lane;
+      constexpr int CHUNKS = BN / 16;                     // 8-column chunks per column half
+#pragma unroll 1
+      for (int cc = 0; cc < CHUNKS; ++cc) {
+        const int col = ch * (BN / 2) + cc * 8;
+        float v[XB][2][8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int n = n0 + col + j;
-          if (n < g.N) {
-            float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns + x0);
-            float4 o0 = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
-                                    v[1][1][j] * g.inv_norm);
-            float4 o1 = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
-                                    v[3][1][j] * g.inv_norm);
-            if (g.accumulate) {
-              const float4 p0 = dst[0], p1 = dst[1];
-              o0.x += p0.x, o0.y += p0.y, o0.z += p0.z, o0.w += p0.w;
-              o1.x += p1.x, o1.y += p1.y, o1.z += p1.z, o1.w += p1.w;
+        for (int bin = 0; bin < XB; ++bin) {
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (2 * BN) + part * BN + col, v[bin][part]);
+          }
+        }
+        tmem_ld_wait();
+        if (m < g.M) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int n = n0 + col + j;
+            if (n < g.N) {
+              float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns + x0);
+              float4 o0 = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
+                                      v[1][1][j] * g.inv_norm);
+              float4 o1 = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
+                                      v[3][1][j] * g.inv_norm);
+              if (g.accumulate) {
+                const float4 p0 = dst[0], p1 = dst[1];
+                o0.x += p0.x, o0.y += p0.y, o0.z += p0.z, o0.w += p0.w;
+                o1.x += p1.x, o1.y += p1.y, o1.z += p1.z, o1.w += p1.w;
+              }
+              dst[0] = o0;
+              dst[1] = o1;
             }
-            dst[0] = o0;
-            dst[1] = o1;
           }
         }
       }
