@@ -45,10 +45,10 @@ struct CoopCfg<128> {
 // select q; Q = 1 is a plain in-register FFT).  In: a[m*P + jl] = x[jl + P*q + R*m],
 // P = R/Q.  Out: a[brev(k, R)] = X[Q*k + q].  lf[qq] = exp(-+2*pi*i*q*qq/(Q*Q)) is
 // the part of the twiddle that depends on the lane.
-template <int N, int R, int Q, bool INV>
+template <int N, int R, int Q, bool INV, bool PK = INV>
 __device__ __forceinline__ void coop_fft(float2 (&a)[R], int q, const float2 (&lf)[Q]) {
   if constexpr (Q == 1) {
-    fft_bitrev<R, INV>(a);
+    fft_bitrev<R, INV, PK>(a);
   } else {
     constexpr int P = R / Q;
     constexpr int LP = 32 / Q;  // lanes per q group
@@ -56,7 +56,7 @@ __device__ __forceinline__ void coop_fft(float2 (&a)[R], int q, const float2 (&l
     // radix-Q step over m for every jl: output qq lands at a[brev(qq, Q)*P + jl]
     static_for<P>([&](auto jc) {
       constexpr int jl = decltype(jc)::value;
-      Dif<Q, jl, P, INV, R>::run(a);
+      Dif<Q, jl, P, INV, R, PK>::run(a);
     });
     float2 c[R];
     static_for<Q>([&](auto qc) {
@@ -88,7 +88,7 @@ __device__ __forceinline__ void coop_fft(float2 (&a)[R], int q, const float2 (&l
         });
       });
     });
-    fft_bitrev<R, INV>(c);
+    fft_bitrev<R, INV, PK>(c);
 #pragma unroll
     for (int i = 0; i < R; ++i) a[i] = c[i];
   }
@@ -125,7 +125,8 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
   extern __shared__ __align__(16) float2 smem[];
   float2* mid = smem;   // [N][PM]        pass A -> pass B
   float2* tile = smem;  // [H+1][PO] + packed row [N]   pass B -> bulk stores (aliases mid)
-  float2* vs = smem + (H + 1) * PO;
+  float2* vsd = smem + (H + 1) * PO;  // packed row, direct half  [H+1]
+  float2* vsm = vsd + (H + 1);        // packed row, mirrored half [H+1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = lane / LP, item = warp * LP + (lane % LP);  // item: column pair p (pass A), row r (pass B)
   float2 lf[Q];
@@ -155,6 +156,15 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       // the previous image's rows may still be leaving the tile that mid aliases
       bulk_wait_read();
       block_sync<T>();
+      if (q == 0) {
+        // Rows ky = 0 and ky = H of a column pair hold four real numbers (sums and
+        // alternating sums of two real columns).  Pass B wants them packed as one complex
+        // row; store u' = u + i v, v' = u - i v (componentwise as below) so that its general
+        // "separate two real spectra" formula yields exactly that packing for row 0.
+        const float2 u = a[brev(0, R)], v = a[brev(R / 2, R)];
+        a[brev(0, R)] = make_float2(u.x - v.y, u.y + v.x);
+        a[brev(R / 2, R)] = make_float2(u.x + v.y, u.y - v.x);
+      }
       static_for<R>([&](auto kc) {
         constexpr int k = decltype(kc)::value;
         mid[(Q * k + q) * PM + item] = a[brev(k, R)];
@@ -168,13 +178,8 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       const float2* row1 = mid + r * PM;
       const float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
       auto take = [&](float4 u, float4 v, float2& a0, float2& a1, float2& b0, float2& b1) {
-        if (r == 0) {
-          a0 = make_float2(u.x, v.x), b0 = make_float2(u.y, v.y);
-          a1 = make_float2(u.z, v.z), b1 = make_float2(u.w, v.w);
-        } else {
-          a0 = make_float2(0.5f * (u.x + v.x), 0.5f * (u.y - v.y)), b0 = make_float2(0.5f * (u.y + v.y), 0.5f * (v.x - u.x));
-          a1 = make_float2(0.5f * (u.z + v.z), 0.5f * (u.w - v.w)), b1 = make_float2(0.5f * (u.w + v.w), 0.5f * (v.z - u.z));
-        }
+        a0 = make_float2(0.5f * (u.x + v.x), 0.5f * (u.y - v.y)), b0 = make_float2(0.5f * (u.y + v.y), 0.5f * (v.x - u.x));
+        a1 = make_float2(0.5f * (u.z + v.z), 0.5f * (u.w - v.w)), b1 = make_float2(0.5f * (u.w + v.w), 0.5f * (v.z - u.z));
       };
       if constexpr (Q == 1) {
 #pragma unroll
@@ -193,35 +198,32 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           }
         }
       }
-      coop_fft<N, R, Q, false>(a, q, lf);
+      coop_fft<N, R, Q, false, true>(a, q, lf);
       block_sync<T>();  // every lane has read its part of mid: the tile may overwrite it
-      if (r == 0) {
-        static_for<R>([&](auto kc) {
-          constexpr int k = decltype(kc)::value;
-          vs[Q * k + q] = a[brev(k, R)];
-        });
-      } else {
-        float2* direct = tile + r;                 // tile[kx][ky = r]
-        float2* mirror = tile + (N - r);           // tile[(N-kx)%N][N - r], conjugated
-        static_for<R>([&](auto kc) {
-          constexpr int k = decltype(kc)::value;
-          const int kx = Q * k + q;
-          const float2 v = a[brev(k, R)];
-          if (Q * k + Q - 1 <= H || kx <= H) {
-            if (kx <= H) direct[kx * PO] = v;
-          }
-          if (Q * k >= H - (Q - 1) || k == 0) {
-            if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
-          }
-        });
-      }
+      // Row r > 0 scatters F[r][kx] to tile[kx][r] (kx <= H) and its Hermitian mirror
+      // conj(F[r][kx]) to tile[(N-kx)%N][N-r] (kx >= H or kx == 0).  The packed row 0 does
+      // the same into the two halves of the scratch row: vsd[kx] = V[kx], vsm[j] = conj(V[(N-j)%N]).
+      float2* direct = (r == 0) ? vsd : tile + r;
+      float2* mirror = (r == 0) ? vsm : tile + (N - r);
+      const int stride = (r == 0) ? 1 : PO;
+      static_for<R>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        const int kx = Q * k + q;
+        const float2 v = a[brev(k, R)];
+        if (Q * k + Q - 1 <= H || kx <= H) {
+          if (kx <= H) direct[kx * stride] = v;
+        }
+        if (Q * k >= H - (Q - 1) || k == 0) {
+          if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * stride] = make_float2(v.x, -v.y);
+        }
+      });
     }
     block_sync<T>();
     // rows ky = 0 and N/2 from the packed row: V = F[0] + i F[N/2]
     for (int kx = threadIdx.x; kx <= H; kx += T) {
-      const float2 v = vs[kx], m = vs[(N - kx) & (N - 1)];
-      tile[kx * PO] = make_float2(0.5f * (v.x + m.x), 0.5f * (v.y - m.y));
-      tile[kx * PO + H] = make_float2(0.5f * (v.y + m.y), 0.5f * (m.x - v.x));
+      const float2 v = vsd[kx], cm = vsm[kx];  // V[kx], conj(V[(N-kx)%N])
+      tile[kx * PO] = make_float2(0.5f * (v.x + cm.x), 0.5f * (v.y + cm.y));
+      tile[kx * PO + H] = make_float2(0.5f * (v.y - cm.y), 0.5f * (cm.x - v.x));
     }
     fence_async_smem();
     block_sync<T>();
@@ -268,29 +270,30 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     float2 a[R];
     if (!mbar_wait(bar, phase, kErrCoopInvWait)) return;
     phase ^= 1;
+    // Row 0 of pass B^-1 is the packed pair of rows ky = 0 and ky = H: P[kx] = F[0][kx] + i F[H][kx].
+    // Rewrite columns 0 and H of the tile in place, tile[kx][0] = p + i h, tile[kx][H] = p - i h,
+    // so that the general Hermitian fetch below (direct from column c1, mirrored and conjugated from
+    // column c2) produces P for row 0 when it is pointed at columns (0, H).  The imaginary parts of
+    // F[0][0] and F[H][0] carry nothing (both rows are transforms of real sequences) and are dropped.
+    for (int kx = threadIdx.x; kx <= H; kx += T) {
+      float2 p = tile[kx * PO], h = tile[kx * PO + H];
+      if (kx == 0) p.y = 0.f, h.y = 0.f;
+      tile[kx * PO] = make_float2(p.x - h.y, p.y + h.x);
+      tile[kx * PO + H] = make_float2(p.x + h.y, p.y - h.x);
+    }
+    block_sync<T>();
     {
-      // ---- pass B^-1: row item along kx = jl + P*q + R*m; row 0 packs ky = 0 and N/2.
+      // ---- pass B^-1: row item along kx = jl + P*q + R*m.
       // F[ky][kx] = tile[kx][ky] for kx <= H, else conj(tile[N-kx][(N-ky)%N]).
       const int r = item;
-      const float2* c1 = tile + r;                       // tile[kx][r]
-      const float2* c2 = tile + ((N - r) & (N - 1));     // tile[N-kx][(N-r)%N]
+      const float2* c1 = tile + r;                                  // tile[kx][r]
+      const float2* c2 = tile + ((r == 0) ? H : N - r);             // tile[N-kx][(N-r)%N]
 #pragma unroll
       for (int m = 0; m < Q; ++m) {
 #pragma unroll
         for (int jl = 0; jl < P; ++jl) {
           const int kx = jl + P * q + R * m;
-          if (r == 0) {
-            // the imaginary parts of F[0][0] and F[N/2][0] carry nothing (both rows are
-            // transforms of real sequences) and are dropped
-            float2 f0, fh;
-            if (kx <= H) {
-              f0 = tile[kx * PO], fh = tile[kx * PO + H];
-            } else {
-              f0 = tile[(N - kx) * PO], fh = tile[(N - kx) * PO + H];
-              f0.y = -f0.y, fh.y = -fh.y;
-            }
-            a[m * P + jl] = (kx == 0) ? make_float2(f0.x, fh.x) : make_float2(f0.x - fh.y, f0.y + fh.x);
-          } else if (kx <= H) {
+          if (kx <= H) {
             a[m * P + jl] = c1[kx * PO];
           } else {
             const float2 t = c2[(N - kx) * PO];
@@ -305,18 +308,17 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       // lane holds G[ky][x] at x = Q*k + q; columns x and x+H share a complex line:
       // Z_p[ky] = G_p[ky] + i G_{p+H}[ky], Z_p[N-ky] = conj(G_p[ky]) + i conj(G_{p+H}[ky]).
       // x + H = Q*(k + R/2) + q sits in the same lane.
+      // Row 0 holds the packed pair (G[0], G[H]) = (re, im); it stores the same two combinations
+      // into rows 0 and H, and pass A^-1 undoes them after loading.
       const int r = item;
+      float2* row1 = mid + r * PM;
+      float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
       static_for<R / 2>([&](auto kc) {
         constexpr int k = decltype(kc)::value;
         const int p = Q * k + q;
         const float2 g0 = a[brev(k, R)], g1 = a[brev(k + R / 2, R)];
-        if (r == 0) {
-          mid[p] = make_float2(g0.x, g1.x);
-          mid[H * PM + p] = make_float2(g0.y, g1.y);
-        } else {
-          mid[r * PM + p] = make_float2(g0.x - g1.y, g0.y + g1.x);
-          mid[(N - r) * PM + p] = make_float2(g0.x + g1.y, g1.x - g0.y);
-        }
+        row1[p] = make_float2(g0.x - g1.y, g0.y + g1.x);
+        row2[p] = make_float2(g0.x + g1.y, g1.x - g0.y);
       });
     }
     block_sync<T>();
@@ -326,6 +328,13 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       for (int m = 0; m < Q; ++m) {
 #pragma unroll
         for (int jl = 0; jl < P; ++jl) a[m * P + jl] = mid[(jl + P * q + R * m) * PM + item];
+      }
+      if (q == 0) {
+        // ky = 0 sits at a[0] and ky = H at a[R/2] of the q = 0 lanes: A = (g0.x - g1.y, g0.y + g1.x),
+        // B = (g0.x + g1.y, g1.x - g0.y) -> Z[0] = (g0.x, g1.x), Z[H] = (g0.y, g1.y)
+        const float2 A = a[0], Bv = a[R / 2];
+        a[0] = make_float2(0.5f * (A.x + Bv.x), 0.5f * (A.y + Bv.y));
+        a[R / 2] = make_float2(0.5f * (A.y - Bv.y), 0.5f * (Bv.x - A.x));
       }
       block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
       if (b + gridDim.x < B) fetch(b + gridDim.x);
@@ -349,7 +358,7 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 
 template <int N>
 constexpr int fwd_smem() {
-  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO + N;
+  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO + N + 2;
   return (mid > tile ? mid : tile) * (int)sizeof(float2);
 }
 template <int N>

@@ -125,7 +125,7 @@ __device__ __forceinline__ void inv_pack_rows(float2* ib, int l) {
   {
     float2 v[N];
     load_row16<N>(ib + l * RS, v);
-    fft_bitrev<N, true>(v);
+    fft_bitrev<N, true, true>(v);
     static_for<N / 2>([&](auto cc) {
       constexpr int c = decltype(cc)::value * 2;
       const float2 p = v[brev(c, N)], q = v[brev(c + 1, N)];
@@ -152,7 +152,7 @@ __device__ __forceinline__ void inv_columns(const float2* ib, int l, float2 (&z)
     z[r] = make_float2(g0.x - g1.y, g0.y + g1.x);
     z[N - r] = make_float2(g0.x + g1.y, g1.x - g0.y);
   });
-  fft_bitrev<N, true>(z);
+  fft_bitrev<N, true, true>(z);
 }
 
 // Cropped store of the two columns held in z (see inv_columns), scaled by `mul`.

@@ -74,6 +74,20 @@ struct Tw {
 
 __device__ __forceinline__ float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
 __device__ __forceinline__ float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+// Complex add / subtract as ONE packed fp32x2 instruction each (Blackwell's FADD2 / FFMA2).
+// The butterflies are issue-bound and two thirds of their instructions are these; whether
+// the packed form wins depends on how the kernel's operands reach register pairs, so each
+// kernel chooses (template parameter PK of the transforms below).
+template <bool PK>
+__device__ __forceinline__ float2 cadd_t(float2 a, float2 b) {
+  if constexpr (PK) return __fadd2_rn(a, b);
+  return make_float2(a.x + b.x, a.y + b.y);
+}
+template <bool PK>
+__device__ __forceinline__ float2 csub_t(float2 a, float2 b) {
+  if constexpr (PK) return __ffma2_rn(b, make_float2(-1.f, -1.f), a);
+  return make_float2(a.x - b.x, a.y - b.y);
+}
 __device__ __forceinline__ float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -115,26 +129,26 @@ __host__ __device__ constexpr int brev(int v, int n) {  // reverse the log2(n) l
 
 // Radix-2 decimation in frequency on a[OFF + j*ST], j in [0, N): afterwards
 // output k sits at a[OFF + brev(k, N)*ST].
-template <int N, int OFF, int ST, bool INV, int TOTAL>
+template <int N, int OFF, int ST, bool INV, int TOTAL, bool PK = false>
 struct Dif {
   static __device__ __forceinline__ void run(float2 (&a)[TOTAL]) {
     if constexpr (N >= 2) {
       static_for<N / 2>([&](auto jc) {
         constexpr int j = decltype(jc)::value;
         float2 u = a[OFF + j * ST], v = a[OFF + (j + N / 2) * ST];
-        a[OFF + j * ST] = cadd(u, v);
-        a[OFF + (j + N / 2) * ST] = mul_tw<j, N, INV>(csub(u, v));
+        a[OFF + j * ST] = cadd_t<PK>(u, v);
+        a[OFF + (j + N / 2) * ST] = mul_tw<j, N, INV>(csub_t<PK>(u, v));
       });
-      Dif<N / 2, OFF, ST, INV, TOTAL>::run(a);
-      Dif<N / 2, OFF + (N / 2) * ST, ST, INV, TOTAL>::run(a);
+      Dif<N / 2, OFF, ST, INV, TOTAL, PK>::run(a);
+      Dif<N / 2, OFF + (N / 2) * ST, ST, INV, TOTAL, PK>::run(a);
     }
   }
 };
 
-// In-place FFT of a[0..N); output k is left at a[brev(k, N)].
-template <int N, bool INV>
+// In-place FFT of a[0..N); output k is left at a[brev(k, N)].  PK: packed fp32x2 butterflies.
+template <int N, bool INV, bool PK = false>
 __device__ __forceinline__ void fft_bitrev(float2 (&a)[N]) {
-  Dif<N, 0, 1, INV, N>::run(a);
+  Dif<N, 0, 1, INV, N, PK>::run(a);
 }
 
 }  // namespace fbfft_b200
