@@ -27,7 +27,7 @@ namespace fbfft_b200 {
 
 namespace {
 
-enum : int { kErrCoopInvWait = 103 };
+enum : int { kErrCoopInvWait = 103, kErrCoopFwdWait = 104 };
 
 template <int N>
 struct CoopCfg;
@@ -115,7 +115,9 @@ __device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
 }
 
 // ------------------------------------------------------------------ forward
-template <int N>
+// IN_BULK: the real input is contiguous with a 16-byte aligned base; each image is staged in
+// shared memory by one cp.async.bulk (into the region the image's own mid/tile reuse afterwards).
+template <int N, bool IN_BULK>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
                                                                                 int padU) {
@@ -131,16 +133,53 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
   const int q = lane / LP, item = warp * LP + (lane % LP);  // item: column pair p (pass A), row r (pass B)
   float2 lf[Q];
   lane_factors<Q, false>(q, lf);
+  // staging (IN_BULK): raw image bytes at the start of the region, mbarrier behind the region
+  constexpr int REGION = (N * PM > (H + 1) * PO + N + 2) ? N * PM : (H + 1) * PO + N + 2;
+  const unsigned bar = smem_u32(smem + REGION);
+  const long long img_bytes = (long long)in.h * in.w * 4, total_bytes = img_bytes * B;
+  unsigned phase = 0;
+  // 16-byte aligned window around image b; false when it would reach past the tensor's end
+  auto window = [&](int b, long long* lo, unsigned* bytes) {
+    const long long g0 = (long long)b * img_bytes, g1 = g0 + img_bytes;
+    *lo = g0 & ~15LL;
+    const long long hi = (g1 + 15) & ~15LL;
+    *bytes = (unsigned)(hi - *lo);
+    return hi <= total_bytes || (total_bytes & 15) == 0;
+  };
+  bool staged = false;
+  auto fetch = [&](int b) {
+    long long lo;
+    unsigned bytes;
+    staged = window(b, &lo, &bytes);
+    if (staged && threadIdx.x == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(smem_u32(smem), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
+    }
+  };
+  if (IN_BULK) {
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    fence_async_smem();
+    block_sync<T>();
+    if (blockIdx.x < B) fetch(blockIdx.x);
+  }
 
   for (int b = blockIdx.x; b < B; b += gridDim.x) {
     float2 a[R];
     {
       // ---- pass A: columns item and item+H, rows y = jl + P*q + R*m
       const float* src = in.p + (long long)b * in.sb;
+      long long sy = in.sy, sx = in.sx;
+      if (IN_BULK && staged) {
+        if (!mbar_wait(bar, phase, kErrCoopFwdWait)) return;
+        phase ^= 1;
+        src = reinterpret_cast<const float*>(smem) + ((((long long)b * img_bytes) & 15) >> 2);
+        sy = in.w, sx = 1;
+      }
       const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
       const bool ok0 = x0 < (unsigned)in.w, ok1 = x1 < (unsigned)in.w;
-      const float* p0 = src + (long long)x0 * in.sx + (long long)(P * q - padU) * in.sy;
-      const float* p1 = src + (long long)x1 * in.sx + (long long)(P * q - padU) * in.sy;
+      const float* p0 = src + (long long)x0 * sx + (long long)(P * q - padU) * sy;
+      const float* p1 = src + (long long)x1 * sx + (long long)(P * q - padU) * sy;
       const int ybase = P * q - padU;
 #pragma unroll
       for (int m = 0; m < Q; ++m) {
@@ -148,14 +187,17 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
         for (int jl = 0; jl < P; ++jl) {
           const int yo = jl + R * m;
           const bool oky = (unsigned)(ybase + yo) < (unsigned)in.h;
-          a[m * P + jl].x = (oky && ok0) ? __ldg(p0 + (long long)yo * in.sy) : 0.f;
-          a[m * P + jl].y = (oky && ok1) ? __ldg(p1 + (long long)yo * in.sy) : 0.f;
+          a[m * P + jl].x = (oky && ok0) ? p0[(long long)yo * sy] : 0.f;
+          a[m * P + jl].y = (oky && ok1) ? p1[(long long)yo * sy] : 0.f;
         }
       }
+      if (IN_BULK) block_sync<T>();  // the staged image is in registers: mid may overwrite it
       coop_fft<N, R, Q, false>(a, q, lf);
-      // the previous image's rows may still be leaving the tile that mid aliases
-      bulk_wait_read();
-      block_sync<T>();
+      if (!IN_BULK) {
+        // the previous image's rows may still be leaving the tile that mid aliases
+        bulk_wait_read();
+        block_sync<T>();
+      }
       if (q == 0) {
         // Rows ky = 0 and ky = H of a column pair hold four real numbers (sums and
         // alternating sums of two real columns).  Pass B wants them packed as one complex
@@ -230,6 +272,13 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     float* dst = out + (long long)b * out_sb;
     for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
     bulk_commit();
+    if (IN_BULK) {
+      // the next image is staged into the region the rows are leaving from
+      bulk_wait_read();
+      block_sync<T>();
+      staged = false;
+      if (b + gridDim.x < B) fetch(b + gridDim.x);
+    }
   }
   bulk_wait_read();
 }
@@ -359,7 +408,7 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 template <int N>
 constexpr int fwd_smem() {
   constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO + N + 2;
-  return (mid > tile ? mid : tile) * (int)sizeof(float2);
+  return (mid > tile ? mid : tile) * (int)sizeof(float2) + 16;
 }
 template <int N>
 constexpr int inv_smem() {
@@ -373,12 +422,19 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
-  fft2d_coop_fwd_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+  const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
+                       in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
+  if (in_bulk) {
+    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+  } else {
+    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+  }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
@@ -388,7 +444,8 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
