@@ -37,7 +37,7 @@ if ROOT not in sys.path:
 GIB = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the
 # ncu capture summarised in profiles/ (captured on 65536 images, scaled by images per launch)
-NCU_TRAFFIC_BYTES_PER_IMAGE = {}
+NCU_TRAFFIC_BYTES_PER_IMAGE = {32: 7609.0, 64: 30170.0}
 
 
 def measured_peak_gbs():
@@ -299,7 +299,8 @@ def run_fft2d(args, world, rank, local):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {how}", "frac_of_8TBs": achieved / 8000.0,
                 "traffic": traffic * b if traffic else None, "algorithmic_bytes_per_launch": b * per_image,
-                "kernel": "fft2d_small_fwd_kernel" if n <= 32 else "fft2d_large_fwd_kernel"}
+                "kernel": "fft2d_small_fwd_kernel" if n <= 32 else ("fft2d_coop_fwd_kernel" if n <= 128 else "rows_fwd_kernel + lines_c2c_kernel"),
+                "traffic_source": "ncu capture on the profile case (profiles/), scaled by images per launch" if traffic else None}
     extra = {}
     if args.extras and rank == 0 and world == 1:
         extra = run_extras(args, x, spec, n)
