@@ -37,7 +37,7 @@ enum : int { kErrFwdWait = 101, kErrInvWait = 102 };
 // OUT_BULK: complex output is contiguous [B][N/2+1][N][2] with a 16-byte aligned base
 template <int N, bool IN_BULK, bool OUT_BULK>
 __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
-                                                                          int padU, int ntasks, int slot_floats) {
+                                                                          int padU, int ntasks, int slot_floats, int slot_pitch) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
   constexpr int RS = SmallCfg<N>::RS, IS = SmallCfg<N>::IS;
   extern __shared__ __align__(16) float2 smem[];
@@ -65,21 +65,40 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
     *bytes = (unsigned)(hi - *lo);
     return hi <= total_bytes || (total_bytes & 15) == 0;
   };
+  // When an image is a whole number of 16-byte units every image gets its own copy into a slot
+  // of pitch slot_pitch = h*w + N/2 floats, which puts the images of a warp N/2 banks apart (the
+  // column reads of pass A are then conflict free); otherwise one copy brings the task's window.
+  const bool per_image = slot_pitch != (int)img_floats;
+  auto issue = [&](int task) -> bool {
+    if (per_image) {
+      int imgs = B - task * IPW;
+      if (imgs > IPW) imgs = IPW;
+      if (lane == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bar, (unsigned)(imgs * img_floats * 4));
+      }
+      __syncwarp();
+      if (lane < imgs)
+        bulk_g2s(smem_u32(slot + lane * slot_pitch), in.p + (long long)(task * IPW + lane) * img_floats,
+                 (unsigned)(img_floats * 4), bar);
+      return true;
+    }
+    long long lo;
+    unsigned bytes;
+    const bool ok = window(task, &lo, &bytes);
+    if (ok && lane == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(smem_u32(slot), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
+    }
+    return ok;
+  };
   unsigned phase = 0;
   bool staged = false;  // the slot holds (or will hold) the current task
   if (IN_BULK) {
     if (lane == 0) mbar_init(bar, 1);
     __syncwarp();
-    if (first < ntasks) {
-      long long lo;
-      unsigned bytes;
-      staged = window(first, &lo, &bytes);
-      if (staged && lane == 0) {
-        fence_async_smem();
-        mbar_expect_tx(bar, bytes);
-        bulk_g2s(smem_u32(slot), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
-      }
-    }
+    if (first < ntasks) staged = issue(first);
   }
 
   for (int task = first; task < ntasks; task += stride) {
@@ -92,8 +111,8 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
         if (!mbar_wait(bar, phase, kErrFwdWait)) return;
         phase ^= 1;
         const long long g0 = (long long)task * IPW * img_floats * 4;
-        const int off0 = (int)((g0 & 15) >> 2);
-        load_columns<N>(slot + off0 + li * img_floats, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
+        const int off0 = per_image ? 0 : (int)((g0 & 15) >> 2);
+        load_columns<N>(slot + off0 + li * slot_pitch, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
       } else {
         load_columns<N>(in.p + (long long)(valid ? b : 0) * in.sb, in.sy, in.sx, in.h, in.w, padL, padU, valid, l, a);
       }
@@ -102,16 +121,7 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
         __syncwarp();
         const int next = task + stride;
         staged = false;
-        if (next < ntasks) {
-          long long lo;
-          unsigned bytes;
-          staged = window(next, &lo, &bytes);
-          if (staged && lane == 0) {
-            fence_async_smem();
-            mbar_expect_tx(bar, bytes);
-            bulk_g2s(smem_u32(slot), reinterpret_cast<const char*>(in.p) + lo, bytes, bar);
-          }
-        }
+        if (next < ntasks) staged = issue(next);
       }
       fft_bitrev<N, false>(a);
       if (OUT_BULK) {
@@ -272,7 +282,8 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const bool out_bulk = cplx_is_contiguous16(out, N);
   const int hw = in.h * in.w;
   // staging slot per warp: the raw images of one task plus alignment slack
-  const int slot_floats = ((IPW * hw + 8 + 3) / 4) * 4;
+  const int slot_pitch = (hw % 4 == 0) ? hw + N / 2 : hw;
+  const int slot_floats = ((IPW * slot_pitch + 8 + 3) / 4) * 4;
   const bool in_bulk = real_is_contiguous16(in, B) && in.h <= N && in.w <= N;
   const int base = work_floats<N>() * 4;
   if (in_bulk) {
@@ -280,17 +291,17 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
     const int grid = grid_for(ntasks, 3);
     if (out_bulk) {
       allow_smem(fft2d_small_fwd_kernel<N, true, true>, smem);
-      fft2d_small_fwd_kernel<N, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats);
+      fft2d_small_fwd_kernel<N, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
     } else {
       allow_smem(fft2d_small_fwd_kernel<N, true, false>, smem);
-      fft2d_small_fwd_kernel<N, true, false><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats);
+      fft2d_small_fwd_kernel<N, true, false><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
     }
   } else {
     const int grid = grid_for(ntasks, 4);
     if (out_bulk) {
-      fft2d_small_fwd_kernel<N, false, true><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0);
+      fft2d_small_fwd_kernel<N, false, true><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0, 0);
     } else {
-      fft2d_small_fwd_kernel<N, false, false><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0);
+      fft2d_small_fwd_kernel<N, false, false><<<grid, kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks, 0, 0);
     }
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
