@@ -356,9 +356,9 @@ def run_conv(args, world, rank, local):
     cfg = {"conv4": (64, 128, 128, 56, 3, 1, 64), "conv5": (32, 96, 96, 128, 13, 0, 128),
            "conv3": (128, 64, 128, 27, 5, 0, 32)}[args.conv_config]
     bg, c, o, hw, k, pad, n = cfg
-    if bg % world:
-        raise SystemExit(f"batch {bg} does not shard over {world} GPUs")
-    b = bg // world
+    from fbcuda_b200.dist import all_reduce_sum, shard_bounds
+    lo, hi = shard_bounds(bg, world, rank)
+    b = hi - lo
     oh = hw + 2 * pad - k + 1
     gen = torch.Generator(device="cuda").manual_seed(4 + rank)
     x = torch.randn((b, c, hw, hw), device="cuda", generator=gen)
@@ -377,17 +377,15 @@ def run_conv(args, world, rank, local):
         fb.conv_update_output(n, x, w, out, ws, inPad=ip)
         fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
         if world > 1 and args.dw_mode == "frequency":
-            import torch.distributed as dist
             fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.REUSE_INPUT_SPECTRUM |
                                         api.REUSE_OUTPUT_SPECTRUM | api.STOP_AFTER_CONTRACTION)
-            dist.all_reduce(wspec)
+            all_reduce_sum(wspec)
             fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.START_FROM_SPECTRUM)
         else:
             fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip,
                                         flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
             if world > 1:
-                import torch.distributed as dist
-                dist.all_reduce(gw)
+                all_reduce_sum(gw)
 
     sampler = ClockSampler(local)
     if rank == 0:

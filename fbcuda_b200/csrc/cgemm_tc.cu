@@ -36,7 +36,6 @@ namespace {
 constexpr int kProducers = 256;           // gather / split / epilogue threads (8 warps)
 constexpr int kTcThreads = kProducers + 32;  // plus one warp that only issues MMAs
 constexpr int BM = 128;   // rows of m per block
-constexpr int XB = 4;     // bins per block
 constexpr int KS = 8;     // k per stage (one tf32 MMA)
 enum : int { kErrTcStageWait = 201, kErrTcFinalWait = 202 };
 
@@ -77,12 +76,14 @@ __device__ __forceinline__ void tmem_ld8(unsigned taddr, float (&v)[8]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct TcArgs {
+  // bin x of element (m, k) of A sits at A + (x/16)*a_bs + x%16 + m*a_rs + k*a_ks (complex
+  // elements); a_bs = 16 is the natural bins-innermost layout, a_bs = planes*16 the bin-blocked one
   const float2* A;
-  long long a_rs, a_ks;  // A[m][k][x] at A + m*a_rs + k*a_ks + x   (complex elements)
+  long long a_rs, a_ks, a_bs;
   const float2* B;
-  long long b_rs, b_ks;  // B[n][k][x]
+  long long b_rs, b_ks, b_bs;  // B[n][k][x]
   float2* D;
-  long long d_ms, d_ns;  // D[m][n][x]
+  long long d_ms, d_ns, d_bs;  // D[m][n][x]
   int M, N, K, X;
   float inv_norm;
   int conjA, conjB, accumulate;
@@ -101,30 +102,54 @@ __device__ __forceinline__ void split4(const float (&v)[4], float4* hi, float4* 
   *hi = make_float4(h[0], h[1], h[2], h[3]);
   *lo = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
 }
+__device__ __forceinline__ float4 flip4(float4 v, unsigned mask) {
+  return make_float4(__uint_as_float(__float_as_uint(v.x) ^ mask), __uint_as_float(__float_as_uint(v.y) ^ mask),
+                     __uint_as_float(__float_as_uint(v.z) ^ mask), __uint_as_float(__float_as_uint(v.w) ^ mask));
+}
+
+// An MMA with M = 128 occupies the tensor pipe for 128 cycles whatever its N (measured: 48 MMAs
+// of N = 64 per step ran at a quarter of the tf32 rate), so the work is packed into as few, as
+// wide MMAs as possible: the B operand of a bin is STACKED along N,
+//   S1 = [ Br_hi | s Bi_hi | Br_lo | s Bi_lo ],   S2 = [ -s Bi_hi | Br_hi | -s Bi_lo | Br_lo ]
+// (BN rows each, s = -1 when B is conjugated), and one accumulator of 4*BN columns per bin receives
+//   Ar_hi x S1 (N = 4BN),  Ar_lo x S1[0:2BN],  Ai_hi x S2 (N = 4BN),  Ai_lo x S2[0:2BN]
+// (the Ai products negated when A is conjugated).  Its columns are then
+//   [ Re (hi*hi + lo*hi) | Im (same) | Re (hi*lo) | Im (hi*lo) ],
+// which the epilogue adds pairwise.  4 MMAs per bin and k-step instead of 12.
+template <int BN>
+struct TcCfg {
+  static constexpr int XB = (BN == 64) ? 2 : 4;           // bins per block: 4*BN*XB <= 512 TMEM columns
+  static constexpr int NS = (BN == 64) ? 3 : 2;           // shared-memory stages
+  static constexpr int A_TILE = BM * KS * 4;              // one (bin, part, split) tile of A
+  static constexpr int S_TILE = 4 * BN * KS * 4;          // one stacked B tile
+  static constexpr int A_STAGE = XB * 4 * A_TILE;
+  static constexpr int B_STAGE = XB * 2 * S_TILE;
+  static constexpr int STAGE = A_STAGE + B_STAGE;
+  static constexpr int A_LBO = (BM / 8) * 128, B_LBO = (4 * BN / 8) * 128, SBO = 128;
+  static constexpr int SMEM = NS * STAGE + 128;
+};
 
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
-  constexpr int A_TILE = BM * KS * 4;            // bytes of one (bin, part, split) tile of A
-  constexpr int B_TILE = BN * KS * 4;
-  constexpr int A_STAGE = XB * 2 * 2 * A_TILE;   // 4 bins x (re, im) x (hi, lo)
-  constexpr int B_STAGE = XB * 2 * 2 * B_TILE;
-  constexpr int STAGE = A_STAGE + B_STAGE;
-  constexpr int A_LBO = (BM / 8) * 128, B_LBO = (BN / 8) * 128, SBO = 128;
+  using Cfg = TcCfg<BN>;
+  constexpr int XB = Cfg::XB, NS = Cfg::NS, A_TILE = Cfg::A_TILE, S_TILE = Cfg::S_TILE;
+  constexpr int A_STAGE = Cfg::A_STAGE, STAGE = Cfg::STAGE, A_LBO = Cfg::A_LBO, B_LBO = Cfg::B_LBO, SBO = Cfg::SBO;
+  constexpr int V4 = XB / 2;                  // float4 loads per operand element (XB bins x 8 bytes)
   constexpr int TMEM_COLS = 512;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* stage_mem = smem_raw;
-  // [0],[1] stage filled (256 producer arrivals), [2],[3] stage free (MMA commit), [4] all MMAs done
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + 2 * STAGE);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 5);
+  // [0..NS) stage filled (256 producer arrivals), [NS..2NS) stage free (MMA commit), [2NS] all MMAs done
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + NS * STAGE);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * NS + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int x0 = blockIdx.x * XB, m0 = blockIdx.y * BM, n0 = blockIdx.z * BN;
 
   if (tid == 0) {
-    mbar_init(smem_u32(bars + 0), kProducers);
-    mbar_init(smem_u32(bars + 1), kProducers);
-    mbar_init(smem_u32(bars + 2), 1);
-    mbar_init(smem_u32(bars + 3), 1);
-    mbar_init(smem_u32(bars + 4), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(smem_u32(bars + i), kProducers);
+      mbar_init(smem_u32(bars + NS + i), 1);
+    }
+    mbar_init(smem_u32(bars + 2 * NS), 1);
     fence_async_smem();
   }
   if (warp == 0) {
@@ -137,34 +162,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   tc_fence_after();
   const unsigned tmem_base = *tmem_slot;
 
-  // ---- gather roles: every thread owns one (row, k-quad) unit of A; threads < 2*BN also one of B
+  // ---- gather roles: every producer owns one (row, k-quad) unit of A; threads < 2*BN also one of B
   const int a_row = tid % BM, a_kq = (tid / BM) & 1;     // kq in {0, 1}
   const bool has_b = tid < 2 * BN;
   const int b_row = tid % BN, b_kq = tid / BN;
   const bool a_row_ok = m0 + a_row < g.M, b_row_ok = has_b && (n0 + b_row < g.N);
-  const float2* a_src = g.A + (long long)(m0 + a_row) * g.a_rs + x0;
-  const float2* b_src = g.B + (long long)(n0 + b_row) * g.b_rs + x0;
+  const float2* a_src = g.A + (long long)(m0 + a_row) * g.a_rs + (long long)(x0 >> 4) * g.a_bs + (x0 & 15);
+  const float2* b_src = g.B + (long long)(n0 + b_row) * g.b_rs + (long long)(x0 >> 4) * g.b_bs + (x0 & 15);
   const unsigned a_dst = (unsigned)(a_kq * A_LBO + (a_row / 8) * 128 + (a_row % 8) * 16);
   const unsigned b_dst = (unsigned)(b_kq * B_LBO + (b_row / 8) * 128 + (b_row % 8) * 16);
+  const unsigned s_mask = g.conjB ? 0x80000000u : 0u;  // sign of the imaginary part of B
 
-  float4 ra[4][2], rb[4][2];  // [k in quad][bins 0-1 | bins 2-3] = (re, im, re, im)
+  float4 ra[4][V4], rb[4][V4];  // [k in quad][pair of bins] = (re, im, re, im)
   auto gather = [&](int k0) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int ka = k0 + a_kq * 4 + j, kb = k0 + b_kq * 4 + j;
-      if (a_row_ok && ka < g.K) {
-        const float4* p = reinterpret_cast<const float4*>(a_src + (long long)ka * g.a_ks);
-        ra[j][0] = __ldg(p);
-        ra[j][1] = __ldg(p + 1);
-      } else {
-        ra[j][0] = ra[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-      if (b_row_ok && kb < g.K) {
-        const float4* p = reinterpret_cast<const float4*>(b_src + (long long)kb * g.b_ks);
-        rb[j][0] = __ldg(p);
-        rb[j][1] = __ldg(p + 1);
-      } else {
-        rb[j][0] = rb[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool oka = a_row_ok && ka < g.K, okb = b_row_ok && kb < g.K;
+      const float4* pa = reinterpret_cast<const float4*>(a_src + (long long)ka * g.a_ks);
+      const float4* pb = reinterpret_cast<const float4*>(b_src + (long long)kb * g.b_ks);
+#pragma unroll
+      for (int v = 0; v < V4; ++v) {
+        ra[j][v] = oka ? __ldg(pa + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        rb[j][v] = okb ? __ldg(pb + v) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
   };
@@ -173,24 +193,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   auto scatter = [&](unsigned char* st) {
 #pragma unroll
     for (int bin = 0; bin < XB; ++bin) {
+      const int h = bin >> 1, c0 = (bin & 1) * 2;
+      {
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        const int c = (bin & 1) * 2 + part, h = bin >> 1;
-        float4 hi, lo;
-        {
-          const float v[4] = {comp(ra[0][h], c), comp(ra[1][h], c), comp(ra[2][h], c), comp(ra[3][h], c)};
+        for (int part = 0; part < 2; ++part) {
+          float4 hi, lo;
+          const float v[4] = {comp(ra[0][h], c0 + part), comp(ra[1][h], c0 + part), comp(ra[2][h], c0 + part),
+                              comp(ra[3][h], c0 + part)};
           split4(v, &hi, &lo);
           unsigned char* t = st + ((bin * 2 + part) * 2) * A_TILE + a_dst;
           *reinterpret_cast<float4*>(t) = hi;
           *reinterpret_cast<float4*>(t + A_TILE) = lo;
         }
-        if (has_b) {
-          const float v[4] = {comp(rb[0][h], c), comp(rb[1][h], c), comp(rb[2][h], c), comp(rb[3][h], c)};
-          split4(v, &hi, &lo);
-          unsigned char* t = st + A_STAGE + ((bin * 2 + part) * 2) * B_TILE + b_dst;
-          *reinterpret_cast<float4*>(t) = hi;
-          *reinterpret_cast<float4*>(t + B_TILE) = lo;
+      }
+      if (has_b) {
+        float4 brh, brl, bih, bil;
+        {
+          const float v[4] = {comp(rb[0][h], c0), comp(rb[1][h], c0), comp(rb[2][h], c0), comp(rb[3][h], c0)};
+          split4(v, &brh, &brl);
         }
+        {
+          const float v[4] = {comp(rb[0][h], c0 + 1), comp(rb[1][h], c0 + 1), comp(rb[2][h], c0 + 1),
+                              comp(rb[3][h], c0 + 1)};
+          split4(v, &bih, &bil);
+        }
+        bih = flip4(bih, s_mask);
+        bil = flip4(bil, s_mask);
+        constexpr int G = (BN / 8) * 128;  // bytes between the row groups of a stack
+        unsigned char* s1 = st + A_STAGE + (bin * 2) * S_TILE + b_dst;
+        unsigned char* s2 = s1 + S_TILE;
+        *reinterpret_cast<float4*>(s1) = brh;
+        *reinterpret_cast<float4*>(s1 + G) = bih;
+        *reinterpret_cast<float4*>(s1 + 2 * G) = brl;
+        *reinterpret_cast<float4*>(s1 + 3 * G) = bil;
+        *reinterpret_cast<float4*>(s2) = flip4(bih, 0x80000000u);
+        *reinterpret_cast<float4*>(s2 + G) = brh;
+        *reinterpret_cast<float4*>(s2 + 2 * G) = flip4(bil, 0x80000000u);
+        *reinterpret_cast<float4*>(s2 + 3 * G) = brl;
       }
     }
   };
@@ -202,59 +241,46 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
     if (lane == 0) {
       const unsigned long long a_desc0 = smem_desc(smem_u32(stage_mem), A_LBO, SBO);
       const unsigned long long b_desc0 = smem_desc(smem_u32(stage_mem) + A_STAGE, B_LBO, SBO);
-      const unsigned idesc_pos = instr_desc(BN, false, false), idesc_neg = instr_desc(BN, true, false);
-      // (A part, B part, target): Re D = Ar*Br -/+ Ai*Bi, Im D = +/- Ar*Bi +/- Ai*Br;
-      // conj(A) flips the sign of Ai, conj(B) of Bi
-      const unsigned id1 = !(g.conjA ^ g.conjB) ? idesc_neg : idesc_pos;  // Ai*Bi
-      const unsigned id2 = g.conjB ? idesc_neg : idesc_pos;               // Ar*Bi
-      const unsigned id3 = g.conjA ? idesc_neg : idesc_pos;               // Ai*Br
-      unsigned full_phase[2] = {0, 0};
+      const bool na = g.conjA != 0;   // conj(A): the Ai products change sign
+      const unsigned id_r4 = instr_desc(4 * BN, false, false), id_r2 = instr_desc(2 * BN, false, false);
+      const unsigned id_i4 = instr_desc(4 * BN, na, false), id_i2 = instr_desc(2 * BN, na, false);
       for (int s = 0; s < nsteps && ok; ++s) {
-        const int buf = s & 1;
-        if (!mbar_wait(smem_u32(bars + buf), full_phase[buf], kErrTcStageWait)) {
+        const int buf = s % NS;
+        if (!mbar_wait(smem_u32(bars + buf), (unsigned)((s / NS) & 1), kErrTcStageWait)) {
           ok = false;
           break;
         }
-        full_phase[buf] ^= 1;
         tc_fence_after();
         const unsigned long long da0 = a_desc0 + (unsigned long long)((buf * STAGE) >> 4);
         const unsigned long long db0 = b_desc0 + (unsigned long long)((buf * STAGE) >> 4);
 #pragma unroll
         for (int bin = 0; bin < XB; ++bin) {
-          const unsigned d_re = tmem_base + bin * (2 * BN), d_im = d_re + BN;
-#pragma unroll
-          for (int term = 0; term < 4; ++term) {
-            const int pa = (term == 1 || term == 3) ? 1 : 0;   // 0 = re, 1 = im
-            const int pb = (term == 1 || term == 2) ? 1 : 0;
-            const unsigned d = (term < 2) ? d_re : d_im;
-            const unsigned idesc = term == 0 ? idesc_pos : (term == 1 ? id1 : (term == 2 ? id2 : id3));
-#pragma unroll
-            for (int sp = 0; sp < 3; ++sp) {
-              const int sa_split = (sp == 2) ? 1 : 0, sb_split = (sp == 1) ? 1 : 0;  // hi*hi, hi*lo, lo*hi
-              const unsigned long long da = da0 + (unsigned long long)((((bin * 2 + pa) * 2 + sa_split) * A_TILE) >> 4);
-              const unsigned long long db = db0 + (unsigned long long)((((bin * 2 + pb) * 2 + sb_split) * B_TILE) >> 4);
-              // the first product into each accumulator overwrites it
-              const unsigned acc = (s > 0 || (term & 1) || sp > 0) ? 1u : 0u;
-              mma_tf32(d, da, db, idesc, acc);
-            }
-          }
+          const unsigned d = tmem_base + bin * (4 * BN);
+          const unsigned long long a_rh = da0 + (unsigned long long)((((bin * 2 + 0) * 2 + 0) * A_TILE) >> 4);
+          const unsigned long long a_rl = da0 + (unsigned long long)((((bin * 2 + 0) * 2 + 1) * A_TILE) >> 4);
+          const unsigned long long a_ih = da0 + (unsigned long long)((((bin * 2 + 1) * 2 + 0) * A_TILE) >> 4);
+          const unsigned long long a_il = da0 + (unsigned long long)((((bin * 2 + 1) * 2 + 1) * A_TILE) >> 4);
+          const unsigned long long s1 = db0 + (unsigned long long)(((bin * 2 + 0) * S_TILE) >> 4);
+          const unsigned long long s2 = db0 + (unsigned long long)(((bin * 2 + 1) * S_TILE) >> 4);
+          mma_tf32(d, a_rh, s1, id_r4, s > 0 ? 1u : 0u);  // the very first product overwrites the accumulator
+          mma_tf32(d, a_ih, s2, id_i4, 1u);
+          mma_tf32(d, a_rl, s1, id_r2, 1u);
+          mma_tf32(d, a_il, s2, id_i2, 1u);
         }
-        mma_commit(smem_u32(bars + 2 + buf));                 // frees the stage when these MMAs retire
-        if (s == nsteps - 1) mma_commit(smem_u32(bars + 4));  // and, after the last step, releases the epilogue
+        mma_commit(smem_u32(bars + NS + buf));                     // frees the stage when these MMAs retire
+        if (s == nsteps - 1) mma_commit(smem_u32(bars + 2 * NS));  // after the last step: releases the epilogue
       }
     }
     __syncwarp();
   } else {
     // ---- producers
-    unsigned free_phase[2] = {0, 0};
     gather(0);
     for (int s = 0; s < nsteps; ++s) {
-      const int buf = s & 1;
+      const int buf = s % NS;
       unsigned char* st = stage_mem + buf * STAGE;
-      if (s >= 2 && ok) {
-        // the MMAs that read this stage two steps ago must have retired
-        if (!mbar_wait(smem_u32(bars + 2 + buf), free_phase[buf], kErrTcStageWait)) ok = false;
-        free_phase[buf] ^= 1;
+      if (s >= NS && ok) {
+        // the MMAs that read this stage NS steps ago must have retired
+        if (!mbar_wait(smem_u32(bars + NS + buf), (unsigned)(((s / NS) - 1) & 1), kErrTcStageWait)) ok = false;
       }
       scatter(st);
       if (s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while this step's MMAs run
@@ -262,7 +288,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bars + buf)) : "memory");
     }
     // ---- epilogue: all MMAs done -> tensor memory -> global
-    if (ok && !mbar_wait(smem_u32(bars + 4), 0, kErrTcFinalWait)) ok = false;
+    if (ok && !mbar_wait(smem_u32(bars + 2 * NS), 0, kErrTcFinalWait)) ok = false;
     tc_fence_after();
     if (ok) {
       const int lq = warp & 3, ch = warp >> 2;            // lane quarter of tensor memory, column half
@@ -271,12 +297,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
 #pragma unroll 1
       for (int cc = 0; cc < CHUNKS; ++cc) {
         const int col = ch * (BN / 2) + cc * 8;
-        float v[XB][2][8];
+        float v[XB][4][8];
 #pragma unroll
         for (int bin = 0; bin < XB; ++bin) {
 #pragma unroll
-          for (int part = 0; part < 2; ++part) {
-            tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (2 * BN) + part * BN + col, v[bin][part]);
+          for (int grp = 0; grp < 4; ++grp) {
+            tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (4 * BN) + grp * BN + col, v[bin][grp]);
           }
         }
         tmem_ld_wait();
@@ -285,18 +311,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
           for (int j = 0; j < 8; ++j) {
             const int n = n0 + col + j;
             if (n < g.N) {
-              float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns + x0);
-              float4 o0 = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
-                                      v[1][1][j] * g.inv_norm);
-              float4 o1 = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
-                                      v[3][1][j] * g.inv_norm);
-              if (g.accumulate) {
-                const float4 p0 = dst[0], p1 = dst[1];
-                o0.x += p0.x, o0.y += p0.y, o0.z += p0.z, o0.w += p0.w;
-                o1.x += p1.x, o1.y += p1.y, o1.z += p1.z, o1.w += p1.w;
+              float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns +
+                                                      (long long)(x0 >> 4) * g.d_bs + (x0 & 15));
+#pragma unroll
+              for (int pr = 0; pr < V4; ++pr) {
+                const int b0 = 2 * pr, b1 = 2 * pr + 1;
+                float4 o = make_float4((v[b0][0][j] + v[b0][2][j]) * g.inv_norm, (v[b0][1][j] + v[b0][3][j]) * g.inv_norm,
+                                       (v[b1][0][j] + v[b1][2][j]) * g.inv_norm, (v[b1][1][j] + v[b1][3][j]) * g.inv_norm);
+                if (g.accumulate) {
+                  const float4 p = dst[pr];
+                  o.x += p.x, o.y += p.y, o.z += p.z, o.w += p.w;
+                }
+                dst[pr] = o;
               }
-              dst[0] = o0;
-              dst[1] = o1;
             }
           }
         }
@@ -312,7 +339,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
 
 template <int BN>
 constexpr int tc_smem_bytes() {
-  return 2 * (XB * 2 * 2 * (BM * KS * 4) + XB * 2 * 2 * (BN * KS * 4)) + 64;
+  return TcCfg<BN>::SMEM;
 }
 
 template <int BN>
@@ -324,7 +351,7 @@ int launch_tc(const TcArgs& a, cudaStream_t s) {
     cudaFuncSetAttribute(cgemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<BN>());
     configured[dev] = true;
   }
-  dim3 grid(a.X / XB, (a.M + BM - 1) / BM, (a.N + BN - 1) / BN);
+  dim3 grid(a.X / TcCfg<BN>::XB, (a.M + BM - 1) / BM, (a.N + BN - 1) / BN);
   cgemm_tc_kernel<BN><<<grid, kTcThreads, tc_smem_bytes<BN>(), s>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -339,7 +366,7 @@ int contraction_mode() { return g_mode; }
 bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const float* b, long long b_rs, long long b_ks,
                         const float* d, long long d_ms, long long d_ns, int M, int N, int K, int X) {
   if (g_mode != 0) return false;
-  if (X % XB != 0 || M < 1 || N < 1 || K < 1) return false;
+  if (X % 4 != 0 || M < 1 || N < 1 || K < 1) return false;
   // 32-byte aligned bin quads: bases 16-byte aligned, every stride a multiple of 2 complex
   const long long st[6] = {a_rs, a_ks, b_rs, b_ks, d_ms, d_ns};
   for (long long v : st)
@@ -354,11 +381,11 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
 // D[m][n][x] (+)= inv_norm * sum_k opA(A[m][k][x]) opB(B[n][k][x]); strides in complex elements
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-             bool accumulate, cudaStream_t s) {
+             bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs) {
   TcArgs t;
-  t.A = reinterpret_cast<const float2*>(a), t.a_rs = a_rs, t.a_ks = a_ks;
-  t.B = reinterpret_cast<const float2*>(b), t.b_rs = b_rs, t.b_ks = b_ks;
-  t.D = reinterpret_cast<float2*>(d), t.d_ms = d_ms, t.d_ns = d_ns;
+  t.A = reinterpret_cast<const float2*>(a), t.a_rs = a_rs, t.a_ks = a_ks, t.a_bs = a_bs;
+  t.B = reinterpret_cast<const float2*>(b), t.b_rs = b_rs, t.b_ks = b_ks, t.b_bs = b_bs;
+  t.D = reinterpret_cast<float2*>(d), t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   if (N <= 16) return launch_tc<16>(t, s);

@@ -25,10 +25,16 @@ struct RealView {
 
 // A batch of complex matrices stored as floats: element (b, r, c, z) at
 // p[b*sb + r*sr + c*sc + z*sz], z = 0 (re) or 1 (im).
+//
+// blk_planes > 0 selects the bin-blocked layout the convolution workspace uses instead: the
+// (N/2+1)*N bins of a plane are cut into blocks of 16 (128 bytes) and block xb of plane b sits
+// at p[((xb * blk_planes + b) * 16 + x % 16) * 2], so that for a fixed block all planes are
+// contiguous -- what the per-bin contraction reads.  sb/sr/sc/sz are ignored then.
 struct CplxView {
   float* p;
   long long sb;
   int sr, sc, sz;
+  long long blk_planes = 0;
 };
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -64,30 +64,70 @@ bool as_images(const Tensor4& t, RealView* v, int* count) {
   return true;
 }
 
-CplxView spectrum_view(float* p, int n) {
+// planes > 0: bin-blocked layout over that many planes (see CplxView)
+CplxView spectrum_view(float* p, int n, long long planes) {
   CplxView v;
   v.p = p;
   v.sb = bins_of(n) * 2;
   v.sr = 2 * n;
   v.sc = 2;
   v.sz = 1;
+  v.blk_planes = planes;
   return v;
 }
 
-int forward(int n, const Tensor4& t, int padL, int padU, float* spec, cudaStream_t s) {
+int forward(int n, const Tensor4& t, int padL, int padU, float* spec, bool blocked, cudaStream_t s) {
   RealView v;
   int count;
   if (!as_images(t, &v, &count)) return kUnsupportedDimension;
-  if (n <= 32) return fft2d_small_forward(n, v, spectrum_view(spec, n), count, padL, padU, s);
-  return fft2d_large_forward(n, v, spectrum_view(spec, n), count, padL, padU, s);
+  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0);
+  if (n <= 32) return fft2d_small_forward(n, v, sv, count, padL, padU, s);
+  return fft2d_large_forward(n, v, sv, count, padL, padU, s);
 }
 
-int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, cudaStream_t s) {
+int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, bool blocked, cudaStream_t s) {
   RealView v;
   int count;
   if (!as_images(t, &v, &count)) return kUnsupportedDimension;
-  if (n <= 32) return fft2d_small_inverse(n, spectrum_view(spec, n), v, count, padL, padU, s);
-  return fft2d_large_inverse(n, spectrum_view(spec, n), v, count, padL, padU, s);
+  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0);
+  if (n <= 32) return fft2d_small_inverse(n, sv, v, count, padL, padU, s);
+  return fft2d_large_inverse(n, sv, v, count, padL, padU, s);
+}
+
+// The workspace spectra use the bin-blocked layout whenever the tensor-core contraction will
+// run (its operand rows are then contiguous runs instead of isolated 32-byte sectors).  All
+// three passes of a layer take the same decision (it depends on B*C*O and on the process-wide
+// contraction mode only), so spectra reused across passes agree.
+bool use_blocked(int n, long long B, long long C, long long O) {
+  return n >= 16 && contraction_mode() == 0 && B * C * O >= 16 * 16 * 8;
+}
+
+// D[m][n] (+)= inv_norm * sum_k opA(A[m][k]) opB(B[n][k]) per bin, where element (m, k) of A is
+// plane a_pm*m + a_pk*k of a spectrum region of a_planes planes (same for B and D)
+int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk, long long a_planes, bool conjA,
+             const float* b, long long b_pn, long long b_pk, long long b_planes, bool conjB, float* d, long long d_pm,
+             long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s) {
+  const long long X = bins_of(n);
+  if (blocked) {
+    return cgemm_tc(a, a_pm * 16, a_pk * 16, conjA, b, b_pn * 16, b_pk * 16, conjB, d, d_pm * 16, d_pn * 16, M, N, K,
+                    (int)X, inv_norm, false, s, a_planes * 16, b_planes * 16, d_planes * 16);
+  }
+  // natural layout: D[m][n] = sum_k opA(A[m][k]) opB(B[n][k]) = cgemm_bins with A' = A (rows m),
+  // B' = B^T: C[i=m][j=n] = sum_k opA(A[i][k]) * opB'(B'[k][j]), B'[k][j] = B[j][k] -> "conj-transposed" flag
+  // carries the transposition, so express through strides instead: use the generic entry with
+  // as0 = a_pm*X, as1 = a_pk*X; B given as [k][j] with bs0 = b_pk*X, bs1 = b_pn*X
+  if (conjA && !conjB) {
+    // cgemm_bins conjugates only together with a transposition: op(A)[i][k] = conj(A[k][i]) with
+    // strides (as0 for k, as1 for i)
+    return cgemm_bins(true, false, false, a, a_pk * X, a_pm * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
+                      (int)X, inv_norm, s);
+  }
+  if (!conjA && conjB) {
+    return cgemm_bins(false, true, false, a, a_pm * X, a_pk * X, b, b_pn * X, b_pk * X, d, d_pm * X, d_pn * X, M, N, K,
+                      (int)X, inv_norm, s);
+  }
+  return cgemm_bins(false, false, false, a, a_pm * X, a_pk * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
+                    (int)X, inv_norm, s);
 }
 
 Tensor4 make_tensor(const float* p, const int* size, const int* stride) {
@@ -176,14 +216,15 @@ int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_s
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long X = bins_of(n);
-  if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, s))) return rc;
-  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, s))) return rc;
-  // res[b][o] = sum_c in[b][c] conj(w[o][c]) / N^2
-  rc = cgemm_bins(false, true, false, ws + r.in_off, C * X, X, ws + r.w_off, C * X, X, ws + r.res_off, O * X, X, B, O, C,
-                  (int)X, 1.0f / ((float)n * (float)n), s);
+  const bool blk = use_blocked(n, B, C, O);
+  if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
+    return rc;
+  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
+  // res[b][o] = sum_c conj(w[o][c]) in[b][c] / N^2      (m = o, n = b, k = c)
+  rc = contract(n, blk, ws + r.w_off, C, 1, (long long)O * C, true, ws + r.in_off, C, 1, (long long)B * C, false,
+                ws + r.res_off, 1, O, (long long)B * O, O, B, C, 1.0f / ((float)n * (float)n), s);
   if (rc) return rc;
-  return inverse(n, ws + r.res_off, to, out_padL, out_padU, s);
+  return inverse(n, ws + r.res_off, to, out_padL, out_padU, blk, s);
 }
 
 int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* in_size, const int* in_stride,
@@ -204,15 +245,15 @@ int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* i
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long X = bins_of(n);
-  if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, s)))
+  const bool blk = use_blocked(n, B, C, O);
+  if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
     return rc;
-  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, s))) return rc;
-  // res[b][c] = sum_o out[b][o] w[o][c] / N^2
-  rc = cgemm_bins(false, false, false, ws + r.out_off, O * X, X, ws + r.w_off, C * X, X, ws + r.res_off, C * X, X, B, C,
-                  O, (int)X, 1.0f / ((float)n * (float)n), s);
+  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
+  // res[b][c] = sum_o w[o][c] out[b][o] / N^2           (m = c, n = b, k = o)
+  rc = contract(n, blk, ws + r.w_off, 1, C, (long long)O * C, false, ws + r.out_off, O, 1, (long long)B * O, false,
+                ws + r.res_off, 1, C, (long long)B * C, C, B, O, 1.0f / ((float)n * (float)n), s);
   if (rc) return rc;
-  return inverse(n, ws + r.res_off, ti, in_padL, in_padU, s);
+  return inverse(n, ws + r.res_off, ti, in_padL, in_padU, blk, s);
 }
 
 int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int* in_size, const int* in_stride,
@@ -233,22 +274,24 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long X = bins_of(n);
+  const bool blk = use_blocked(n, B, C, O);
   if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
     if (B == 0) {
       if (cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
     } else {
-      if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, s)))
+      if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
         return rc;
-      if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, s)))
+      if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) &&
+          (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
         return rc;
-      // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]
-      rc = cgemm_bins(true, false, false, ws + r.out_off, O * X, X, ws + r.in_off, C * X, X, ws + r.res_off, C * X, X, O,
-                      C, B, (int)X, scale / ((float)n * (float)n), s);
+      // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]      (m = o, n = c, k = b)
+      rc = contract(n, blk, ws + r.out_off, 1, O, (long long)B * O, true, ws + r.in_off, 1, C, (long long)B * C, false,
+                    ws + r.res_off, C, 1, (long long)O * C, O, C, B, scale / ((float)n * (float)n), s);
       if (rc) return rc;
     }
   }
   if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
-  return inverse(n, ws + r.res_off, tw, 0, 0, s);
+  return inverse(n, ws + r.res_off, tw, 0, 0, blk, s);
 }
 
 }  // extern "C"

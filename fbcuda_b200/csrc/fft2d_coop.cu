@@ -120,7 +120,7 @@ __device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
 template <int N, bool IN_BULK>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
-                                                                                int padU) {
+                                                                                int padU, long long blk_planes) {
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
@@ -270,7 +270,16 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     fence_async_smem();
     block_sync<T>();
     float* dst = out + (long long)b * out_sb;
-    for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
+    if (blk_planes) {
+      // bin-blocked layout (convolution workspace): 128-byte pieces, planes adjacent
+      constexpr int CB = N / 16;
+      for (int i = threadIdx.x; i < (H + 1) * CB; i += T) {
+        const int kx = i / CB, cb = i % CB;
+        bulk_s2g(out + ((long long)i * blk_planes + b) * 32, smem_u32(tile + kx * PO + cb * 16), 128);
+      }
+    } else {
+      for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
+    }
     bulk_commit();
     if (IN_BULK) {
       // the next image is staged into the region the rows are leaving from
@@ -287,7 +296,7 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 template <int N>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
                                                                                 long long in_sb, RealView out, int B,
-                                                                                int padL, int padU) {
+                                                                                int padL, int padU, long long blk_planes) {
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
@@ -310,8 +319,16 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     fence_async_smem();
     if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)((H + 1) * N * 8));
     block_sync<T>();
-    const float* src = in + (long long)b * in_sb;
-    for (int kx = threadIdx.x; kx <= H; kx += T) bulk_g2s(smem_u32(tile + kx * PO), src + (long long)kx * (2 * N), N * 8, bar);
+    if (blk_planes) {
+      constexpr int CB = N / 16;
+      for (int i = threadIdx.x; i < (H + 1) * CB; i += T) {
+        const int kx = i / CB, cb = i % CB;
+        bulk_g2s(smem_u32(tile + kx * PO + cb * 16), in + ((long long)i * blk_planes + b) * 32, 128, bar);
+      }
+    } else {
+      const float* src = in + (long long)b * in_sb;
+      for (int kx = threadIdx.x; kx <= H; kx += T) bulk_g2s(smem_u32(tile + kx * PO), src + (long long)kx * (2 * N), N * 8, bar);
+    }
   };
   if (blockIdx.x < B) fetch(blockIdx.x);
 
@@ -431,9 +448,9 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
   if (in_bulk) {
-    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   } else {
-    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU);
+    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -450,13 +467,14 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
-  fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU);
+  fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
 }  // namespace
 
 bool fft2d_coop_supported(int n, const CplxView& c) {
+  if (c.blk_planes) return (n == 64 || n == 128) && aligned16(c.p);
   return (n == 64 || n == 128) && c.sz == 1 && c.sc == 2 && c.sr == 2 * n && (c.sb % 4) == 0 && aligned16(c.p);
 }
 

@@ -137,7 +137,18 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
     if (OUT_BULK) {
       fence_async_smem();
       __syncwarp();
-      if (RS == N) {
+      if (N >= 16 && out.blk_planes) {
+        // bin-blocked layout: every 16-bin (128-byte) piece of a row goes next to the same piece
+        // of the neighbouring planes
+        constexpr int CB = N >= 16 ? N / 16 : 1;
+        for (int r = lane; r < IPW * ROWS * CB; r += 32) {
+          const int img = r / (ROWS * CB), rem = r % (ROWS * CB), row = rem / CB, cb = rem % CB;
+          const int bb = task * IPW + img;
+          if (bb < B)
+            bulk_s2g(out.p + ((long long)(row * CB + cb) * out.blk_planes + bb) * 32,
+                     smem_u32(buf + img * IS + row * RS + cb * 16), 128);
+        }
+      } else if (RS == N) {
         // rows are contiguous in shared memory: one copy per image
         if (lane < IPW && task * IPW + lane < B)
           bulk_s2g(out.p + (long long)(task * IPW + lane) * out.sb, smem_u32(buf + lane * IS), ROWS * N * 8);
@@ -195,7 +206,14 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
     __syncwarp();
     if (lane == 0) mbar_expect_tx(bar, (unsigned)(imgs * ROWS * N * 8));
     __syncwarp();
-    if (RS == N) {
+    if (N >= 16 && in.blk_planes) {
+      constexpr int CB = N >= 16 ? N / 16 : 1;
+      for (int r = lane; r < imgs * ROWS * CB; r += 32) {
+        const int img = r / (ROWS * CB), rem = r % (ROWS * CB), row = rem / CB, cb = rem % CB;
+        bulk_g2s(smem_u32(dstbuf + img * IS + row * RS + cb * 16),
+                 in.p + ((long long)(row * CB + cb) * in.blk_planes + task * IPW + img) * 32, 128, bar);
+      }
+    } else if (RS == N) {
       // rows are contiguous in shared memory: one copy per image
       if (lane < imgs)
         bulk_g2s(smem_u32(dstbuf + lane * IS), in.p + (long long)(task * IPW + lane) * in.sb, ROWS * N * 8, bar);
@@ -258,6 +276,7 @@ constexpr int work_floats() {
 }
 
 bool cplx_is_contiguous16(const CplxView& c, int cols) {
+  if (c.blk_planes) return cols >= 16 && aligned16(c.p);
   return c.sz == 1 && c.sc == 2 && c.sr == 2 * cols && (c.sb % 4) == 0 && aligned16(c.p);
 }
 bool real_is_contiguous16(const RealView& r, int B) {

@@ -54,7 +54,7 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
                         const float* d, long long d_ms, long long d_ns, int M, int N, int K, int X);
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-             bool accumulate, cudaStream_t s);
+             bool accumulate, cudaStream_t s, long long a_bs = 16, long long b_bs = 16, long long d_bs = 16);
 void set_contraction_mode(int mode);  // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only
 int contraction_mode();
 int read_device_error_tc();

@@ -1,0 +1,71 @@
+"""World-size-2 gloo run on CPU of the data-parallel protocol for accGradParameters:
+each rank contracts its batch shard into a frequency-domain weight gradient, the
+ranks all-reduce it, and the inverse transform of the sum equals the full-batch
+gradient -- checked with the float64 oracle standing in for the kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fbcuda_b200.dist import all_reduce_sum, shard_bounds
+from oracle import fbfft_oracle as orc
+
+
+def test_shard_bounds_cover_the_batch():
+    for batch in (0, 1, 7, 64):
+        for world in (1, 2, 3, 8):
+            spans = [shard_bounds(batch, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == batch
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [hi - lo for lo, hi in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_bounds(4, 2, 2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n, b, c, o, hw, k = 16, 5, 3, 2, 12, 3
+    rng = np.random.default_rng(3)
+    x = rng.normal(size=(b, c, hw, hw))
+    go = rng.normal(size=(b, o, hw - k + 1, hw - k + 1))
+    lo, hi = shard_bounds(b, world, rank)
+    # frequency-domain contribution of this shard (what STOP_AFTER_CONTRACTION leaves behind)
+    fi = np.fft.rfft2(np.pad(x[lo:hi], ((0, 0), (0, 0), (0, n - hw), (0, n - hw))), axes=(-2, -1))
+    fo = np.fft.rfft2(np.pad(go[lo:hi], ((0, 0), (0, 0), (0, n - hw + k - 1), (0, n - hw + k - 1))), axes=(-2, -1))
+    spec = np.einsum("bcyx,boyx->ocyx", fi, np.conj(fo))
+    t = torch.from_numpy(np.stack([spec.real, spec.imag], -1).copy())
+    all_reduce_sum(t)
+    total = t[..., 0].numpy() + 1j * t[..., 1].numpy()
+    gw = np.fft.irfft2(total, s=(n, n), axes=(-2, -1))[..., :k, :k]
+    want = orc.conv_acc_grad_parameters(x, go, k, k)
+    err = orc.rel_l2(gw, want)
+    # spatial-domain variant: inverse first, then all-reduce
+    gw_local = torch.from_numpy(np.fft.irfft2(spec, s=(n, n), axes=(-2, -1))[..., :k, :k].copy())
+    all_reduce_sum(gw_local)
+    err2 = orc.rel_l2(gw_local.numpy(), want)
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
+        f.write(f"{err} {err2}")
+    dist.destroy_process_group()
+
+
+def test_two_rank_weight_gradient_all_reduce(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        e1, e2 = map(float, open(tmp_path / f"r{r}.txt").read().split())
+        assert e1 < 1e-12 and e2 < 1e-12
