@@ -107,49 +107,55 @@ __device__ __forceinline__ float4 flip4(float4 v, unsigned mask) {
                      __uint_as_float(__float_as_uint(v.z) ^ mask), __uint_as_float(__float_as_uint(v.w) ^ mask));
 }
 
-// An MMA with M = 128 occupies the tensor pipe for 128 cycles whatever its N (measured: 48 MMAs
-// of N = 64 per step ran at a quarter of the tf32 rate), so the work is packed into as few, as
-// wide MMAs as possible: the B operand of a bin is STACKED along N,
-//   S1 = [ Br_hi | s Bi_hi | Br_lo | s Bi_lo ],   S2 = [ -s Bi_hi | Br_hi | -s Bi_lo | Br_lo ]
-// (BN rows each, s = -1 when B is conjugated), and one accumulator of 4*BN columns per bin receives
-//   Ar_hi x S1 (N = 4BN),  Ar_lo x S1[0:2BN],  Ai_hi x S2 (N = 4BN),  Ai_lo x S2[0:2BN]
-// (the Ai products negated when A is conjugated).  Its columns are then
-//   [ Re (hi*hi + lo*hi) | Im (same) | Re (hi*lo) | Im (hi*lo) ],
-// which the epilogue adds pairwise.  4 MMAs per bin and k-step instead of 12.
+__device__ __forceinline__ void ldg32(const float2* p, float4& lo, float4& hi) {
+  // one 256-bit load per lane: a whole 32-byte sector per request slot instead of two half-sector requests
+  asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w), "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w)
+               : "l"(p));
+}
+
+// An MMA with M = 128 occupies the tensor pipe for about 128 cycles whatever its N (measured: 48
+// MMAs of N = 64 per step ran at a quarter of the tf32 rate), so the real and imaginary parts of B
+// are STACKED along N and each MMA is 2*BN wide:
+//   S = [ Br | s Bi ],   S' = [ -s Bi | Br ]      (BN rows each; s = -1 when B is conjugated)
+// and the accumulator of a bin, [ Re | Im ] (2*BN columns), receives per k-step
+//   Ar_hi x S_hi,  Ar_hi x S_lo,  Ar_lo x S_hi,  Ai_hi x S'_hi,  Ai_hi x S'_lo,  Ai_lo x S'_hi
+// (the Ai products negated when A is conjugated): 6 MMAs instead of 12.
+// A block owns 4 bins = 4 x 2*BN = 512 tensor-memory columns at BN = 64.  Shared memory is a ring of
+// three "half stages" of two bins each, so the MMAs of one bin pair run while the next is written.
 template <int BN>
 struct TcCfg {
-  static constexpr int XB = (BN == 64) ? 2 : 4;           // bins per block: 4*BN*XB <= 512 TMEM columns
-  static constexpr int NS = (BN == 64) ? 3 : 2;           // shared-memory stages
-  static constexpr int A_TILE = BM * KS * 4;              // one (bin, part, split) tile of A
-  static constexpr int S_TILE = 4 * BN * KS * 4;          // one stacked B tile
-  static constexpr int A_STAGE = XB * 4 * A_TILE;
-  static constexpr int B_STAGE = XB * 2 * S_TILE;
-  static constexpr int STAGE = A_STAGE + B_STAGE;
-  static constexpr int A_LBO = (BM / 8) * 128, B_LBO = (4 * BN / 8) * 128, SBO = 128;
-  static constexpr int SMEM = NS * STAGE + 128;
+  static constexpr int XB = 4;                             // bins per block
+  static constexpr int NSH = 3;                            // half stages (2 bins each) in the ring
+  static constexpr int A_TILE = BM * KS * 4;               // one (bin, part, split) tile of A
+  static constexpr int S_TILE = 2 * BN * KS * 4;           // one stacked B tile
+  static constexpr int HALF_A = 2 * 4 * A_TILE;
+  static constexpr int HALF_B = 2 * 4 * S_TILE;
+  static constexpr int HSTAGE = HALF_A + HALF_B;
+  static constexpr int A_LBO = (BM / 8) * 128, B_LBO = (2 * BN / 8) * 128, SBO = 128;
+  static constexpr int SMEM = NSH * HSTAGE + 128;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   using Cfg = TcCfg<BN>;
-  constexpr int XB = Cfg::XB, NS = Cfg::NS, A_TILE = Cfg::A_TILE, S_TILE = Cfg::S_TILE;
-  constexpr int A_STAGE = Cfg::A_STAGE, STAGE = Cfg::STAGE, A_LBO = Cfg::A_LBO, B_LBO = Cfg::B_LBO, SBO = Cfg::SBO;
-  constexpr int V4 = XB / 2;                  // float4 loads per operand element (XB bins x 8 bytes)
+  constexpr int XB = Cfg::XB, NSH = Cfg::NSH, A_TILE = Cfg::A_TILE, S_TILE = Cfg::S_TILE;
+  constexpr int HALF_A = Cfg::HALF_A, HSTAGE = Cfg::HSTAGE, A_LBO = Cfg::A_LBO, B_LBO = Cfg::B_LBO, SBO = Cfg::SBO;
   constexpr int TMEM_COLS = 512;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* stage_mem = smem_raw;
-  // [0..NS) stage filled (256 producer arrivals), [NS..2NS) stage free (MMA commit), [2NS] all MMAs done
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + NS * STAGE);
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * NS + 1);
+  // [0..NSH) half stage filled (256 producer arrivals), [NSH..2NSH) half stage free (MMA commit), [2NSH] done
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + NSH * HSTAGE);
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * NSH + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int x0 = blockIdx.x * XB, m0 = blockIdx.y * BM, n0 = blockIdx.z * BN;
 
   if (tid == 0) {
-    for (int i = 0; i < NS; ++i) {
+    for (int i = 0; i < NSH; ++i) {
       mbar_init(smem_u32(bars + i), kProducers);
-      mbar_init(smem_u32(bars + NS + i), 1);
+      mbar_init(smem_u32(bars + NSH + i), 1);
     }
-    mbar_init(smem_u32(bars + 2 * NS), 1);
+    mbar_init(smem_u32(bars + 2 * NSH), 1);
     fence_async_smem();
   }
   if (warp == 0) {
@@ -173,102 +179,112 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   const unsigned b_dst = (unsigned)(b_kq * B_LBO + (b_row / 8) * 128 + (b_row % 8) * 16);
   const unsigned s_mask = g.conjB ? 0x80000000u : 0u;  // sign of the imaginary part of B
 
-  float4 ra[4][V4], rb[4][V4];  // [k in quad][pair of bins] = (re, im, re, im)
+  float4 ra[4][2], rb[4][2];  // [k in quad][bins 0-1 | bins 2-3] = (re, im, re, im)
   auto gather = [&](int k0) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int ka = k0 + a_kq * 4 + j, kb = k0 + b_kq * 4 + j;
-      const bool oka = a_row_ok && ka < g.K, okb = b_row_ok && kb < g.K;
-      const float4* pa = reinterpret_cast<const float4*>(a_src + (long long)ka * g.a_ks);
-      const float4* pb = reinterpret_cast<const float4*>(b_src + (long long)kb * g.b_ks);
-#pragma unroll
-      for (int v = 0; v < V4; ++v) {
-        ra[j][v] = oka ? __ldg(pa + v) : make_float4(0.f, 0.f, 0.f, 0.f);
-        rb[j][v] = okb ? __ldg(pb + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a_row_ok && ka < g.K) {
+        ldg32(a_src + (long long)ka * g.a_ks, ra[j][0], ra[j][1]);
+      } else {
+        ra[j][0] = ra[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      if (b_row_ok && kb < g.K) {
+        ldg32(b_src + (long long)kb * g.b_ks, rb[j][0], rb[j][1]);
+      } else {
+        rb[j][0] = rb[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
   };
   // component c of a float4 (compile-time c)
   auto comp = [](const float4& v, int c) { return c == 0 ? v.x : (c == 1 ? v.y : (c == 2 ? v.z : v.w)); };
-  auto scatter = [&](unsigned char* st) {
+  // writes bins 2*pair and 2*pair+1 of the current k-step into half stage `st`
+  auto scatter = [&](unsigned char* st, int pair) {
 #pragma unroll
-    for (int bin = 0; bin < XB; ++bin) {
-      const int h = bin >> 1, c0 = (bin & 1) * 2;
-      {
+    for (int binl = 0; binl < 2; ++binl) {
+      const int c0 = binl * 2;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {
-          float4 hi, lo;
-          const float v[4] = {comp(ra[0][h], c0 + part), comp(ra[1][h], c0 + part), comp(ra[2][h], c0 + part),
-                              comp(ra[3][h], c0 + part)};
-          split4(v, &hi, &lo);
-          unsigned char* t = st + ((bin * 2 + part) * 2) * A_TILE + a_dst;
-          *reinterpret_cast<float4*>(t) = hi;
-          *reinterpret_cast<float4*>(t + A_TILE) = lo;
-        }
+      for (int part = 0; part < 2; ++part) {
+        float4 hi, lo;
+        const float v[4] = {pair ? comp(ra[0][1], c0 + part) : comp(ra[0][0], c0 + part),
+                            pair ? comp(ra[1][1], c0 + part) : comp(ra[1][0], c0 + part),
+                            pair ? comp(ra[2][1], c0 + part) : comp(ra[2][0], c0 + part),
+                            pair ? comp(ra[3][1], c0 + part) : comp(ra[3][0], c0 + part)};
+        split4(v, &hi, &lo);
+        unsigned char* t = st + ((binl * 2 + part) * 2) * A_TILE + a_dst;
+        *reinterpret_cast<float4*>(t) = hi;
+        *reinterpret_cast<float4*>(t + A_TILE) = lo;
       }
       if (has_b) {
         float4 brh, brl, bih, bil;
         {
-          const float v[4] = {comp(rb[0][h], c0), comp(rb[1][h], c0), comp(rb[2][h], c0), comp(rb[3][h], c0)};
+          const float v[4] = {pair ? comp(rb[0][1], c0) : comp(rb[0][0], c0), pair ? comp(rb[1][1], c0) : comp(rb[1][0], c0),
+                              pair ? comp(rb[2][1], c0) : comp(rb[2][0], c0), pair ? comp(rb[3][1], c0) : comp(rb[3][0], c0)};
           split4(v, &brh, &brl);
         }
         {
-          const float v[4] = {comp(rb[0][h], c0 + 1), comp(rb[1][h], c0 + 1), comp(rb[2][h], c0 + 1),
-                              comp(rb[3][h], c0 + 1)};
+          const float v[4] = {pair ? comp(rb[0][1], c0 + 1) : comp(rb[0][0], c0 + 1),
+                              pair ? comp(rb[1][1], c0 + 1) : comp(rb[1][0], c0 + 1),
+                              pair ? comp(rb[2][1], c0 + 1) : comp(rb[2][0], c0 + 1),
+                              pair ? comp(rb[3][1], c0 + 1) : comp(rb[3][0], c0 + 1)};
           split4(v, &bih, &bil);
         }
         bih = flip4(bih, s_mask);
         bil = flip4(bil, s_mask);
-        constexpr int G = (BN / 8) * 128;  // bytes between the row groups of a stack
-        unsigned char* s1 = st + A_STAGE + (bin * 2) * S_TILE + b_dst;
-        unsigned char* s2 = s1 + S_TILE;
-        *reinterpret_cast<float4*>(s1) = brh;
-        *reinterpret_cast<float4*>(s1 + G) = bih;
-        *reinterpret_cast<float4*>(s1 + 2 * G) = brl;
-        *reinterpret_cast<float4*>(s1 + 3 * G) = bil;
-        *reinterpret_cast<float4*>(s2) = flip4(bih, 0x80000000u);
-        *reinterpret_cast<float4*>(s2 + G) = brh;
-        *reinterpret_cast<float4*>(s2 + 2 * G) = flip4(bil, 0x80000000u);
-        *reinterpret_cast<float4*>(s2 + 3 * G) = brl;
+        constexpr int G = (BN / 8) * 128;  // bytes from the first to the second row group of a stack
+        unsigned char* t = st + HALF_A + (binl * 4) * S_TILE + b_dst;
+        *reinterpret_cast<float4*>(t) = brh;                                         // S_hi  = [ Br_hi | s Bi_hi ]
+        *reinterpret_cast<float4*>(t + G) = bih;
+        *reinterpret_cast<float4*>(t + S_TILE) = brl;                                // S_lo
+        *reinterpret_cast<float4*>(t + S_TILE + G) = bil;
+        *reinterpret_cast<float4*>(t + 2 * S_TILE) = flip4(bih, 0x80000000u);        // S'_hi = [ -s Bi_hi | Br_hi ]
+        *reinterpret_cast<float4*>(t + 2 * S_TILE + G) = brh;
+        *reinterpret_cast<float4*>(t + 3 * S_TILE) = flip4(bil, 0x80000000u);        // S'_lo
+        *reinterpret_cast<float4*>(t + 3 * S_TILE + G) = brl;
       }
     }
   };
 
   const int nsteps = (g.K + KS - 1) / KS;
+  const int nhalf = 2 * nsteps;
   bool ok = true;
   if (warp == kProducers / 32) {
     // ---- MMA warp: one lane issues; it never touches operands, only descriptors
     if (lane == 0) {
       const unsigned long long a_desc0 = smem_desc(smem_u32(stage_mem), A_LBO, SBO);
-      const unsigned long long b_desc0 = smem_desc(smem_u32(stage_mem) + A_STAGE, B_LBO, SBO);
-      const bool na = g.conjA != 0;   // conj(A): the Ai products change sign
-      const unsigned id_r4 = instr_desc(4 * BN, false, false), id_r2 = instr_desc(2 * BN, false, false);
-      const unsigned id_i4 = instr_desc(4 * BN, na, false), id_i2 = instr_desc(2 * BN, na, false);
-      for (int s = 0; s < nsteps && ok; ++s) {
-        const int buf = s % NS;
-        if (!mbar_wait(smem_u32(bars + buf), (unsigned)((s / NS) & 1), kErrTcStageWait)) {
+      const unsigned long long b_desc0 = smem_desc(smem_u32(stage_mem) + HALF_A, B_LBO, SBO);
+      const unsigned id_r = instr_desc(2 * BN, false, false);
+      const unsigned id_i = instr_desc(2 * BN, g.conjA != 0, false);  // conj(A): the Ai products change sign
+      for (int h = 0; h < nhalf && ok; ++h) {
+        const int buf = h % NSH, pair = h & 1;
+        if (!mbar_wait(smem_u32(bars + buf), (unsigned)((h / NSH) & 1), kErrTcStageWait)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const unsigned long long da0 = a_desc0 + (unsigned long long)((buf * STAGE) >> 4);
-        const unsigned long long db0 = b_desc0 + (unsigned long long)((buf * STAGE) >> 4);
+        const unsigned long long da0 = a_desc0 + (unsigned long long)((buf * HSTAGE) >> 4);
+        const unsigned long long db0 = b_desc0 + (unsigned long long)((buf * HSTAGE) >> 4);
+        const unsigned first = (h >= 2) ? 1u : 0u;  // the first product into an accumulator overwrites it
 #pragma unroll
-        for (int bin = 0; bin < XB; ++bin) {
-          const unsigned d = tmem_base + bin * (4 * BN);
-          const unsigned long long a_rh = da0 + (unsigned long long)((((bin * 2 + 0) * 2 + 0) * A_TILE) >> 4);
-          const unsigned long long a_rl = da0 + (unsigned long long)((((bin * 2 + 0) * 2 + 1) * A_TILE) >> 4);
-          const unsigned long long a_ih = da0 + (unsigned long long)((((bin * 2 + 1) * 2 + 0) * A_TILE) >> 4);
-          const unsigned long long a_il = da0 + (unsigned long long)((((bin * 2 + 1) * 2 + 1) * A_TILE) >> 4);
-          const unsigned long long s1 = db0 + (unsigned long long)(((bin * 2 + 0) * S_TILE) >> 4);
-          const unsigned long long s2 = db0 + (unsigned long long)(((bin * 2 + 1) * S_TILE) >> 4);
-          mma_tf32(d, a_rh, s1, id_r4, s > 0 ? 1u : 0u);  // the very first product overwrites the accumulator
-          mma_tf32(d, a_ih, s2, id_i4, 1u);
-          mma_tf32(d, a_rl, s1, id_r2, 1u);
-          mma_tf32(d, a_il, s2, id_i2, 1u);
+        for (int binl = 0; binl < 2; ++binl) {
+          const unsigned d = tmem_base + (pair * 2 + binl) * (2 * BN);
+          const unsigned long long a_rh = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 0) * A_TILE) >> 4);
+          const unsigned long long a_rl = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 1) * A_TILE) >> 4);
+          const unsigned long long a_ih = da0 + (unsigned long long)((((binl * 2 + 1) * 2 + 0) * A_TILE) >> 4);
+          const unsigned long long a_il = da0 + (unsigned long long)((((binl * 2 + 1) * 2 + 1) * A_TILE) >> 4);
+          const unsigned long long s_h = db0 + (unsigned long long)(((binl * 4 + 0) * S_TILE) >> 4);
+          const unsigned long long s_l = db0 + (unsigned long long)(((binl * 4 + 1) * S_TILE) >> 4);
+          const unsigned long long t_h = db0 + (unsigned long long)(((binl * 4 + 2) * S_TILE) >> 4);
+          const unsigned long long t_l = db0 + (unsigned long long)(((binl * 4 + 3) * S_TILE) >> 4);
+          mma_tf32(d, a_rh, s_h, id_r, first);
+          mma_tf32(d, a_ih, t_h, id_i, 1u);
+          mma_tf32(d, a_rh, s_l, id_r, 1u);
+          mma_tf32(d, a_ih, t_l, id_i, 1u);
+          mma_tf32(d, a_rl, s_h, id_r, 1u);
+          mma_tf32(d, a_il, t_h, id_i, 1u);
         }
-        mma_commit(smem_u32(bars + NS + buf));                     // frees the stage when these MMAs retire
-        if (s == nsteps - 1) mma_commit(smem_u32(bars + 2 * NS));  // after the last step: releases the epilogue
+        mma_commit(smem_u32(bars + NSH + buf));                     // frees the half stage when these MMAs retire
+        if (h == nhalf - 1) mma_commit(smem_u32(bars + 2 * NSH));   // after the last one: releases the epilogue
       }
     }
     __syncwarp();
@@ -276,19 +292,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
     // ---- producers
     gather(0);
     for (int s = 0; s < nsteps; ++s) {
-      const int buf = s % NS;
-      unsigned char* st = stage_mem + buf * STAGE;
-      if (s >= NS && ok) {
-        // the MMAs that read this stage NS steps ago must have retired
-        if (!mbar_wait(smem_u32(bars + NS + buf), (unsigned)(((s / NS) - 1) & 1), kErrTcStageWait)) ok = false;
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        const int h = 2 * s + pair, buf = h % NSH;
+        if (h >= NSH && ok) {
+          // the MMAs that read this half stage NSH half steps ago must have retired
+          if (!mbar_wait(smem_u32(bars + NSH + buf), (unsigned)(((h / NSH) - 1) & 1), kErrTcStageWait)) ok = false;
+        }
+        scatter(stage_mem + buf * HSTAGE, pair);
+        if (pair == 1 && s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while the MMAs run
+        fence_async_smem();                                     // generic-proxy writes -> visible to the tensor core
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bars + buf)) : "memory");
       }
-      scatter(st);
-      if (s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while this step's MMAs run
-      fence_async_smem();                        // generic-proxy writes -> visible to the tensor core
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bars + buf)) : "memory");
     }
     // ---- epilogue: all MMAs done -> tensor memory -> global
-    if (ok && !mbar_wait(smem_u32(bars + 2 * NS), 0, kErrTcFinalWait)) ok = false;
+    if (ok && !mbar_wait(smem_u32(bars + 2 * NSH), 0, kErrTcFinalWait)) ok = false;
     tc_fence_after();
     if (ok) {
       const int lq = warp & 3, ch = warp >> 2;            // lane quarter of tensor memory, column half
@@ -297,12 +315,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
 #pragma unroll 1
       for (int cc = 0; cc < CHUNKS; ++cc) {
         const int col = ch * (BN / 2) + cc * 8;
-        float v[XB][4][8];
+        float v[XB][2][8];
 #pragma unroll
         for (int bin = 0; bin < XB; ++bin) {
 #pragma unroll
-          for (int grp = 0; grp < 4; ++grp) {
-            tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (4 * BN) + grp * BN + col, v[bin][grp]);
+          for (int part = 0; part < 2; ++part) {
+            tmem_ld8(tmem_base + ((unsigned)(lq * 32) << 16) + bin * (2 * BN) + part * BN + col, v[bin][part]);
           }
         }
         tmem_ld_wait();
@@ -313,17 +331,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
             if (n < g.N) {
               float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns +
                                                       (long long)(x0 >> 4) * g.d_bs + (x0 & 15));
-#pragma unroll
-              for (int pr = 0; pr < V4; ++pr) {
-                const int b0 = 2 * pr, b1 = 2 * pr + 1;
-                float4 o = make_float4((v[b0][0][j] + v[b0][2][j]) * g.inv_norm, (v[b0][1][j] + v[b0][3][j]) * g.inv_norm,
-                                       (v[b1][0][j] + v[b1][2][j]) * g.inv_norm, (v[b1][1][j] + v[b1][3][j]) * g.inv_norm);
-                if (g.accumulate) {
-                  const float4 p = dst[pr];
-                  o.x += p.x, o.y += p.y, o.z += p.z, o.w += p.w;
-                }
-                dst[pr] = o;
+              float4 o0 = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
+                                      v[1][1][j] * g.inv_norm);
+              float4 o1 = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
+                                      v[3][1][j] * g.inv_norm);
+              if (g.accumulate) {
+                const float4 p0 = dst[0], p1 = dst[1];
+                o0.x += p0.x, o0.y += p0.y, o0.z += p0.z, o0.w += p0.w;
+                o1.x += p1.x, o1.y += p1.y, o1.z += p1.z, o1.w += p1.w;
               }
+              dst[0] = o0;
+              dst[1] = o1;
             }
           }
         }
@@ -370,8 +388,8 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
   // 32-byte aligned bin quads: bases 16-byte aligned, every stride a multiple of 2 complex
   const long long st[6] = {a_rs, a_ks, b_rs, b_ks, d_ms, d_ns};
   for (long long v : st)
-    if (v % 2 != 0) return false;
-  if (!aligned16(a) || !aligned16(b) || !aligned16(d)) return false;
+    if (v % 4 != 0) return false;   // 32-byte loads: every stride a multiple of 4 complex
+  if ((reinterpret_cast<uintptr_t>(a) & 31u) || (reinterpret_cast<uintptr_t>(b) & 31u) || !aligned16(d)) return false;
   const long long grid_y = (M + BM - 1) / BM, grid_z = (N + 15) / 16;
   if (grid_y > 65535 || grid_z > 65535) return false;
   // small problems are not worth a 128-row tile

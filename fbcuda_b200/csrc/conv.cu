@@ -216,7 +216,7 @@ int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_s
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool blk = use_blocked(n, B, C, O);
+  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
   if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
     return rc;
   if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
@@ -245,7 +245,7 @@ int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* i
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool blk = use_blocked(n, B, C, O);
+  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
   if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
     return rc;
   if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
@@ -274,7 +274,7 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long X = bins_of(n);
-  const bool blk = use_blocked(n, B, C, O);
+  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
   if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
     if (B == 0) {
       if (cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
