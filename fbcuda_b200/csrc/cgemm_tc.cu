@@ -126,7 +126,9 @@ __device__ __forceinline__ void ldg32(const float2* p, float4& lo, float4& hi) {
 template <int BN>
 struct TcCfg {
   static constexpr int XB = 4;                             // bins per block
-  static constexpr int NSH = 3;                            // half stages (2 bins each) in the ring
+  static constexpr int NSH = (BN == 64) ? 3 : 2;           // half stages (2 bins each) in the ring
+  static constexpr int MIN_BLOCKS = (BN == 64) ? 1 : 2;    // resident blocks per SM (shared memory, TMEM)
+  static constexpr int TMEM_COLS = (XB * 2 * BN < 32) ? 32 : XB * 2 * BN;
   static constexpr int A_TILE = BM * KS * 4;               // one (bin, part, split) tile of A
   static constexpr int S_TILE = 2 * BN * KS * 4;           // one stacked B tile
   static constexpr int HALF_A = 2 * 4 * A_TILE;
@@ -137,18 +139,19 @@ struct TcCfg {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
+__global__ void __launch_bounds__(kTcThreads, TcCfg<BN>::MIN_BLOCKS) cgemm_tc_kernel(TcArgs g) {
   using Cfg = TcCfg<BN>;
   constexpr int XB = Cfg::XB, NSH = Cfg::NSH, A_TILE = Cfg::A_TILE, S_TILE = Cfg::S_TILE;
   constexpr int HALF_A = Cfg::HALF_A, HSTAGE = Cfg::HSTAGE, A_LBO = Cfg::A_LBO, B_LBO = Cfg::B_LBO, SBO = Cfg::SBO;
-  constexpr int TMEM_COLS = 512;
+  constexpr int TMEM_COLS = Cfg::TMEM_COLS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* stage_mem = smem_raw;
   // [0..NSH) half stage filled (256 producer arrivals), [NSH..2NSH) half stage free (MMA commit), [2NSH] done
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + NSH * HSTAGE);
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * NSH + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int x0 = blockIdx.x * XB, m0 = blockIdx.y * BM, n0 = blockIdx.z * BN;
+  // n tiles are the fastest grid index: blocks that share an A tile run at the same time (L2 reuse)
+  const int n0 = blockIdx.x * BN, x0 = blockIdx.y * XB, m0 = blockIdx.z * BM;
 
   if (tid == 0) {
     for (int i = 0; i < NSH; ++i) {
@@ -179,8 +182,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   const unsigned b_dst = (unsigned)(b_kq * B_LBO + (b_row / 8) * 128 + (b_row % 8) * 16);
   const unsigned s_mask = g.conjB ? 0x80000000u : 0u;  // sign of the imaginary part of B
 
-  float4 ra[4][2], rb[4][2];  // [k in quad][bins 0-1 | bins 2-3] = (re, im, re, im)
-  auto gather = [&](int k0) {
+  // Two register sets: the loads of step s+1 are issued before step s is converted, so a whole
+  // conversion (and the MMAs behind it) hides their latency.
+  struct Regs {
+    float4 a[4][2], b[4][2];  // [k in quad][bins 0-1 | bins 2-3] = (re, im, re, im)
+  };
+  Regs r0;
+  auto gather = [&](Regs& R, int k0) {
+    float4 (&ra)[4][2] = R.a;
+    float4 (&rb)[4][2] = R.b;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int ka = k0 + a_kq * 4 + j, kb = k0 + b_kq * 4 + j;
@@ -199,7 +209,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
   // component c of a float4 (compile-time c)
   auto comp = [](const float4& v, int c) { return c == 0 ? v.x : (c == 1 ? v.y : (c == 2 ? v.z : v.w)); };
   // writes bins 2*pair and 2*pair+1 of the current k-step into half stage `st`
-  auto scatter = [&](unsigned char* st, int pair) {
+  auto scatter = [&](const Regs& R, unsigned char* st, int pair) {
+    const float4 (&ra)[4][2] = R.a;
+    const float4 (&rb)[4][2] = R.b;
 #pragma unroll
     for (int binl = 0; binl < 2; ++binl) {
       const int c0 = binl * 2;
@@ -290,8 +302,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
     __syncwarp();
   } else {
     // ---- producers
-    gather(0);
-    for (int s = 0; s < nsteps; ++s) {
+    auto convert = [&](const Regs& R, int s) {
 #pragma unroll
       for (int pair = 0; pair < 2; ++pair) {
         const int h = 2 * s + pair, buf = h % NSH;
@@ -299,11 +310,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) cgemm_tc_kernel(TcArgs g) {
           // the MMAs that read this half stage NSH half steps ago must have retired
           if (!mbar_wait(smem_u32(bars + NSH + buf), (unsigned)(((h / NSH) - 1) & 1), kErrTcStageWait)) ok = false;
         }
-        scatter(stage_mem + buf * HSTAGE, pair);
-        if (pair == 1 && s + 1 < nsteps) gather((s + 1) * KS);  // next step's loads fly while the MMAs run
-        fence_async_smem();                                     // generic-proxy writes -> visible to the tensor core
+        scatter(R, stage_mem + buf * HSTAGE, pair);
+        if (pair == 1 && s + 1 < nsteps) gather(r0, (s + 1) * KS);  // next step's loads fly behind the MMAs
+        fence_async_smem();  // generic-proxy writes -> visible to the tensor core
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bars + buf)) : "memory");
       }
+    };
+    gather(r0, 0);
+    for (int s = 0; s < nsteps; ++s) {
+      convert(r0, s);  // converts the first bin pair, then the second
     }
     // ---- epilogue: all MMAs done -> tensor memory -> global
     if (ok && !mbar_wait(smem_u32(bars + 2 * NSH), 0, kErrTcFinalWait)) ok = false;
@@ -369,7 +384,7 @@ int launch_tc(const TcArgs& a, cudaStream_t s) {
     cudaFuncSetAttribute(cgemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes<BN>());
     configured[dev] = true;
   }
-  dim3 grid(a.X / TcCfg<BN>::XB, (a.M + BM - 1) / BM, (a.N + BN - 1) / BN);
+  dim3 grid((a.N + BN - 1) / BN, a.X / TcCfg<BN>::XB, (a.M + BM - 1) / BM);
   cgemm_tc_kernel<BN><<<grid, kTcThreads, tc_smem_bytes<BN>(), s>>>(a);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -390,8 +405,7 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
   for (long long v : st)
     if (v % 4 != 0) return false;   // 32-byte loads: every stride a multiple of 4 complex
   if ((reinterpret_cast<uintptr_t>(a) & 31u) || (reinterpret_cast<uintptr_t>(b) & 31u) || !aligned16(d)) return false;
-  const long long grid_y = (M + BM - 1) / BM, grid_z = (N + 15) / 16;
-  if (grid_y > 65535 || grid_z > 65535) return false;
+  if ((M + BM - 1) / BM > 65535 || X / 4 > 65535) return false;
   // small problems are not worth a 128-row tile
   return (long long)M * N * K >= 16 * 16 * 8;
 }
@@ -406,6 +420,7 @@ int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const f
   t.D = reinterpret_cast<float2*>(d), t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
+  // (two resident blocks per SM with BN = 32 were measured slower than one with BN = 64 for wide batches)
   if (N <= 16) return launch_tc<16>(t, s);
   if (N <= 32) return launch_tc<32>(t, s);
   return launch_tc<64>(t, s);

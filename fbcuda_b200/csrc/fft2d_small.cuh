@@ -200,11 +200,22 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+  // try_wait suspends the thread in hardware until the phase completes or a time limit expires
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // true when the phase completed; false (after recording `code`) when the limit ran out
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
-  for (int i = 0; i < (1 << 22); ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if (i > 64) __nanosleep(64);
+  for (int i = 0; i < (1 << 20); ++i) {
+    if (mbar_try(bar, parity)) return true;
   }
   atomicExch(&g_device_error, code);
   return false;
