@@ -90,7 +90,8 @@ def device_status() -> int:
 
 
 def set_contraction_mode(mode: int) -> None:
-    """0: tensor cores (3xTF32) when the operands qualify; 1: FP32 CUDA cores only."""
+    """0: tensor cores (3xTF32, TMA-fed persistent kernel) when the operands qualify; 1: FP32 CUDA cores only;
+    2: tensor cores through the gather kernel only (comparison point)."""
     _check(lib().fbfft_b200_set_contraction_mode(int(mode)))
 
 

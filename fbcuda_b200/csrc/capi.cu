@@ -100,12 +100,13 @@ int fbfft_b200_version(void) { return 100; }
 const char* fbfft_b200_last_error(void) { return g_last_error; }
 
 int fbfft_b200_device_status(void) {
-  const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc();
-  return a != 0 ? a : (b != 0 ? b : c);
+  const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc(), d = read_device_error_tma();
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : d));
 }
 
 int fbfft_b200_set_contraction_mode(int mode) {
-  if (mode != 0 && mode != 1) return fail(kUnsupportedDimension, "set_contraction_mode: 0 (tensor cores) or 1 (FP32 cores)");
+  if (mode < 0 || mode > 2)
+    return fail(kUnsupportedDimension, "set_contraction_mode: 0 (tensor cores), 1 (FP32 cores) or 2 (tensor cores, gather kernel)");
   set_contraction_mode(mode);
   return kSuccess;
 }

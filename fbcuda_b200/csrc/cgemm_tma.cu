@@ -1,0 +1,525 @@
+// Per-frequency-bin complex contraction, persistent warp-specialised version: operands arrive by
+// TMA tensor copies, the 3xTF32 split runs from shared memory, the products run on the
+// 5th-generation tensor cores (tcgen05.mma kind::tf32, accumulators in tensor memory) and the
+// result leaves by TMA tensor stores.  Same math as cgemm_bins.cu / the reference's transposeMM
+// (MM-inl.cuh:188-196):
+//
+//   D[m][n][x] (+)= inv_norm * sum_k opA(A[m][k][x]) * opB(B[n][k][x]),  x = frequency bin.
+//
+// A tile is 128 rows of m, BN columns of n and 4 consecutive bins (32 contiguous bytes of every
+// operand element: one DRAM sector).  Each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// (n tiles fastest, so blocks that run at the same time share the A operand in L2).  Roles:
+//   warp 8        one lane issues, per 4 values of k, one 4-D tensor copy for A ([k][row][32 B] in
+//                 shared memory, 16 KB) and one for B, into a ring of NR raw stages; rows, columns
+//                 and k beyond the tensor are zero-filled by the copy engine;
+//   warps 0-7     read the raw stages, split every fp32 into hi = tf32(x) and lo = x - hi, and write
+//                 K-major operand tiles in the tensor core's no-swizzle layout (8 x 16-byte core
+//                 matrices) per bin: Ar, Ai (hi and lo) and the stack [-s Bi | Br | s Bi] (hi and lo;
+//                 s = -1 when B is conjugated), into a ring of two half stages of two bins each;
+//   warp 9        one lane issues, per bin and k-step of 8, six MMAs of 128 x 2BN x 8 into the bin's
+//                 [Re | Im] accumulator:  Ar_h x S_h, Ai_h x S'_h, Ar_h x S_l, Ai_h x S'_l, Ar_l x S_h,
+//                 Ai_l x S'_h with S = rows BN..3BN of the stack = [Br | s Bi] and S' = rows 0..2BN =
+//                 [-s Bi | Br] (the Ai products negated when A is conjugated); tcgen05.commit frees
+//                 the half stage and, after the last k-step, hands the accumulators to the epilogue;
+//   warps 10-13   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
+//                 interleave the 4 bins' re/im into 32 bytes per (m, n) in a 4 KB staging buffer and
+//                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
+// Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
+// block still releases its tensor memory before returning.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
+
+#include "fft2d_small.cuh"  // mbarrier helpers, fence_async_smem
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+constexpr int kConvThreads = 256;  // warps 0-7
+constexpr int kWarpTma = 8, kWarpMma = 9, kWarpEpi = 10;
+constexpr int kThreads = 14 * 32;
+constexpr int BM = 128, XB = 4, KQ = 4, KS = 8;
+enum : int { kErrRawFull = 211, kErrRawFree = 212, kErrCvFull = 213, kErrCvFree = 214, kErrAccFull = 215, kErrAccFree = 216 };
+
+template <int BN>
+struct Cfg {
+  static constexpr int NR = 4;                       // raw stages (4 values of k each)
+  static constexpr int NH = 2;                       // converted half stages (2 bins x 8 k each)
+  static constexpr int NACC = (BN == 64) ? 1 : 2;    // accumulator sets in tensor memory
+  static constexpr int ACC_COLS = XB * 2 * BN;
+  static constexpr int TMEM_COLS = NACC * ACC_COLS;  // 512, 512, 256
+  static constexpr int A_RAW = KQ * BM * 32, B_RAW = KQ * BN * 32, RAW = A_RAW + B_RAW;
+  static constexpr int A_TILE = BM * KS * 4;         // one (bin, part, split) tile of A
+  static constexpr int B_TILE = 3 * BN * KS * 4;     // one (bin, split) stack of B
+  static constexpr int HALF_A = 2 * 2 * 2 * A_TILE, HALF_B = 2 * 2 * B_TILE, HSTAGE = HALF_A + HALF_B;
+  static constexpr int EPI_WARP = 32 * 4 * 32;       // 32 rows x 4 columns x 32 bytes
+  static constexpr int A_LBO = (BM / 8) * 128, B_LBO = (3 * BN / 8) * 128, SBO = 128;
+  static constexpr int OFF_CONV = NR * RAW, OFF_EPI = OFF_CONV + NH * HSTAGE, OFF_BAR = OFF_EPI + 4 * EPI_WARP;
+  static constexpr int SMEM = OFF_BAR + 256;
+};
+
+__device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo_bytes, unsigned sbo_bytes) {
+  // K-major, no swizzle: 8-row x 16-byte core matrices; LBO between the two 16-byte k-chunks of
+  // an 8-wide k-step, SBO between 8-row groups; descriptor version 1 (bits 46-47)
+  return (unsigned long long)((addr >> 4) & 0x3FFF) | ((unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         ((unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ULL << 46);
+}
+__device__ __forceinline__ unsigned instr_desc(int n, bool neg_a) {
+  // D fp32, A and B tf32, both K-major, M = 128
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((neg_a ? 1u : 0u) << 13) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc,
+                                         unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld4(unsigned taddr, float (&v)[4]) {
+  unsigned r0, r1, r2, r3;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(taddr));
+  v[0] = __uint_as_float(r0), v[1] = __uint_as_float(r1), v[2] = __uint_as_float(r2), v[3] = __uint_as_float(r3);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load4(unsigned dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store4(const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm), "r"(c0),
+               "r"(c1), "r"(c2), "r"(c3), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add4(const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned src) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(src)
+               : "memory");
+}
+// Bounded wait: gives up after two seconds, or as soon as another role of the block has given up
+// (abort word in shared memory), recording `code`
+__device__ __forceinline__ bool wait_bar(unsigned bar, unsigned parity, int code, volatile int* abort_word) {
+  if (mbar_try(bar, parity)) return true;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    if (mbar_try(bar, parity)) return true;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (*abort_word != 0 || t1 - t0 > 2000000000ULL) break;
+  }
+  *abort_word = 1;
+  atomicExch(&g_device_error, code);
+  return false;
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// hi = the operand rounded to tf32 (exactly what the tensor core then reads); lo = the remainder,
+// of which the tensor core keeps the top 10 bits
+__device__ __forceinline__ void split4(const float (&v)[4], float4* hi, float4* lo) {
+  float h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    unsigned r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v[i]));
+    h[i] = __uint_as_float(r);
+  }
+  *hi = make_float4(h[0], h[1], h[2], h[3]);
+  *lo = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
+}
+__device__ __forceinline__ float4 flip4(float4 v, unsigned mask) {
+  return make_float4(__uint_as_float(__float_as_uint(v.x) ^ mask), __uint_as_float(__float_as_uint(v.y) ^ mask),
+                     __uint_as_float(__float_as_uint(v.z) ^ mask), __uint_as_float(__float_as_uint(v.w) ^ mask));
+}
+
+struct TmaArgs {
+  int M, N, K, X;
+  int a_blocked, b_blocked, d_blocked;  // bin-blocked operand: coordinates (2*(x%16), ., ., x/16), else (2x, ., ., 0)
+  float inv_norm;
+  int conjA, conjB, accumulate;
+  int n_tiles, m_tiles, total_tiles;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_b,
+                                                                  const __grid_constant__ CUtensorMap map_d, TmaArgs g) {
+  using C = Cfg<BN>;
+  constexpr int NR = C::NR, NH = C::NH, NACC = C::NACC;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* raw_mem = smem_raw;
+  unsigned char* conv_mem = smem_raw + C::OFF_CONV;
+  unsigned char* epi_mem = smem_raw + C::OFF_EPI;
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem_raw + C::OFF_BAR);
+  // barrier indices
+  constexpr int RAW_FULL = 0, RAW_FREE = NR, CV_FULL = 2 * NR, CV_FREE = 2 * NR + NH, ACC_FULL = 2 * NR + 2 * NH,
+                ACC_FREE = ACC_FULL + 2, NBARS = ACC_FREE + 2;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + NBARS);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  if (tid == 0) {
+    *abort_word = 0;
+    for (int i = 0; i < NR; ++i) {
+      mbar_init(bar(RAW_FULL + i), 1);
+      mbar_init(bar(RAW_FREE + i), kConvThreads / 32);
+    }
+    for (int i = 0; i < NH; ++i) {
+      mbar_init(bar(CV_FULL + i), kConvThreads / 32);
+      mbar_init(bar(CV_FREE + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(ACC_FULL + i), 1);
+      mbar_init(bar(ACC_FREE + i), 4);
+    }
+    fence_async_smem();
+  }
+  if (warp == kWarpMma) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = *tmem_slot;
+
+  const int nsteps = (g.K + KS - 1) / KS;
+  // tile t -> (n tile, m tile, bin quad); the loop bounds are the same in every role
+  auto tile_coords = [&](int t, int* n0, int* m0, int* x0) {
+    *n0 = (t % g.n_tiles) * BN;
+    *m0 = ((t / g.n_tiles) % g.m_tiles) * BM;
+    *x0 = (t / (g.n_tiles * g.m_tiles)) * XB;
+  };
+
+  if (warp == kWarpTma) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      unsigned rs = 0;  // raw stages issued so far
+      bool ok = true;
+      for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
+        int n0, m0, x0;
+        tile_coords(t, &n0, &m0, &x0);
+        const int ax = g.a_blocked ? 2 * (x0 & 15) : 2 * x0, ab = g.a_blocked ? (x0 >> 4) : 0;
+        const int bx = g.b_blocked ? 2 * (x0 & 15) : 2 * x0, bb = g.b_blocked ? (x0 >> 4) : 0;
+        for (int q = 0; q < 2 * nsteps; ++q, ++rs) {
+          const unsigned st = rs % NR;
+          if (rs >= NR && !wait_bar(bar(RAW_FREE + st), ((rs / NR) - 1) & 1, kErrRawFree, abort_word)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(bar(RAW_FULL + st), C::RAW);
+          const unsigned dst = smem_u32(raw_mem + st * C::RAW);
+          tma_load4(dst, &map_a, ax, m0, q * KQ, ab, bar(RAW_FULL + st));
+          tma_load4(dst + C::A_RAW, &map_b, bx, n0, q * KQ, bb, bar(RAW_FULL + st));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const unsigned id_r = instr_desc(2 * BN, false);
+      const unsigned id_i = instr_desc(2 * BN, g.conjA != 0);  // conj(A): the Ai products change sign
+      unsigned h = 0, it = 0;  // half stages consumed, tiles done
+      bool ok = true;
+      for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++it) {
+        const unsigned acc = it % NACC;
+        if (it >= NACC && !wait_bar(bar(ACC_FREE + acc), ((it / NACC) - 1) & 1, kErrAccFree, abort_word)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int s = 0; s < nsteps && ok; ++s) {
+          for (int pair = 0; pair < 2; ++pair, ++h) {
+            const unsigned buf = h % NH;
+            if (!wait_bar(bar(CV_FULL + buf), (h / NH) & 1, kErrCvFull, abort_word)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const unsigned base = smem_u32(conv_mem + buf * C::HSTAGE);
+            const unsigned long long da0 = smem_desc(base, C::A_LBO, C::SBO);
+            const unsigned long long db0 = smem_desc(base + C::HALF_A, C::B_LBO, C::SBO);
+            const unsigned first = (s > 0) ? 1u : 0u;  // the first product into an accumulator overwrites it
+#pragma unroll
+            for (int binl = 0; binl < 2; ++binl) {
+              const unsigned d = tmem_base + acc * C::ACC_COLS + (pair * 2 + binl) * (2 * BN);
+              const unsigned long long a_rh = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 0) * C::A_TILE) >> 4);
+              const unsigned long long a_rl = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 1) * C::A_TILE) >> 4);
+              const unsigned long long a_ih = da0 + (unsigned long long)((((binl * 2 + 1) * 2 + 0) * C::A_TILE) >> 4);
+              const unsigned long long a_il = da0 + (unsigned long long)((((binl * 2 + 1) * 2 + 1) * C::A_TILE) >> 4);
+              const unsigned long long t_h = db0 + (unsigned long long)(((binl * 2 + 0) * C::B_TILE) >> 4);  // S'_hi
+              const unsigned long long t_l = db0 + (unsigned long long)(((binl * 2 + 1) * C::B_TILE) >> 4);  // S'_lo
+              const unsigned long long s_h = t_h + (unsigned long long)(((BN / 8) * 128) >> 4);              // S_hi
+              const unsigned long long s_l = t_l + (unsigned long long)(((BN / 8) * 128) >> 4);              // S_lo
+              mma_tf32(d, a_rh, s_h, id_r, first);
+              mma_tf32(d, a_ih, t_h, id_i, 1u);
+              mma_tf32(d, a_rh, s_l, id_r, 1u);
+              mma_tf32(d, a_ih, t_l, id_i, 1u);
+              mma_tf32(d, a_rl, s_h, id_r, 1u);
+              mma_tf32(d, a_il, t_h, id_i, 1u);
+            }
+            mma_commit(bar(CV_FREE + buf));  // frees the half stage when these MMAs retire
+          }
+        }
+        if (ok) mma_commit(bar(ACC_FULL + acc));  // all products of the tile retired: epilogue may read
+      }
+    }
+    __syncwarp();
+  } else if (warp >= kWarpEpi) {
+    // ------------------------------------------------------------------ epilogue
+    const int lq = warp & 3;  // the quarter of the tensor-memory lanes this warp may read
+    unsigned char* stag = epi_mem + (warp - kWarpEpi) * C::EPI_WARP;
+    const unsigned stag_u32 = smem_u32(stag);
+    unsigned it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x, ++it) {
+      int n0, m0, x0;
+      tile_coords(t, &n0, &m0, &x0);
+      const unsigned acc = it % NACC;
+      if (!wait_bar(bar(ACC_FULL + acc), (it / NACC) & 1, kErrAccFull, abort_word)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int dx = g.d_blocked ? 2 * (x0 & 15) : 2 * x0, db = g.d_blocked ? (x0 >> 4) : 0;
+      const int mrow = m0 + lq * 32;
+      if (mrow < g.M) {
+#pragma unroll 1
+        for (int nc = 0; nc < BN && n0 + nc < g.N; nc += 4) {
+          float v[XB][2][4];
+#pragma unroll
+          for (int bin = 0; bin < XB; ++bin) {
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              tmem_ld4(tmem_base + ((unsigned)(lq * 32) << 16) + acc * C::ACC_COLS + bin * (2 * BN) + part * BN + nc,
+                       v[bin][part]);
+            }
+          }
+          tmem_ld_wait();
+          // the previous store of this warp must have finished reading the staging buffer
+          if (lane == 0) bulk_wait_read();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float4* dst = reinterpret_cast<float4*>(stag + (j * 32 + lane) * 32);
+            dst[0] = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
+                                 v[1][1][j] * g.inv_norm);
+            dst[1] = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
+                                 v[3][1][j] * g.inv_norm);
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (g.accumulate) {
+              tma_reduce_add4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
+            } else {
+              tma_store4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
+            }
+            bulk_commit();
+          }
+        }
+      }
+      // this warp's reads of the accumulators are complete: the next tile may overwrite them
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(ACC_FREE + acc));
+    }
+    if (lane == 0) bulk_wait_all();
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ converters (warps 0-7)
+    const int a_row = tid % BM, a_kq = tid / BM;            // A: 128 rows x 2 k-quads
+    const int bt = tid % 128, b_sel = tid / 128;            // B: (row, k-quad) units, one bin of the pair each
+    const bool has_b = bt < 2 * BN;
+    const int b_row = bt % BN, b_kq = (bt / BN) & 1;
+    const unsigned a_dst = (unsigned)(a_kq * C::A_LBO + (a_row / 8) * 128 + (a_row % 8) * 16);
+    const unsigned b_dst = (unsigned)(b_kq * C::B_LBO + (b_row / 8) * 128 + (b_row % 8) * 16);
+    const unsigned s_mask = g.conjB ? 0x80000000u : 0u;  // sign of the imaginary part of B
+    constexpr int G = (BN / 8) * 128;                    // bytes between the blocks of a B stack
+    unsigned rs = 0, h = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
+      for (int s = 0; s < nsteps && ok; ++s, rs += 2) {
+        const unsigned st0 = rs % NR, st1 = (rs + 1) % NR;
+        if (!wait_bar(bar(RAW_FULL + st0), (rs / NR) & 1, kErrRawFull, abort_word) ||
+            !wait_bar(bar(RAW_FULL + st1), ((rs + 1) / NR) & 1, kErrRawFull, abort_word)) {
+          ok = false;
+          break;
+        }
+        const unsigned char* ra = raw_mem + (a_kq ? st1 : st0) * C::RAW;
+        const unsigned char* rb = raw_mem + (b_kq ? st1 : st0) * C::RAW + C::A_RAW;
+#pragma unroll
+        for (int pair = 0; pair < 2; ++pair, ++h) {
+          const unsigned buf = h % NH;
+          // the MMAs that read this half stage NH half steps ago must have retired
+          if (h >= NH && !wait_bar(bar(CV_FREE + buf), ((h / NH) - 1) & 1, kErrCvFree, abort_word)) {
+            ok = false;
+            break;
+          }
+          unsigned char* cst = conv_mem + buf * C::HSTAGE;
+          {
+            float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + (j * BM + a_row) * 32 + pair * 16);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // c = binl*2 + part
+              const float w[4] = {c == 0 ? v[0].x : c == 1 ? v[0].y : c == 2 ? v[0].z : v[0].w,
+                                  c == 0 ? v[1].x : c == 1 ? v[1].y : c == 2 ? v[1].z : v[1].w,
+                                  c == 0 ? v[2].x : c == 1 ? v[2].y : c == 2 ? v[2].z : v[2].w,
+                                  c == 0 ? v[3].x : c == 1 ? v[3].y : c == 2 ? v[3].z : v[3].w};
+              float4 hi, lo;
+              split4(w, &hi, &lo);
+              unsigned char* tdst = cst + (c * 2) * C::A_TILE + a_dst;
+              *reinterpret_cast<float4*>(tdst) = hi;
+              *reinterpret_cast<float4*>(tdst + C::A_TILE) = lo;
+            }
+          }
+          if (has_b) {
+            float2 v[4];  // (re, im) of bin 2*pair + b_sel
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              v[j] = *reinterpret_cast<const float2*>(rb + (j * BN + b_row) * 32 + (pair * 2 + b_sel) * 8);
+            const float wr[4] = {v[0].x, v[1].x, v[2].x, v[3].x}, wi[4] = {v[0].y, v[1].y, v[2].y, v[3].y};
+            float4 brh, brl, bih, bil;
+            split4(wr, &brh, &brl);
+            split4(wi, &bih, &bil);
+            bih = flip4(bih, s_mask);  // s Bi
+            bil = flip4(bil, s_mask);
+            unsigned char* tdst = cst + C::HALF_A + (b_sel * 2) * C::B_TILE + b_dst;
+            *reinterpret_cast<float4*>(tdst) = flip4(bih, 0x80000000u);  // hi stack: [-s Bi | Br | s Bi]
+            *reinterpret_cast<float4*>(tdst + G) = brh;
+            *reinterpret_cast<float4*>(tdst + 2 * G) = bih;
+            *reinterpret_cast<float4*>(tdst + C::B_TILE) = flip4(bil, 0x80000000u);  // lo stack
+            *reinterpret_cast<float4*>(tdst + C::B_TILE + G) = brl;
+            *reinterpret_cast<float4*>(tdst + C::B_TILE + 2 * G) = bil;
+          }
+          fence_async_smem();  // generic-proxy writes -> visible to the tensor core
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(CV_FULL + buf));
+        }
+        // both raw stages of this k-step are consumed by this warp
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(RAW_FREE + st0));
+          mbar_arrive(bar(RAW_FREE + st1));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kWarpMma) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS));
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 4-D view of an operand whose bin x of element (row, k) sits at p + (x/16)*bs + x%16 + row*rs + k*ks
+// complex elements: (floats of the bins, rows, k, 16-bin blocks).  bs == 16 is the natural
+// bins-innermost layout, one "block" holding all X bins.
+bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long long bs, int rows, int kcount, int X,
+              int box_rows, int box_k) {
+  EncodeTiledFn enc = encoder();
+  if (!enc) return false;
+  const bool blocked = bs != 16;
+  const cuuint64_t dims[4] = {(cuuint64_t)(blocked ? 32 : 2 * X), (cuuint64_t)rows, (cuuint64_t)kcount,
+                              (cuuint64_t)(blocked ? X / 16 : 1)};
+  const cuuint64_t strides[3] = {(cuuint64_t)rs * 8, (cuuint64_t)ks * 8, (cuuint64_t)(blocked ? bs * 8 : (long long)X * 8)};
+  const cuuint32_t box[4] = {8, (cuuint32_t)box_rows, (cuuint32_t)box_k, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(p), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN>
+int launch_tma(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(cgemm_tma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+    configured[dev] = true;
+  }
+  a.n_tiles = (a.N + BN - 1) / BN;
+  a.m_tiles = (a.M + BM - 1) / BM;
+  const long long total = (long long)a.n_tiles * a.m_tiles * (a.X / XB);
+  a.total_tiles = (int)total;
+  const int grid = total < sm_count() ? (int)total : sm_count();
+  cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(ma, mb, md, a);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+}  // namespace
+
+bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,
+                         long long b_ks, long long b_bs, const float* d, long long d_ms, long long d_ns, long long d_bs,
+                         int M, int N, int K, int X) {
+  if (X % 4 != 0 || M < 1 || N < 1 || K < 1) return false;
+  if ((a_bs != 16 || b_bs != 16 || d_bs != 16) && X % 16 != 0) return false;
+  // tensor copies: 16-byte aligned bases and strides (an even number of complex elements)
+  const long long st[9] = {a_rs, a_ks, a_bs, b_rs, b_ks, b_bs, d_ms, d_ns, d_bs};
+  for (long long v : st)
+    if (v <= 0 || v % 2 != 0 || v * 8 >= (1LL << 40)) return false;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(d)) return false;
+  if ((long long)((N + 15) / 16) * ((M + BM - 1) / BM) * (X / 4) > 0x7fffffffLL) return false;
+  return encoder() != nullptr;
+}
+
+int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
+              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
+              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs) {
+  const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
+  alignas(64) CUtensorMap ma, mb, md;
+  if (!make_map(&ma, a, a_rs, a_ks, a_bs, M, K, X, BM, KQ) || !make_map(&mb, b, b_rs, b_ks, b_bs, N, K, X, BN, KQ) ||
+      !make_map(&md, d, d_ms, d_ns, d_bs, M, N, X, 32, 4)) {
+    return -1;  // the caller falls back to the gather kernel
+  }
+  TmaArgs t;
+  t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
+  t.a_blocked = a_bs != 16, t.b_blocked = b_bs != 16, t.d_blocked = d_bs != 16;
+  t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
+  t.n_tiles = t.m_tiles = t.total_tiles = 0;
+  if (BN == 16) return launch_tma<16>(ma, mb, md, t, s);
+  if (BN == 32) return launch_tma<32>(ma, mb, md, t, s);
+  return launch_tma<64>(ma, mb, md, t, s);
+}
+
+int read_device_error_tma() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace fbfft_b200

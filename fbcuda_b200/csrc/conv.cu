@@ -99,7 +99,7 @@ int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, bool block
 // three passes of a layer take the same decision (it depends on B*C*O and on the process-wide
 // contraction mode only), so spectra reused across passes agree.
 bool use_blocked(int n, long long B, long long C, long long O) {
-  return n >= 16 && contraction_mode() == 0 && B * C * O >= 16 * 16 * 8;
+  return n >= 16 && contraction_mode() != 1 && B * C * O >= 16 * 16 * 8;
 }
 
 // D[m][n] (+)= inv_norm * sum_k opA(A[m][k]) opB(B[n][k]) per bin, where element (m, k) of A is
