@@ -26,6 +26,7 @@
 //                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
 // Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
 // block still releases its tensor memory before returning.
+#include <cstdlib>
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
 
 #include "fft2d_small.cuh"  // mbarrier helpers, fence_async_smem
@@ -36,8 +37,9 @@ namespace fbfft_b200 {
 namespace {
 
 constexpr int kConvThreads = 256;  // warps 0-7
-constexpr int kWarpTma = 8, kWarpMma = 9, kWarpEpi = 10;
-constexpr int kThreads = 14 * 32;
+constexpr int kProdThreads = 128;  // warps 8-11
+constexpr int kWarpProd = 8, kWarpMma = 12, kWarpEpi = 13;
+constexpr int kThreads = 17 * 32;
 constexpr int BM = 128, XB = 4, KQ = 4, KS = 8;
 enum : int { kErrRawFull = 211, kErrRawFree = 212, kErrCvFull = 213, kErrCvFree = 214, kErrAccFull = 215, kErrAccFree = 216 };
 
@@ -93,11 +95,8 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tma_load4(unsigned dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
-      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, unsigned src_bytes) {
+  asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 __device__ __forceinline__ void tma_store4(const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned src) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm), "r"(c0),
@@ -145,17 +144,22 @@ __device__ __forceinline__ float4 flip4(float4 v, unsigned mask) {
 }
 
 struct TmaArgs {
+  // bin x of element (m, k) of A sits at A + (x/16)*a_bs + x%16 + m*a_rs + k*a_ks (complex elements);
+  // a_bs = 16 is the natural bins-innermost layout, a_bs = planes*16 the bin-blocked one
+  const float2* A;
+  long long a_rs, a_ks, a_bs;
+  const float2* B;
+  long long b_rs, b_ks, b_bs;  // B[n][k][x]
   int M, N, K, X;
-  int a_blocked, b_blocked, d_blocked;  // bin-blocked operand: coordinates (2*(x%16), ., ., x/16), else (2x, ., ., 0)
+  int d_blocked;  // bin-blocked result: store coordinates (2*(x%16), m, n, x/16), else (2x, m, n, 0)
   float inv_norm;
   int conjA, conjB, accumulate;
   int n_tiles, m_tiles, total_tiles;
+  int debug;  // TEMP ablation bits: 1 no conversion, 2 no MMA, 4 no stores, 8 no loads
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                  const __grid_constant__ CUtensorMap map_b,
-                                                                  const __grid_constant__ CUtensorMap map_d, TmaArgs g) {
+__global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_d, TmaArgs g) {
   using C = Cfg<BN>;
   constexpr int NR = C::NR, NH = C::NH, NACC = C::NACC;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
   if (tid == 0) {
     *abort_word = 0;
     for (int i = 0; i < NR; ++i) {
-      mbar_init(bar(RAW_FULL + i), 1);
+      mbar_init(bar(RAW_FULL + i), kProdThreads);
       mbar_init(bar(RAW_FREE + i), kConvThreads / 32);
     }
     for (int i = 0; i < NH; ++i) {
@@ -199,36 +203,63 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
 
   const int nsteps = (g.K + KS - 1) / KS;
   // tile t -> (n tile, m tile, bin quad); the loop bounds are the same in every role
+  // (the 4 bin quads of a 128-byte line of the operands are the fastest index when the bin count
+  // allows it, then n tiles: blocks that run at the same time share operand lines in L2)
+  const bool quad_fast = (g.X & 15) == 0;
   auto tile_coords = [&](int t, int* n0, int* m0, int* x0) {
-    *n0 = (t % g.n_tiles) * BN;
-    *m0 = ((t / g.n_tiles) % g.m_tiles) * BM;
-    *x0 = (t / (g.n_tiles * g.m_tiles)) * XB;
+    const int qf = quad_fast ? (t & 3) : 0, u = quad_fast ? (t >> 2) : t;
+    *n0 = (u % g.n_tiles) * BN;
+    *m0 = ((u / g.n_tiles) % g.m_tiles) * BM;
+    const int xr = u / (g.n_tiles * g.m_tiles);
+    *x0 = (quad_fast ? xr * 4 + qf : xr) * XB;
   };
 
-  if (warp == kWarpTma) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      unsigned rs = 0;  // raw stages issued so far
-      bool ok = true;
-      for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
-        int n0, m0, x0;
-        tile_coords(t, &n0, &m0, &x0);
-        const int ax = g.a_blocked ? 2 * (x0 & 15) : 2 * x0, ab = g.a_blocked ? (x0 >> 4) : 0;
-        const int bx = g.b_blocked ? 2 * (x0 & 15) : 2 * x0, bb = g.b_blocked ? (x0 >> 4) : 0;
-        for (int q = 0; q < 2 * nsteps; ++q, ++rs) {
-          const unsigned st = rs % NR;
-          if (rs >= NR && !wait_bar(bar(RAW_FREE + st), ((rs / NR) - 1) & 1, kErrRawFree, abort_word)) {
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(bar(RAW_FULL + st), C::RAW);
-          const unsigned dst = smem_u32(raw_mem + st * C::RAW);
-          tma_load4(dst, &map_a, ax, m0, q * KQ, ab, bar(RAW_FULL + st));
-          tma_load4(dst + C::A_RAW, &map_b, bx, n0, q * KQ, bb, bar(RAW_FULL + st));
+  if (warp >= kWarpProd && warp < kWarpMma) {
+    // ------------------------------------------------------------------ operand loads
+    // Two lanes per 32-byte segment (one row, one k, the tile's 4 bins); every thread issues its
+    // share of a raw stage as 16-byte asynchronous copies (zero-filled outside the tensor) and lets
+    // the stage's barrier count their completion.
+    const int p = tid - kWarpProd * 32, half = p & 1, sp = p >> 1;  // sp in 0..63
+    unsigned rs = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
+      int n0, m0, x0;
+      tile_coords(t, &n0, &m0, &x0);
+      const float2* pa = g.A + (long long)(x0 >> 4) * g.a_bs + (x0 & 15) + 2 * half + (long long)(m0 + sp) * g.a_rs;
+      const bool a_ok0 = m0 + sp < g.M, a_ok1 = m0 + sp + 64 < g.M;
+      const long long a_up = 64 * g.a_rs;
+      for (int q = 0; q < 2 * nsteps; ++q, ++rs) {
+        const unsigned st = rs % NR;
+        if (rs >= NR && !wait_bar(bar(RAW_FREE + st), ((rs / NR) - 1) & 1, kErrRawFree, abort_word)) {
+          ok = false;
+          break;
         }
+        if (g.debug & 8) {
+          mbar_arrive(bar(RAW_FULL + st));
+          continue;
+        }
+        const unsigned dst = smem_u32(raw_mem + st * C::RAW) + half * 16;
+#pragma unroll
+        for (int j = 0; j < KQ; ++j) {
+          const int k = q * KQ + j;
+          const bool kv = k < g.K;
+          const float2* src = pa + (long long)(kv ? k : 0) * g.a_ks;
+          cp_async16(dst + (j * BM + sp) * 32, (kv && a_ok0) ? src : g.A, (kv && a_ok0) ? 16u : 0u);
+          cp_async16(dst + (j * BM + sp + 64) * 32, (kv && a_ok1) ? src + a_up : g.A, (kv && a_ok1) ? 16u : 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < (KQ * BN) / 64; ++i) {
+          const int seg = i * 64 + sp, j = seg / BN, row = seg % BN;
+          const int k = q * KQ + j;
+          const bool v = k < g.K && n0 + row < g.N;
+          const float2* src = g.B + (long long)(x0 >> 4) * g.b_bs + (x0 & 15) + 2 * half + (long long)(n0 + row) * g.b_rs +
+                              (long long)k * g.b_ks;
+          cp_async16(dst + C::A_RAW + (j * BN + row) * 32, v ? src : g.B, v ? 16u : 0u);
+        }
+        // the barrier receives this thread's arrival once all its copies above have landed
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(RAW_FULL + st)) : "memory");
       }
     }
-    __syncwarp();
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -257,6 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             const unsigned first = (s > 0) ? 1u : 0u;  // the first product into an accumulator overwrites it
 #pragma unroll
             for (int binl = 0; binl < 2; ++binl) {
+              if (g.debug & 2) break;
               const unsigned d = tmem_base + acc * C::ACC_COLS + (pair * 2 + binl) * (2 * BN);
               const unsigned long long a_rh = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 0) * C::A_TILE) >> 4);
               const unsigned long long a_rl = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 1) * C::A_TILE) >> 4);
@@ -324,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           }
           fence_async_smem();
           __syncwarp();
-          if (lane == 0) {
+          if (lane == 0 && !(g.debug & 4)) {
             if (g.accumulate) {
               tma_reduce_add4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
             } else {
@@ -372,7 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             break;
           }
           unsigned char* cst = conv_mem + buf * C::HSTAGE;
-          {
+          if (!(g.debug & 1)) {
             float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + (j * BM + a_row) * 32 + pair * 16);
@@ -389,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
               *reinterpret_cast<float4*>(tdst + C::A_TILE) = lo;
             }
           }
-          if (has_b) {
+          if (has_b && !(g.debug & 1)) {
             float2 v[4];  // (re, im) of bin 2*pair + b_sel
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -464,7 +496,7 @@ bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long l
 }
 
 template <int BN>
-int launch_tma(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
+int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -477,7 +509,7 @@ int launch_tma(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& 
   const long long total = (long long)a.n_tiles * a.m_tiles * (a.X / XB);
   a.total_tiles = (int)total;
   const int grid = total < sm_count() ? (int)total : sm_count();
-  cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(ma, mb, md, a);
+  cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
@@ -501,19 +533,21 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
               bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs) {
   const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
-  alignas(64) CUtensorMap ma, mb, md;
-  if (!make_map(&ma, a, a_rs, a_ks, a_bs, M, K, X, BM, KQ) || !make_map(&mb, b, b_rs, b_ks, b_bs, N, K, X, BN, KQ) ||
-      !make_map(&md, d, d_ms, d_ns, d_bs, M, N, X, 32, 4)) {
+  alignas(64) CUtensorMap md;
+  if (!make_map(&md, d, d_ms, d_ns, d_bs, M, N, X, 32, 4)) {
     return -1;  // the caller falls back to the gather kernel
   }
   TmaArgs t;
+  t.A = reinterpret_cast<const float2*>(a), t.a_rs = a_rs, t.a_ks = a_ks, t.a_bs = a_bs;
+  t.B = reinterpret_cast<const float2*>(b), t.b_rs = b_rs, t.b_ks = b_ks, t.b_bs = b_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
-  t.a_blocked = a_bs != 16, t.b_blocked = b_bs != 16, t.d_blocked = d_bs != 16;
+  t.d_blocked = d_bs != 16;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
-  if (BN == 16) return launch_tma<16>(ma, mb, md, t, s);
-  if (BN == 32) return launch_tma<32>(ma, mb, md, t, s);
-  return launch_tma<64>(ma, mb, md, t, s);
+  t.debug = getenv("FBFFT_TMA_DEBUG") ? atoi(getenv("FBFFT_TMA_DEBUG")) : 0;
+  if (BN == 16) return launch_tma<16>(md, t, s);
+  if (BN == 32) return launch_tma<32>(md, t, s);
+  return launch_tma<64>(md, t, s);
 }
 
 int read_device_error_tma() {
