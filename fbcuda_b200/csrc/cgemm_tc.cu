@@ -87,6 +87,7 @@ struct TcArgs {
   int M, N, K, X;
   float inv_norm;
   int conjA, conjB, accumulate;
+  int a_qb, b_qb;  // bins per block of A and B (16, or 4 for the quad-blocked forward spectra)
 };
 
 // hi = the operand rounded to tf32 (10-bit mantissa, low 13 bits zero: exactly what the
@@ -176,8 +177,8 @@ __global__ void __launch_bounds__(kTcThreads, TcCfg<BN>::MIN_BLOCKS) cgemm_tc_ke
   const bool has_b = tid < 2 * BN;
   const int b_row = tid % BN, b_kq = tid / BN;
   const bool a_row_ok = m0 + a_row < g.M, b_row_ok = has_b && (n0 + b_row < g.N);
-  const float2* a_src = g.A + (long long)(m0 + a_row) * g.a_rs + (long long)(x0 >> 4) * g.a_bs + (x0 & 15);
-  const float2* b_src = g.B + (long long)(n0 + b_row) * g.b_rs + (long long)(x0 >> 4) * g.b_bs + (x0 & 15);
+  const float2* a_src = g.A + (long long)(m0 + a_row) * g.a_rs + (long long)(x0 / g.a_qb) * g.a_bs + (x0 % g.a_qb);
+  const float2* b_src = g.B + (long long)(n0 + b_row) * g.b_rs + (long long)(x0 / g.b_qb) * g.b_bs + (x0 % g.b_qb);
   const unsigned a_dst = (unsigned)(a_kq * A_LBO + (a_row / 8) * 128 + (a_row % 8) * 16);
   const unsigned b_dst = (unsigned)(b_kq * B_LBO + (b_row / 8) * 128 + (b_row % 8) * 16);
   const unsigned s_mask = g.conjB ? 0x80000000u : 0u;  // sign of the imaginary part of B
@@ -413,12 +414,12 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
 // D[m][n][x] (+)= inv_norm * sum_k opA(A[m][k][x]) opB(B[n][k][x]); strides in complex elements
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-             bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs) {
+             bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb) {
   // first choice: the persistent TMA-fed kernel (cgemm_tma.cu); this file's gather kernel remains
   // for drivers without the tensor-map encoder and as the comparison point (mode 2)
   if (g_mode == 0 && cgemm_tma_supported(a, a_rs, a_ks, a_bs, b, b_rs, b_ks, b_bs, d, d_ms, d_ns, d_bs, M, N, K, X)) {
     const int rc = cgemm_tma(a, a_rs, a_ks, conjA, b, b_rs, b_ks, conjB, d, d_ms, d_ns, M, N, K, X, inv_norm, accumulate,
-                             s, a_bs, b_bs, d_bs);
+                             s, a_bs, b_bs, d_bs, a_qb, b_qb);
     if (rc >= 0) return rc;
   }
   TcArgs t;
@@ -427,6 +428,7 @@ int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const f
   t.D = reinterpret_cast<float2*>(d), t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
+  t.a_qb = a_qb, t.b_qb = b_qb;
   // (two resident blocks per SM with BN = 32 were measured slower than one with BN = 64 for wide batches)
   if (N <= 16) return launch_tc<16>(t, s);
   if (N <= 32) return launch_tc<32>(t, s);

@@ -45,12 +45,19 @@ enum : int { kErrRawFull = 211, kErrRawFree = 212, kErrCvFull = 213, kErrCvFree 
 
 template <int BN>
 struct Cfg {
-  static constexpr int NR = 4;                       // raw stages (4 values of k each)
-  static constexpr int NH = 2;                       // converted half stages (2 bins x 8 k each)
+#ifndef FBFFT_NR
+#define FBFFT_NR 4
+#define FBFFT_NH 2
+#endif
+  static constexpr int NR = FBFFT_NR;                // raw stages (4 values of k each)
+  static constexpr int NH = FBFFT_NH;                     // converted half stages (2 bins x 8 k each)
   static constexpr int NACC = (BN == 64) ? 1 : 2;    // accumulator sets in tensor memory
   static constexpr int ACC_COLS = XB * 2 * BN;
   static constexpr int TMEM_COLS = NACC * ACC_COLS;  // 512, 512, 256
-  static constexpr int A_RAW = KQ * BM * 32, B_RAW = KQ * BN * 32, RAW = A_RAW + B_RAW;
+  // raw stage: [k][row][32 bytes] per operand, the k slices 32 bytes further apart than their size so that
+  // copies issued k-fastest do not all land in the same banks
+  static constexpr int A_KSTRIDE = BM * 32 + 32, B_KSTRIDE = BN * 32 + 32;
+  static constexpr int A_RAW = KQ * A_KSTRIDE, B_RAW = KQ * B_KSTRIDE, RAW = A_RAW + B_RAW;
   static constexpr int A_TILE = BM * KS * 4;         // one (bin, part, split) tile of A
   static constexpr int B_TILE = 3 * BN * KS * 4;     // one (bin, split) stack of B
   static constexpr int HALF_A = 2 * 2 * 2 * A_TILE, HALF_B = 2 * 2 * B_TILE, HSTAGE = HALF_A + HALF_B;
@@ -144,12 +151,13 @@ __device__ __forceinline__ float4 flip4(float4 v, unsigned mask) {
 }
 
 struct TmaArgs {
-  // bin x of element (m, k) of A sits at A + (x/16)*a_bs + x%16 + m*a_rs + k*a_ks (complex elements);
-  // a_bs = 16 is the natural bins-innermost layout, a_bs = planes*16 the bin-blocked one
+  // bin x of element (m, k) of A sits at A + (x/a_qb)*a_bs + x%a_qb + m*a_rs + k*a_ks (complex
+  // elements): bins in blocks of a_qb (16 or 4); a_qb = a_bs = 16 is the natural bins-innermost layout
   const float2* A;
   long long a_rs, a_ks, a_bs;
   const float2* B;
   long long b_rs, b_ks, b_bs;  // B[n][k][x]
+  int a_qb, b_qb;
   int M, N, K, X;
   int d_blocked;  // bin-blocked result: store coordinates (2*(x%16), m, n, x/16), else (2x, m, n, 0)
   float inv_norm;
@@ -218,16 +226,19 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
     // ------------------------------------------------------------------ operand loads
     // Two lanes per 32-byte segment (one row, one k, the tile's 4 bins); every thread issues its
     // share of a raw stage as 16-byte asynchronous copies (zero-filled outside the tensor) and lets
-    // the stage's barrier count their completion.
+    // the stage's barrier count their completion.  Consecutive segments of a warp follow the
+    // direction in which the operand is contiguous (rows or k), so that a warp's copies coalesce
+    // into whole 128-byte lines when the layout allows it.
     const int p = tid - kWarpProd * 32, half = p & 1, sp = p >> 1;  // sp in 0..63
+    // unit u = i*64 + sp of an operand with R rows: k-fastest (row = u / 4, j = u % 4) or row-fastest
+    const bool a_kfast = g.a_ks < g.a_rs, b_kfast = g.b_ks < g.b_rs;
     unsigned rs = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
       int n0, m0, x0;
       tile_coords(t, &n0, &m0, &x0);
-      const float2* pa = g.A + (long long)(x0 >> 4) * g.a_bs + (x0 & 15) + 2 * half + (long long)(m0 + sp) * g.a_rs;
-      const bool a_ok0 = m0 + sp < g.M, a_ok1 = m0 + sp + 64 < g.M;
-      const long long a_up = 64 * g.a_rs;
+      const float2* pa = g.A + (long long)(x0 / g.a_qb) * g.a_bs + (x0 % g.a_qb) + 2 * half;
+      const float2* pb = g.B + (long long)(x0 / g.b_qb) * g.b_bs + (x0 % g.b_qb) + 2 * half;
       for (int q = 0; q < 2 * nsteps; ++q, ++rs) {
         const unsigned st = rs % NR;
         if (rs >= NR && !wait_bar(bar(RAW_FREE + st), ((rs / NR) - 1) & 1, kErrRawFree, abort_word)) {
@@ -240,21 +251,22 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
         }
         const unsigned dst = smem_u32(raw_mem + st * C::RAW) + half * 16;
 #pragma unroll
-        for (int j = 0; j < KQ; ++j) {
+        for (int i = 0; i < (KQ * BM) / 64; ++i) {
+          const int u = i * 64 + sp;
+          const int row = a_kfast ? (u >> 2) : (u % BM), j = a_kfast ? (u & 3) : (u / BM);
           const int k = q * KQ + j;
-          const bool kv = k < g.K;
-          const float2* src = pa + (long long)(kv ? k : 0) * g.a_ks;
-          cp_async16(dst + (j * BM + sp) * 32, (kv && a_ok0) ? src : g.A, (kv && a_ok0) ? 16u : 0u);
-          cp_async16(dst + (j * BM + sp + 64) * 32, (kv && a_ok1) ? src + a_up : g.A, (kv && a_ok1) ? 16u : 0u);
+          const bool v = k < g.K && m0 + row < g.M;
+          cp_async16(dst + j * C::A_KSTRIDE + row * 32, v ? pa + (long long)(m0 + row) * g.a_rs + (long long)k * g.a_ks : g.A,
+                     v ? 16u : 0u);
         }
 #pragma unroll
         for (int i = 0; i < (KQ * BN) / 64; ++i) {
-          const int seg = i * 64 + sp, j = seg / BN, row = seg % BN;
+          const int u = i * 64 + sp;
+          const int row = b_kfast ? (u >> 2) : (u % BN), j = b_kfast ? (u & 3) : (u / BN);
           const int k = q * KQ + j;
           const bool v = k < g.K && n0 + row < g.N;
-          const float2* src = g.B + (long long)(x0 >> 4) * g.b_bs + (x0 & 15) + 2 * half + (long long)(n0 + row) * g.b_rs +
-                              (long long)k * g.b_ks;
-          cp_async16(dst + C::A_RAW + (j * BN + row) * 32, v ? src : g.B, v ? 16u : 0u);
+          cp_async16(dst + C::A_RAW + j * C::B_KSTRIDE + row * 32,
+                     v ? pb + (long long)(n0 + row) * g.b_rs + (long long)k * g.b_ks : g.B, v ? 16u : 0u);
         }
         // the barrier receives this thread's arrival once all its copies above have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(RAW_FULL + st)) : "memory");
@@ -407,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           if (!(g.debug & 1)) {
             float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + (j * BM + a_row) * 32 + pair * 16);
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + j * C::A_KSTRIDE + a_row * 32 + pair * 16);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {  // c = binl*2 + part
               const float w[4] = {c == 0 ? v[0].x : c == 1 ? v[0].y : c == 2 ? v[0].z : v[0].w,
@@ -425,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             float2 v[4];  // (re, im) of bin 2*pair + b_sel
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              v[j] = *reinterpret_cast<const float2*>(rb + (j * BN + b_row) * 32 + (pair * 2 + b_sel) * 8);
+              v[j] = *reinterpret_cast<const float2*>(rb + j * C::B_KSTRIDE + b_row * 32 + (pair * 2 + b_sel) * 8);
             const float wr[4] = {v[0].x, v[1].x, v[2].x, v[3].x}, wi[4] = {v[0].y, v[1].y, v[2].y, v[3].y};
             float4 brh, brl, bih, bil;
             split4(wr, &brh, &brl);
@@ -531,7 +543,7 @@ bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long lo
 
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs) {
+              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb) {
   const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
   alignas(64) CUtensorMap md;
   if (!make_map(&md, d, d_ms, d_ns, d_bs, M, N, X, 32, 4)) {
@@ -541,6 +553,7 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.A = reinterpret_cast<const float2*>(a), t.a_rs = a_rs, t.a_ks = a_ks, t.a_bs = a_bs;
   t.B = reinterpret_cast<const float2*>(b), t.b_rs = b_rs, t.b_ks = b_ks, t.b_bs = b_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
+  t.a_qb = a_qb, t.b_qb = b_qb;
   t.d_blocked = d_bs != 16;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;

@@ -30,11 +30,15 @@ struct RealView {
 // (N/2+1)*N bins of a plane are cut into blocks of 16 (128 bytes) and block xb of plane b sits
 // at p[((xb * blk_planes + b) * 16 + x % 16) * 2], so that for a fixed block all planes are
 // contiguous -- what the per-bin contraction reads.  sb/sr/sc/sz are ignored then.
+// blk_bins = 4 is the same with blocks of 4 bins (32 bytes): p[((x/4 * blk_planes + b) * 4 + x % 4) * 2],
+// the layout of the contraction's operands (a 4-bin tile of consecutive planes is one contiguous
+// run); only the forward transforms write it.
 struct CplxView {
   float* p;
   long long sb;
   int sr, sc, sz;
   long long blk_planes = 0;
+  int blk_bins = 16;
 };
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -64,8 +64,8 @@ bool as_images(const Tensor4& t, RealView* v, int* count) {
   return true;
 }
 
-// planes > 0: bin-blocked layout over that many planes (see CplxView)
-CplxView spectrum_view(float* p, int n, long long planes) {
+// planes > 0: bin-blocked layout over that many planes, in blocks of blk_bins bins (see CplxView)
+CplxView spectrum_view(float* p, int n, long long planes, int blk_bins) {
   CplxView v;
   v.p = p;
   v.sb = bins_of(n) * 2;
@@ -73,6 +73,7 @@ CplxView spectrum_view(float* p, int n, long long planes) {
   v.sc = 2;
   v.sz = 1;
   v.blk_planes = planes;
+  v.blk_bins = blk_bins;
   return v;
 }
 
@@ -80,7 +81,10 @@ int forward(int n, const Tensor4& t, int padL, int padU, float* spec, bool block
   RealView v;
   int count;
   if (!as_images(t, &v, &count)) return kUnsupportedDimension;
-  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0);
+  // forward spectra are contraction operands: 4-bin blocks
+  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0, 4);
+  // weights (3x3, 5x5, 7x7): direct evaluation, bound by the spectrum's bytes instead of butterflies
+  if (fft2d_pruned_supported(n, v, sv, padL, padU)) return fft2d_pruned_forward(n, v, sv, count, padL, padU, s);
   if (n <= 32) return fft2d_small_forward(n, v, sv, count, padL, padU, s);
   return fft2d_large_forward(n, v, sv, count, padL, padU, s);
 }
@@ -89,7 +93,9 @@ int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, bool block
   RealView v;
   int count;
   if (!as_images(t, &v, &count)) return kUnsupportedDimension;
-  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0);
+  // the contraction's result: 16-bin blocks (128-byte pieces for the inverse transform's row copies)
+  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0, 16);
+  if (fft2d_pruned_supported(n, v, sv, padL, padU)) return fft2d_pruned_inverse(n, sv, v, count, padL, padU, s);
   if (n <= 32) return fft2d_small_inverse(n, sv, v, count, padL, padU, s);
   return fft2d_large_inverse(n, sv, v, count, padL, padU, s);
 }
@@ -109,8 +115,9 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
              long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s) {
   const long long X = bins_of(n);
   if (blocked) {
-    return cgemm_tc(a, a_pm * 16, a_pk * 16, conjA, b, b_pn * 16, b_pk * 16, conjB, d, d_pm * 16, d_pn * 16, M, N, K,
-                    (int)X, inv_norm, false, s, a_planes * 16, b_planes * 16, d_planes * 16);
+    // operands in 4-bin blocks (plane stride 4 complex), result in 16-bin blocks
+    return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * 16, d_pn * 16, M, N, K, (int)X,
+                    inv_norm, false, s, a_planes * 4, b_planes * 4, d_planes * 16, 4, 4);
   }
   // natural layout: D[m][n] = sum_k opA(A[m][k]) opB(B[n][k]) = cgemm_bins with A' = A (rows m),
   // B' = B^T: C[i=m][j=n] = sum_k opA(A[i][k]) * opB'(B'[k][j]), B'[k][j] = B[j][k] -> "conj-transposed" flag

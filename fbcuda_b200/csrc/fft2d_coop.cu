@@ -120,7 +120,7 @@ __device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
 template <int N, bool IN_BULK>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
-                                                                                int padU, long long blk_planes) {
+                                                                                int padU, long long blk_planes, int blk_bins) {
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
@@ -270,7 +270,15 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     fence_async_smem();
     block_sync<T>();
     float* dst = out + (long long)b * out_sb;
-    if (blk_planes) {
+    if (blk_planes && blk_bins == 4) {
+      // 4-bin blocks (contraction operands): 32-byte pieces, planes adjacent; two lanes per piece
+      constexpr int QR = N / 4;
+      for (int i = threadIdx.x; i < (H + 1) * QR * 2; i += T) {
+        const int half = i & 1, piece = i >> 1;
+        const float4 v = *reinterpret_cast<const float4*>(tile + (piece / QR) * PO + (piece % QR) * 4 + half * 2);
+        *reinterpret_cast<float4*>(out + ((long long)piece * blk_planes + b) * 8 + half * 4) = v;
+      }
+    } else if (blk_planes) {
       // bin-blocked layout (convolution workspace): 128-byte pieces, planes adjacent
       constexpr int CB = N / 16;
       for (int i = threadIdx.x; i < (H + 1) * CB; i += T) {
@@ -448,9 +456,9 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
   if (in_bulk) {
-    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
   } else {
-    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }

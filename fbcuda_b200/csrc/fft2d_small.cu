@@ -137,7 +137,20 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
     if (OUT_BULK) {
       fence_async_smem();
       __syncwarp();
-      if (N >= 16 && out.blk_planes) {
+      if (N >= 16 && out.blk_planes && out.blk_bins == 4) {
+        // 4-bin blocks: every 32-byte piece of a row goes next to the same piece of the neighbouring
+        // planes; two lanes per piece, the images of the warp adjacent in memory
+        constexpr int QR = N / 4;
+        for (int e = lane; e < IPW * ROWS * QR * 2; e += 32) {
+          const int half = e & 1, img = (e >> 1) % IPW, piece = (e >> 1) / IPW;  // piece = row * QR + quad in row
+          const int bb = task * IPW + img;
+          if (bb < B) {
+            const float4 v = *reinterpret_cast<const float4*>(buf + img * IS + (piece / QR) * RS + (piece % QR) * 4 + half * 2);
+            *reinterpret_cast<float4*>(out.p + ((long long)piece * out.blk_planes + bb) * 8 + half * 4) = v;
+          }
+        }
+        __syncwarp();
+      } else if (N >= 16 && out.blk_planes) {
         // bin-blocked layout: every 16-bin (128-byte) piece of a row goes next to the same piece
         // of the neighbouring planes
         constexpr int CB = N >= 16 ? N / 16 : 1;

@@ -21,6 +21,10 @@ bool fft2d_coop_supported(int n, const CplxView& c);
 int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 int read_device_error_coop();
+// direct evaluation for images with a support of at most 8 x 8, N in {16, 32, 64, 128} (fft2d_pruned.cu)
+bool fft2d_pruned_supported(int n, const RealView& real, const CplxView& cplx, int padL, int padU);
+int fft2d_pruned_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
+int fft2d_pruned_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 // the reference's two-call protocol for N >= 64 (fft_lines.cu)
 int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, int B, int padL, int padU,
                              cudaStream_t s);
@@ -54,14 +58,15 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
                         const float* d, long long d_ms, long long d_ns, int M, int N, int K, int X);
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-             bool accumulate, cudaStream_t s, long long a_bs = 16, long long b_bs = 16, long long d_bs = 16);
+             bool accumulate, cudaStream_t s, long long a_bs = 16, long long b_bs = 16, long long d_bs = 16, int a_qb = 16,
+             int b_qb = 16);
 // persistent TMA-fed version (cgemm_tma.cu); returns -1 when a tensor map cannot be encoded
 bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,
                          long long b_ks, long long b_bs, const float* d, long long d_ms, long long d_ns, long long d_bs,
                          int M, int N, int K, int X);
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs);
+              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb);
 int read_device_error_tma();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only
 void set_contraction_mode(int mode);
