@@ -412,10 +412,13 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       }
       block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
       if (b + gridDim.x < B) fetch(b + gridDim.x);
-      coop_fft<N, R, Q, true>(a, q, lf);
-      float* dst = out.p + (long long)b * out.sb;
       const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
       const bool ok0 = x0 < (unsigned)out.w, ok1 = x1 < (unsigned)out.w;
+      // a warp none of whose columns is kept by the crop (small outputs such as weight gradients)
+      // skips its transforms
+      if (__all_sync(0xffffffffu, !ok0 && !ok1)) continue;
+      coop_fft<N, R, Q, true>(a, q, lf);
+      float* dst = out.p + (long long)b * out.sb;
       float* p0 = dst + (long long)x0 * out.sx + (long long)(q - padU) * out.sy;
       float* p1 = dst + (long long)x1 * out.sx + (long long)(q - padU) * out.sy;
       static_for<R>([&](auto kc) {
