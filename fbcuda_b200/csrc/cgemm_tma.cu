@@ -1,6 +1,6 @@
 // Per-frequency-bin complex contraction, persistent warp-specialised version: operands arrive by
-// TMA tensor copies, the 3xTF32 split runs from shared memory, the products run on the
-// 5th-generation tensor cores (tcgen05.mma kind::tf32, accumulators in tensor memory) and the
+// asynchronous copies into shared memory, the 3xTF32 split runs from there, the products run on
+// the 5th-generation tensor cores (tcgen05.mma kind::tf32, accumulators in tensor memory) and the
 // result leaves by TMA tensor stores.  Same math as cgemm_bins.cu / the reference's transposeMM
 // (MM-inl.cuh:188-196):
 //
@@ -8,25 +8,32 @@
 //
 // A tile is 128 rows of m, BN columns of n and 4 consecutive bins (32 contiguous bytes of every
 // operand element: one DRAM sector).  Each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
-// (n tiles fastest, so blocks that run at the same time share the A operand in L2).  Roles:
-//   warp 8        one lane issues, per 4 values of k, one 4-D tensor copy for A ([k][row][32 B] in
-//                 shared memory, 16 KB) and one for B, into a ring of NR raw stages; rows, columns
-//                 and k beyond the tensor are zero-filled by the copy engine;
+// Roles (17 warps):
+//   warps 8-11    issue, per 4 values of k, the 16-byte cp.async copies of one raw stage ([k][row]
+//                 [32 B] per operand, zero-filled outside the tensor) into a ring of NR stages; the
+//                 stage's mbarrier counts the copies' completion.  Lanes follow the direction in
+//                 which the operand is contiguous, so the convolution workspace (4-bin blocks,
+//                 planes adjacent) is read in whole 128-byte lines.  (TMA tensor copies were measured
+//                 first: with a 32-byte inner box they reach 1.3 TB/s, these copies 2 TB/s on
+//                 bins-innermost tensors and the full rate on the blocked workspace.)
 //   warps 0-7     read the raw stages, split every fp32 into hi = tf32(x) and lo = x - hi, and write
 //                 K-major operand tiles in the tensor core's no-swizzle layout (8 x 16-byte core
 //                 matrices) per bin: Ar, Ai (hi and lo) and the stack [-s Bi | Br | s Bi] (hi and lo;
 //                 s = -1 when B is conjugated), into a ring of two half stages of two bins each;
-//   warp 9        one lane issues, per bin and k-step of 8, six MMAs of 128 x 2BN x 8 into the bin's
+//   warp 12       one lane issues, per bin and k-step of 8, six MMAs of 128 x 2BN x 8 into the bin's
 //                 [Re | Im] accumulator:  Ar_h x S_h, Ai_h x S'_h, Ar_h x S_l, Ai_h x S'_l, Ar_l x S_h,
 //                 Ai_l x S'_h with S = rows BN..3BN of the stack = [Br | s Bi] and S' = rows 0..2BN =
 //                 [-s Bi | Br] (the Ai products negated when A is conjugated); tcgen05.commit frees
 //                 the half stage and, after the last k-step, hands the accumulators to the epilogue;
-//   warps 10-13   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
+//   warps 13-16   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
 //                 interleave the 4 bins' re/im into 32 bytes per (m, n) in a 4 KB staging buffer and
 //                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
+// What bounds it: shared-memory bandwidth.  Per half stage the MMAs read 96 KB of operand tiles,
+// the split writes 56 KB and reads 24 KB, the copies write 24 KB -- about 200 KB at 128 B/clock;
+// measured alone, the MMAs run at the tf32 peak and the split at 70 % of the shared-memory rate,
+// and together their times add.
 // Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
 // block still releases its tensor memory before returning.
-#include <cstdlib>
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
 
 #include "fft2d_small.cuh"  // mbarrier helpers, fence_async_smem
@@ -45,12 +52,8 @@ enum : int { kErrRawFull = 211, kErrRawFree = 212, kErrCvFull = 213, kErrCvFree 
 
 template <int BN>
 struct Cfg {
-#ifndef FBFFT_NR
-#define FBFFT_NR 4
-#define FBFFT_NH 2
-#endif
-  static constexpr int NR = FBFFT_NR;                // raw stages (4 values of k each)
-  static constexpr int NH = FBFFT_NH;                     // converted half stages (2 bins x 8 k each)
+  static constexpr int NR = 4;                       // raw stages (4 values of k each)
+  static constexpr int NH = 2;                       // converted half stages (2 bins x 8 k each)
   static constexpr int NACC = (BN == 64) ? 1 : 2;    // accumulator sets in tensor memory
   static constexpr int ACC_COLS = XB * 2 * BN;
   static constexpr int TMEM_COLS = NACC * ACC_COLS;  // 512, 512, 256
@@ -163,7 +166,6 @@ struct TmaArgs {
   float inv_norm;
   int conjA, conjB, accumulate;
   int n_tiles, m_tiles, total_tiles;
-  int debug;  // TEMP ablation bits: 1 no conversion, 2 no MMA, 4 no stores, 8 no loads
 };
 
 template <int BN>
@@ -245,10 +247,6 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           ok = false;
           break;
         }
-        if (g.debug & 8) {
-          mbar_arrive(bar(RAW_FULL + st));
-          continue;
-        }
         const unsigned dst = smem_u32(raw_mem + st * C::RAW) + half * 16;
 #pragma unroll
         for (int i = 0; i < (KQ * BM) / 64; ++i) {
@@ -300,7 +298,6 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             const unsigned first = (s > 0) ? 1u : 0u;  // the first product into an accumulator overwrites it
 #pragma unroll
             for (int binl = 0; binl < 2; ++binl) {
-              if (g.debug & 2) break;
               const unsigned d = tmem_base + acc * C::ACC_COLS + (pair * 2 + binl) * (2 * BN);
               const unsigned long long a_rh = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 0) * C::A_TILE) >> 4);
               const unsigned long long a_rl = da0 + (unsigned long long)((((binl * 2 + 0) * 2 + 1) * C::A_TILE) >> 4);
@@ -368,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           }
           fence_async_smem();
           __syncwarp();
-          if (lane == 0 && !(g.debug & 4)) {
+          if (lane == 0) {
             if (g.accumulate) {
               tma_reduce_add4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
             } else {
@@ -416,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             break;
           }
           unsigned char* cst = conv_mem + buf * C::HSTAGE;
-          if (!(g.debug & 1)) {
+          {
             float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + j * C::A_KSTRIDE + a_row * 32 + pair * 16);
@@ -433,7 +430,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
               *reinterpret_cast<float4*>(tdst + C::A_TILE) = lo;
             }
           }
-          if (has_b && !(g.debug & 1)) {
+          if (has_b) {
             float2 v[4];  // (re, im) of bin 2*pair + b_sel
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -557,7 +554,6 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.d_blocked = d_bs != 16;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
-  t.debug = getenv("FBFFT_TMA_DEBUG") ? atoi(getenv("FBFFT_TMA_DEBUG")) : 0;
   if (BN == 16) return launch_tma<16>(md, t, s);
   if (BN == 32) return launch_tma<32>(md, t, s);
   return launch_tma<64>(md, t, s);

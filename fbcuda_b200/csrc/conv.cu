@@ -12,7 +12,6 @@
 //   accGradParameters  wF  [o][c] = sum_b conj(outF[b][o]) * inF[b][c]
 // every result scaled by 1/N^2 (accGradParameters also by `scale`) and cropped at
 // the tensor's (padU, padL) offset inside the N x N canvas; weights sit at (0, 0).
-#include <cstdlib>
 #include "../../include/fbfft_b200.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -85,7 +84,7 @@ int forward(int n, const Tensor4& t, int padL, int padU, float* spec, bool block
   // forward spectra are contraction operands: 4-bin blocks
   const CplxView sv = spectrum_view(spec, n, blocked ? count : 0, 4);
   // weights (3x3, 5x5, 7x7): direct evaluation, bound by the spectrum's bytes instead of butterflies
-  if (!getenv("FBFFT_NO_PRUNED_FWD") && n >= 64 && v.h * 4 <= n && v.w * 4 <= n && fft2d_pruned_supported(n, v, sv, padL, padU))
+  if (n >= 64 && v.h * 4 <= n && v.w * 4 <= n && fft2d_pruned_supported(n, v, sv, padL, padU))
     return fft2d_pruned_forward(n, v, sv, count, padL, padU, s);
   if (n <= 32) return fft2d_small_forward(n, v, sv, count, padL, padU, s);
   return fft2d_large_forward(n, v, sv, count, padL, padU, s);
