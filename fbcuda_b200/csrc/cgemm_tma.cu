@@ -52,7 +52,7 @@ enum : int { kErrRawFull = 211, kErrRawFree = 212, kErrCvFull = 213, kErrCvFree 
 
 template <int BN>
 struct Cfg {
-  static constexpr int NR = 4;                       // raw stages (4 values of k each)
+  static constexpr int NR = 4;                       // raw stages (4 values of k each; a k-step of 8 needs two)
   static constexpr int NH = 2;                       // converted half stages (2 bins x 8 k each)
   static constexpr int NACC = (BN == 64) ? 1 : 2;    // accumulator sets in tensor memory
   static constexpr int ACC_COLS = XB * 2 * BN;
@@ -64,7 +64,7 @@ struct Cfg {
   static constexpr int A_TILE = BM * KS * 4;         // one (bin, part, split) tile of A
   static constexpr int B_TILE = 3 * BN * KS * 4;     // one (bin, split) stack of B
   static constexpr int HALF_A = 2 * 2 * 2 * A_TILE, HALF_B = 2 * 2 * B_TILE, HSTAGE = HALF_A + HALF_B;
-  static constexpr int EPI_WARP = 32 * 4 * 32;       // 32 rows x 4 columns x 32 bytes
+  static constexpr int EPI_WARP = 32 * 4 * 32;       // staging per epilogue warp: 32 rows x 4 columns x 32 bytes
   static constexpr int A_LBO = (BM / 8) * 128, B_LBO = (3 * BN / 8) * 128, SBO = 128;
   static constexpr int OFF_CONV = NR * RAW, OFF_EPI = OFF_CONV + NH * HSTAGE, OFF_BAR = OFF_EPI + 4 * EPI_WARP;
   static constexpr int SMEM = OFF_BAR + 256;
@@ -247,14 +247,16 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           ok = false;
           break;
         }
-        const unsigned dst = smem_u32(raw_mem + st * C::RAW) + half * 16;
+        // the two 16-byte halves of a row's 32 bytes swap places every 4 rows: the split's 16-byte
+        // reads of consecutive rows then fall into different banks
+        const unsigned dst = smem_u32(raw_mem + st * C::RAW);
 #pragma unroll
         for (int i = 0; i < (KQ * BM) / 64; ++i) {
           const int u = i * 64 + sp;
           const int row = a_kfast ? (u >> 2) : (u % BM), j = a_kfast ? (u & 3) : (u / BM);
           const int k = q * KQ + j;
           const bool v = k < g.K && m0 + row < g.M;
-          cp_async16(dst + j * C::A_KSTRIDE + row * 32, v ? pa + (long long)(m0 + row) * g.a_rs + (long long)k * g.a_ks : g.A,
+          cp_async16(dst + j * C::A_KSTRIDE + row * 32 + ((half ^ ((row >> 2) & 1)) << 4), v ? pa + (long long)(m0 + row) * g.a_rs + (long long)k * g.a_ks : g.A,
                      v ? 16u : 0u);
         }
 #pragma unroll
@@ -263,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           const int row = b_kfast ? (u >> 2) : (u % BN), j = b_kfast ? (u & 3) : (u / BN);
           const int k = q * KQ + j;
           const bool v = k < g.K && n0 + row < g.N;
-          cp_async16(dst + C::A_RAW + j * C::B_KSTRIDE + row * 32,
+          cp_async16(dst + C::A_RAW + j * C::B_KSTRIDE + row * 32 + ((half ^ ((row >> 2) & 1)) << 4),
                      v ? pb + (long long)(n0 + row) * g.b_rs + (long long)k * g.b_ks : g.B, v ? 16u : 0u);
         }
         // the barrier receives this thread's arrival once all its copies above have landed
@@ -339,46 +341,64 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
       tc_fence_after();
       const int dx = g.d_blocked ? 2 * (x0 & 15) : 2 * x0, db = g.d_blocked ? (x0 >> 4) : 0;
       const int mrow = m0 + lq * 32;
-      if (mrow < g.M) {
+      const int ncols = (g.N - n0 < BN) ? g.N - n0 : BN;
+      const int nch = (mrow < g.M) ? (ncols + 3) / 4 : 0;  // chunks of 4 columns this warp stores
+      const unsigned tacc = tmem_base + ((unsigned)(lq * 32) << 16) + acc * C::ACC_COLS;
+      auto load_chunk = [&](int c, float (&v)[XB][2][4]) {
+#pragma unroll
+        for (int bin = 0; bin < XB; ++bin) {
+#pragma unroll
+          for (int part = 0; part < 2; ++part) tmem_ld4(tacc + bin * (2 * BN) + part * BN + c * 4, v[bin][part]);
+        }
+      };
+      // this warp's reads of the accumulators are complete: the next tile may overwrite them
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(ACC_FREE + acc));
+      };
+      auto emit = [&](const float (&v)[XB][2][4], int c) {
+        // the previous store of this warp must have finished reading the staging buffer
+        if (lane == 0) bulk_wait_read();
+        __syncwarp();
+        unsigned char* buf = stag;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float4* dst = reinterpret_cast<float4*>(buf + (j * 32 + lane) * 32);
+          dst[0] = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
+                               v[1][1][j] * g.inv_norm);
+          dst[1] = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
+                               v[3][1][j] * g.inv_norm);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (g.accumulate) {
+            tma_reduce_add4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
+          } else {
+            tma_store4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
+          }
+          bulk_commit();
+        }
+      };
+      if (nch == 0) {
+        release();
+      } else {
+        // two register sets: the accumulator reads of the next chunk fly while this one is stored
+        float va[XB][2][4], vb[XB][2][4];
+        load_chunk(0, va);
 #pragma unroll 1
-        for (int nc = 0; nc < BN && n0 + nc < g.N; nc += 4) {
-          float v[XB][2][4];
-#pragma unroll
-          for (int bin = 0; bin < XB; ++bin) {
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              tmem_ld4(tmem_base + ((unsigned)(lq * 32) << 16) + acc * C::ACC_COLS + bin * (2 * BN) + part * BN + nc,
-                       v[bin][part]);
-            }
-          }
+        for (int c = 0; c < nch; c += 2) {
           tmem_ld_wait();
-          // the previous store of this warp must have finished reading the staging buffer
-          if (lane == 0) bulk_wait_read();
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float4* dst = reinterpret_cast<float4*>(stag + (j * 32 + lane) * 32);
-            dst[0] = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
-                                 v[1][1][j] * g.inv_norm);
-            dst[1] = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
-                                 v[3][1][j] * g.inv_norm);
-          }
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (g.accumulate) {
-              tma_reduce_add4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
-            } else {
-              tma_store4(&map_d, dx, mrow, n0 + nc, db, stag_u32);
-            }
-            bulk_commit();
+          if (c + 1 < nch) load_chunk(c + 1, vb); else release();
+          emit(va, c);
+          if (c + 1 < nch) {
+            tmem_ld_wait();
+            if (c + 2 < nch) load_chunk(c + 2, va); else release();
+            emit(vb, c + 1);
           }
         }
       }
-      // this warp's reads of the accumulators are complete: the next tile may overwrite them
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(ACC_FREE + acc));
     }
     if (lane == 0) bulk_wait_all();
     __syncwarp();
@@ -416,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           {
             float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + j * C::A_KSTRIDE + a_row * 32 + pair * 16);
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + j * C::A_KSTRIDE + a_row * 32 + ((pair ^ ((a_row >> 2) & 1)) << 4));
 #pragma unroll
             for (int c = 0; c < 4; ++c) {  // c = binl*2 + part
               const float w[4] = {c == 0 ? v[0].x : c == 1 ? v[0].y : c == 2 ? v[0].z : v[0].w,
@@ -434,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             float2 v[4];  // (re, im) of bin 2*pair + b_sel
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              v[j] = *reinterpret_cast<const float2*>(rb + j * C::B_KSTRIDE + b_row * 32 + (pair * 2 + b_sel) * 8);
+              v[j] = *reinterpret_cast<const float2*>(rb + j * C::B_KSTRIDE + b_row * 32 + ((pair ^ ((b_row >> 2) & 1)) << 4) + b_sel * 8);
             const float wr[4] = {v[0].x, v[1].x, v[2].x, v[3].x}, wi[4] = {v[0].y, v[1].y, v[2].y, v[3].y};
             float4 brh, brl, bih, bil;
             split4(wr, &brh, &brl);
