@@ -117,7 +117,9 @@ __device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
 // ------------------------------------------------------------------ forward
 // IN_BULK: the real input is contiguous with a 16-byte aligned base; each image is staged in
 // shared memory by one cp.async.bulk (into the region the image's own mid/tile reuse afterwards).
-template <int N, bool IN_BULK>
+// FULL (with IN_BULK): the images are N x N with no padding, so pass A reads the staged image
+// with compile-time strides and no bounds predicates.
+template <int N, bool IN_BULK, bool FULL = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
                                                                                 int padU, long long blk_planes, int blk_bins) {
@@ -126,15 +128,17 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
   constexpr int H = N / 2, T = H * Q;
   extern __shared__ __align__(16) float2 smem[];
   float2* mid = smem;   // [N][PM]        pass A -> pass B
-  float2* tile = smem;  // [H+1][PO] + packed row [N]   pass B -> bulk stores (aliases mid)
-  float2* vsd = smem + (H + 1) * PO;  // packed row, direct half  [H+1]
-  float2* vsm = vsd + (H + 1);        // packed row, mirrored half [H+1]
+  float2* tile = smem;  // [H+1][PO]      pass B -> bulk stores (aliases mid)
+  // the packed row's two halves live in the tile's padding columns N (direct) and N + 1 (mirrored),
+  // so that every row scatters with the same compile-time stride
+  float2* vsd = smem + N;
+  float2* vsm = smem + N + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = lane / LP, item = warp * LP + (lane % LP);  // item: column pair p (pass A), row r (pass B)
   float2 lf[Q];
   lane_factors<Q, false>(q, lf);
   // staging (IN_BULK): raw image bytes at the start of the region, mbarrier behind the region
-  constexpr int REGION = (N * PM > (H + 1) * PO + N + 2) ? N * PM : (H + 1) * PO + N + 2;
+  constexpr int REGION = (N * PM > (H + 1) * PO) ? N * PM : (H + 1) * PO;
   const unsigned bar = smem_u32(smem + REGION);
   const long long img_bytes = (long long)in.h * in.w * 4, total_bytes = img_bytes * B;
   unsigned phase = 0;
@@ -176,19 +180,31 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
         src = reinterpret_cast<const float*>(smem) + ((((long long)b * img_bytes) & 15) >> 2);
         sy = in.w, sx = 1;
       }
-      const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
-      const bool ok0 = x0 < (unsigned)in.w, ok1 = x1 < (unsigned)in.w;
-      const float* p0 = src + (long long)x0 * sx + (long long)(P * q - padU) * sy;
-      const float* p1 = src + (long long)x1 * sx + (long long)(P * q - padU) * sy;
-      const int ybase = P * q - padU;
+      if constexpr (FULL) {
+        const float* p0 = reinterpret_cast<const float*>(smem) + item + P * q * N;
 #pragma unroll
-      for (int m = 0; m < Q; ++m) {
+        for (int m = 0; m < Q; ++m) {
 #pragma unroll
-        for (int jl = 0; jl < P; ++jl) {
-          const int yo = jl + R * m;
-          const bool oky = (unsigned)(ybase + yo) < (unsigned)in.h;
-          a[m * P + jl].x = (oky && ok0) ? p0[(long long)yo * sy] : 0.f;
-          a[m * P + jl].y = (oky && ok1) ? p1[(long long)yo * sy] : 0.f;
+          for (int jl = 0; jl < P; ++jl) {
+            a[m * P + jl].x = p0[(jl + R * m) * N];
+            a[m * P + jl].y = p0[(jl + R * m) * N + H];
+          }
+        }
+      } else {
+        const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
+        const bool ok0 = x0 < (unsigned)in.w, ok1 = x1 < (unsigned)in.w;
+        const float* p0 = src + (long long)x0 * sx + (long long)(P * q - padU) * sy;
+        const float* p1 = src + (long long)x1 * sx + (long long)(P * q - padU) * sy;
+        const int ybase = P * q - padU;
+#pragma unroll
+        for (int m = 0; m < Q; ++m) {
+#pragma unroll
+          for (int jl = 0; jl < P; ++jl) {
+            const int yo = jl + R * m;
+            const bool oky = (unsigned)(ybase + yo) < (unsigned)in.h;
+            a[m * P + jl].x = (oky && ok0) ? p0[(long long)yo * sy] : 0.f;
+            a[m * P + jl].y = (oky && ok1) ? p1[(long long)yo * sy] : 0.f;
+          }
         }
       }
       if (IN_BULK) block_sync<T>();  // the staged image is in registers: mid may overwrite it
@@ -247,23 +263,22 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       // the same into the two halves of the scratch row: vsd[kx] = V[kx], vsm[j] = conj(V[(N-j)%N]).
       float2* direct = (r == 0) ? vsd : tile + r;
       float2* mirror = (r == 0) ? vsm : tile + (N - r);
-      const int stride = (r == 0) ? 1 : PO;
       static_for<R>([&](auto kc) {
         constexpr int k = decltype(kc)::value;
         const int kx = Q * k + q;
         const float2 v = a[brev(k, R)];
         if (Q * k + Q - 1 <= H || kx <= H) {
-          if (kx <= H) direct[kx * stride] = v;
+          if (kx <= H) direct[kx * PO] = v;
         }
         if (Q * k >= H - (Q - 1) || k == 0) {
-          if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * stride] = make_float2(v.x, -v.y);
+          if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
         }
       });
     }
     block_sync<T>();
     // rows ky = 0 and N/2 from the packed row: V = F[0] + i F[N/2]
     for (int kx = threadIdx.x; kx <= H; kx += T) {
-      const float2 v = vsd[kx], cm = vsm[kx];  // V[kx], conj(V[(N-kx)%N])
+      const float2 v = vsd[kx * PO], cm = vsm[kx * PO];  // V[kx], conj(V[(N-kx)%N])
       tile[kx * PO] = make_float2(0.5f * (v.x + cm.x), 0.5f * (v.y + cm.y));
       tile[kx * PO + H] = make_float2(0.5f * (v.y - cm.y), 0.5f * (cm.x - v.x));
     }
@@ -435,7 +450,7 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 
 template <int N>
 constexpr int fwd_smem() {
-  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO + N + 2;
+  constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO;
   return (mid > tile ? mid : tile) * (int)sizeof(float2) + 16;
 }
 template <int N>
@@ -452,13 +467,16 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
-  if (in_bulk) {
+  if (in_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
+    fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
+  } else if (in_bulk) {
     fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
   } else {
     fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
@@ -474,6 +492,7 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
