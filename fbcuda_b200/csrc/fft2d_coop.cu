@@ -316,7 +316,9 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 }
 
 // ------------------------------------------------------------------ inverse
-template <int N>
+// FULL: the output images are contiguous N x N with no crop offset (compile-time strides, no
+// bounds predicates on the stores)
+template <int N, bool FULL = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
                                                                                 long long in_sb, RealView out, int B,
                                                                                 int padL, int padU, long long blk_planes) {
@@ -434,16 +436,26 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       if (__all_sync(0xffffffffu, !ok0 && !ok1)) continue;
       coop_fft<N, R, Q, true>(a, q, lf);
       float* dst = out.p + (long long)b * out.sb;
-      float* p0 = dst + (long long)x0 * out.sx + (long long)(q - padU) * out.sy;
-      float* p1 = dst + (long long)x1 * out.sx + (long long)(q - padU) * out.sy;
-      static_for<R>([&](auto kc) {
-        constexpr int k = decltype(kc)::value;
-        if ((unsigned)(Q * k + q - padU) < (unsigned)out.h) {
+      if constexpr (FULL) {
+        float* p0 = dst + item + q * N;
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
           const float2 t = a[brev(k, R)];
-          if (ok0) p0[(long long)(Q * k) * out.sy] = t.x;
-          if (ok1) p1[(long long)(Q * k) * out.sy] = t.y;
-        }
-      });
+          p0[Q * k * N] = t.x;
+          p0[Q * k * N + H] = t.y;
+        });
+      } else {
+        float* p0 = dst + (long long)x0 * out.sx + (long long)(q - padU) * out.sy;
+        float* p1 = dst + (long long)x1 * out.sx + (long long)(q - padU) * out.sy;
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          if ((unsigned)(Q * k + q - padU) < (unsigned)out.h) {
+            const float2 t = a[brev(k, R)];
+            if (ok0) p0[(long long)(Q * k) * out.sy] = t.x;
+            if (ok1) p1[(long long)(Q * k) * out.sy] = t.y;
+          }
+        });
+      }
     }
   }
 }
@@ -469,6 +481,7 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
@@ -494,10 +507,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
-  fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  // (measured: the predicate-free stores gain at N = 128, 0.57 -> 0.78 of the copy bandwidth, and lose at N = 64)
+  if (N == 128 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0) {
+    fft2d_coop_inv_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  } else {
+    fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 

@@ -35,7 +35,8 @@ enum : int { kErrFwdWait = 101, kErrInvWait = 102 };
 // ------------------------------------------------------------------ forward
 // IN_BULK : real input is contiguous [B][h][w] with a 16-byte aligned base
 // OUT_BULK: complex output is contiguous [B][N/2+1][N][2] with a 16-byte aligned base
-template <int N, bool IN_BULK, bool OUT_BULK>
+// FULL    : (with IN_BULK) the images are N x N without padding: compile-time offsets, no predicates
+template <int N, bool IN_BULK, bool OUT_BULK, bool FULL = false>
 __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
                                                                           int padU, int ntasks, int slot_floats, int slot_pitch) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
@@ -112,7 +113,11 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
         phase ^= 1;
         const long long g0 = (long long)task * IPW * img_floats * 4;
         const int off0 = per_image ? 0 : (int)((g0 & 15) >> 2);
-        load_columns<N>(slot + off0 + li * slot_pitch, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
+        if constexpr (FULL) {
+          load_columns_full<N>(slot + li * (N * N + N / 2), l, a);  // per-image slots of pitch N*N + N/2
+        } else {
+          load_columns<N>(slot + off0 + li * slot_pitch, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
+        }
       } else {
         load_columns<N>(in.p + (long long)(valid ? b : 0) * in.sb, in.sy, in.sx, in.h, in.w, padL, padU, valid, l, a);
       }
@@ -196,7 +201,8 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
 // ------------------------------------------------------------------ inverse
 // IN_BULK: complex input contiguous and 16-byte aligned; rows are fetched with bulk
 // copies one task ahead into the second of two work buffers.
-template <int N, bool IN_BULK>
+// FULL   : the output images are contiguous N x N without crop offset
+template <int N, bool IN_BULK, bool FULL = false>
 __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxView in, RealView out, int B, int padL,
                                                                           int padU, int ntasks) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
@@ -276,7 +282,13 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
       float2 z[N];
       inv_columns<N>(ib, l, z);
       const int b = task * IPW + li;
-      if (b < B) store_columns<N>(out.p + (long long)b * out.sb, out.sy, out.sx, out.h, out.w, padL, padU, l, z, 1.0f);
+      if (b < B) {
+        if constexpr (FULL) {
+          store_columns_full<N>(out.p + (long long)b * (N * N), l, z);
+        } else {
+          store_columns<N>(out.p + (long long)b * out.sb, out.sy, out.sx, out.h, out.w, padL, padU, l, z, 1.0f);
+        }
+      }
     }
     __syncwarp();
     cur ^= IN_BULK ? 1 : 0;
@@ -321,7 +333,11 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   if (in_bulk) {
     const int smem = base + kWarps * slot_floats * 4 + kWarps * 8;
     const int grid = grid_for(ntasks, 3);
-    if (out_bulk) {
+    // (measured: the predicate-free variant gains at N = 16 and loses a little at N = 8 and 32)
+    if (N == 16 && out_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
+      allow_smem(fft2d_small_fwd_kernel<N, true, true, true>, smem);
+      fft2d_small_fwd_kernel<N, true, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
+    } else if (out_bulk) {
       allow_smem(fft2d_small_fwd_kernel<N, true, true>, smem);
       fft2d_small_fwd_kernel<N, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
     } else {
@@ -346,8 +362,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   const int base = work_floats<N>() * 4;
   if (cplx_is_contiguous16(in, N)) {
     const int smem = 2 * base + kWarps * 16;
-    allow_smem(fft2d_small_inv_kernel<N, true>, smem);
-    fft2d_small_inv_kernel<N, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    // (measured: gains at N = 16, loses at N = 8 and 32)
+    const bool full = N == 16 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0 &&
+                      (B <= 1 || out.sb == (long long)N * N);
+    if (full) {
+      allow_smem(fft2d_small_inv_kernel<N, true, true>, smem);
+      fft2d_small_inv_kernel<N, true, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    } else {
+      allow_smem(fft2d_small_inv_kernel<N, true>, smem);
+      fft2d_small_inv_kernel<N, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    }
   } else {
     fft2d_small_inv_kernel<N, false><<<grid_for(ntasks, 4), kSmallThreads, base, s>>>(in, out, B, padL, padU, ntasks);
   }

@@ -57,6 +57,17 @@ __device__ __forceinline__ void load_columns(const float* src, long long sy, lon
   }
 }
 
+// The same for a contiguous N x N image without padding: compile-time offsets, no predicates.
+template <int N>
+__device__ __forceinline__ void load_columns_full(const float* src, int l, float2 (&a)[N]) {
+  constexpr int T = N / 2;
+#pragma unroll
+  for (int y = 0; y < N; ++y) {
+    a[y].x = src[y * N + l];
+    a[y].y = src[y * N + l + T];
+  }
+}
+
 // Pass A tail: a[] holds the bit-reversed transform Z of (column l) + i (column
 // l+T).  Separates A = (Z[r] + conj Z[N-r])/2 and B = (Z[r] - conj Z[N-r])/2i and
 // writes rows 0..T-1 of both columns; rows 0 and N/2 are real and share row 0 as
@@ -171,6 +182,18 @@ __device__ __forceinline__ void store_columns(float* dst, long long sy, long lon
       if (ok0) p0[(long long)y * sy] = t.x * mul;
       if (ok1) p1[(long long)y * sy] = t.y * mul;
     }
+  });
+}
+
+// The same for a contiguous N x N output without crop offset.
+template <int N>
+__device__ __forceinline__ void store_columns_full(float* dst, int l, const float2 (&z)[N]) {
+  constexpr int T = N / 2;
+  static_for<N>([&](auto yc) {
+    constexpr int y = decltype(yc)::value;
+    const float2 t = z[brev(y, N)];
+    dst[y * N + l] = t.x;
+    dst[y * N + l + T] = t.y;
   });
 }
 
