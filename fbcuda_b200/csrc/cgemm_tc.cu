@@ -87,7 +87,7 @@ struct TcArgs {
   int M, N, K, X;
   float inv_norm;
   int conjA, conjB, accumulate;
-  int a_qb, b_qb;  // bins per block of A and B (16, or 4 for the quad-blocked forward spectra)
+  int a_qb, b_qb, d_qb;  // bins per block of A, B and D
 };
 
 // hi = the operand rounded to tf32 (10-bit mantissa, low 13 bits zero: exactly what the
@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(kTcThreads, TcCfg<BN>::MIN_BLOCKS) cgemm_tc_ke
             const int n = n0 + col + j;
             if (n < g.N) {
               float4* dst = reinterpret_cast<float4*>(g.D + (long long)m * g.d_ms + (long long)n * g.d_ns +
-                                                      (long long)(x0 >> 4) * g.d_bs + (x0 & 15));
+                                                      (long long)(x0 / g.d_qb) * g.d_bs + (x0 % g.d_qb));
               float4 o0 = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
                                       v[1][1][j] * g.inv_norm);
               float4 o1 = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
@@ -414,12 +414,12 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
 // D[m][n][x] (+)= inv_norm * sum_k opA(A[m][k][x]) opB(B[n][k][x]); strides in complex elements
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-             bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb) {
+             bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb) {
   // first choice: the persistent TMA-fed kernel (cgemm_tma.cu); this file's gather kernel remains
   // for drivers without the tensor-map encoder and as the comparison point (mode 2)
-  if (g_mode == 0 && cgemm_tma_supported(a, a_rs, a_ks, a_bs, b, b_rs, b_ks, b_bs, d, d_ms, d_ns, d_bs, M, N, K, X)) {
+  if (g_mode == 0 && cgemm_tma_supported(a, a_rs, a_ks, a_bs, b, b_rs, b_ks, b_bs, d, d_ms, d_ns, d_bs, d_qb, M, N, K, X)) {
     const int rc = cgemm_tma(a, a_rs, a_ks, conjA, b, b_rs, b_ks, conjB, d, d_ms, d_ns, M, N, K, X, inv_norm, accumulate,
-                             s, a_bs, b_bs, d_bs, a_qb, b_qb);
+                             s, a_bs, b_bs, d_bs, a_qb, b_qb, d_qb);
     if (rc >= 0) return rc;
   }
   TcArgs t;
@@ -428,7 +428,7 @@ int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const f
   t.D = reinterpret_cast<float2*>(d), t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
-  t.a_qb = a_qb, t.b_qb = b_qb;
+  t.a_qb = a_qb, t.b_qb = b_qb, t.d_qb = d_qb;
   // (two resident blocks per SM with BN = 32 were measured slower than one with BN = 64 for wide batches)
   if (N <= 16) return launch_tc<16>(t, s);
   if (N <= 32) return launch_tc<32>(t, s);

@@ -162,7 +162,7 @@ struct TmaArgs {
   long long b_rs, b_ks, b_bs;  // B[n][k][x]
   int a_qb, b_qb;
   int M, N, K, X;
-  int d_blocked;  // bin-blocked result: store coordinates (2*(x%16), m, n, x/16), else (2x, m, n, 0)
+  int d_qb;  // bins per block of D; 0 = bins innermost (store coordinates (2x, m, n, 0) instead of (2*(x % d_qb), m, n, x / d_qb))
   float inv_norm;
   int conjA, conjB, accumulate;
   int n_tiles, m_tiles, total_tiles;
@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
         break;
       }
       tc_fence_after();
-      const int dx = g.d_blocked ? 2 * (x0 & 15) : 2 * x0, db = g.d_blocked ? (x0 >> 4) : 0;
+      const int dx = g.d_qb ? 2 * (x0 % g.d_qb) : 2 * x0, db = g.d_qb ? x0 / g.d_qb : 0;
       const int mrow = m0 + lq * 32;
       const int ncols = (g.N - n0 < BN) ? g.N - n0 : BN;
       const int nch = (mrow < g.M) ? (ncols + 3) / 4 : 0;  // chunks of 4 columns this warp stores
@@ -506,16 +506,16 @@ EncodeTiledFn encoder() {
   return fn;
 }
 
-// 4-D view of an operand whose bin x of element (row, k) sits at p + (x/16)*bs + x%16 + row*rs + k*ks
-// complex elements: (floats of the bins, rows, k, 16-bin blocks).  bs == 16 is the natural
-// bins-innermost layout, one "block" holding all X bins.
-bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long long bs, int rows, int kcount, int X,
-              int box_rows, int box_k) {
+// 4-D view of a tensor whose bin x of element (row, k) sits at p + (x/qb)*bs + x%qb + row*rs + k*ks
+// complex elements: (floats of a block's bins, rows, k, blocks).  bs == qb is the natural
+// bins-innermost layout, seen as one "block" holding all X bins.
+bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long long bs, int qb, int rows, int kcount,
+              int X, int box_rows, int box_k) {
   EncodeTiledFn enc = encoder();
   if (!enc) return false;
-  const bool blocked = bs != 16;
-  const cuuint64_t dims[4] = {(cuuint64_t)(blocked ? 32 : 2 * X), (cuuint64_t)rows, (cuuint64_t)kcount,
-                              (cuuint64_t)(blocked ? X / 16 : 1)};
+  const bool blocked = bs != qb;
+  const cuuint64_t dims[4] = {(cuuint64_t)(blocked ? 2 * qb : 2 * X), (cuuint64_t)rows, (cuuint64_t)kcount,
+                              (cuuint64_t)(blocked ? X / qb : 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)rs * 8, (cuuint64_t)ks * 8, (cuuint64_t)(blocked ? bs * 8 : (long long)X * 8)};
   const cuuint32_t box[4] = {8, (cuuint32_t)box_rows, (cuuint32_t)box_k, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -546,9 +546,9 @@ int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
 
 bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,
                          long long b_ks, long long b_bs, const float* d, long long d_ms, long long d_ns, long long d_bs,
-                         int M, int N, int K, int X) {
+                         int d_qb, int M, int N, int K, int X) {
   if (X % 4 != 0 || M < 1 || N < 1 || K < 1) return false;
-  if ((a_bs != 16 || b_bs != 16 || d_bs != 16) && X % 16 != 0) return false;
+  if (d_qb < 4 || d_qb % 4 != 0 || (d_bs != d_qb && X % d_qb != 0)) return false;
   // tensor copies: 16-byte aligned bases and strides (an even number of complex elements)
   const long long st[9] = {a_rs, a_ks, a_bs, b_rs, b_ks, b_bs, d_ms, d_ns, d_bs};
   for (long long v : st)
@@ -560,10 +560,10 @@ bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long lo
 
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb) {
+              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb) {
   const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
   alignas(64) CUtensorMap md;
-  if (!make_map(&md, d, d_ms, d_ns, d_bs, M, N, X, 32, 4)) {
+  if (!make_map(&md, d, d_ms, d_ns, d_bs, d_qb, M, N, X, 32, 4)) {
     return -1;  // the caller falls back to the gather kernel
   }
   TmaArgs t;
@@ -571,7 +571,7 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.B = reinterpret_cast<const float2*>(b), t.b_rs = b_rs, t.b_ks = b_ks, t.b_bs = b_bs;
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.a_qb = a_qb, t.b_qb = b_qb;
-  t.d_blocked = d_bs != 16;
+  t.d_qb = (d_bs != d_qb) ? d_qb : 0;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
   if (BN == 16) return launch_tma<16>(md, t, s);

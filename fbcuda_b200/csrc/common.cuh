@@ -26,19 +26,20 @@ struct RealView {
 // A batch of complex matrices stored as floats: element (b, r, c, z) at
 // p[b*sb + r*sr + c*sc + z*sz], z = 0 (re) or 1 (im).
 //
-// blk_planes > 0 selects the bin-blocked layout the convolution workspace uses instead: the
-// (N/2+1)*N bins of a plane are cut into blocks of 16 (128 bytes) and block xb of plane b sits
-// at p[((xb * blk_planes + b) * 16 + x % 16) * 2], so that for a fixed block all planes are
-// contiguous -- what the per-bin contraction reads.  sb/sr/sc/sz are ignored then.
-// blk_bins = 4 is the same with blocks of 4 bins (32 bytes): p[((x/4 * blk_planes + b) * 4 + x % 4) * 2],
-// the layout of the contraction's operands (a 4-bin tile of consecutive planes is one contiguous
-// run); only the forward transforms write it.
+// blk_planes > 0 selects the bin-blocked layouts of the convolution workspace instead: the
+// (N/2+1)*N stored bins of a plane are cut into blocks of blk_bins bins and block xb of plane b
+// sits at p[((xb * blk_planes + b) * blk_bins + x % blk_bins) * 2], so that for a fixed block all
+// planes are adjacent.  sb/sr/sc/sz are ignored then.  Two block sizes are in use:
+//   blk_bins = 4   the contraction's operands (written by the forward transforms): a 4-bin tile of
+//                  consecutive planes is one contiguous run;
+//   blk_bins = N   the contraction's result (read by the inverse transforms): a block is one stored
+//                  row of the spectrum, fetched by one bulk copy.
 struct CplxView {
   float* p;
   long long sb;
   int sr, sc, sz;
   long long blk_planes = 0;
-  int blk_bins = 16;
+  int blk_bins = 4;
 };
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

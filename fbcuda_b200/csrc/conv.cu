@@ -94,8 +94,8 @@ int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, bool block
   RealView v;
   int count;
   if (!as_images(t, &v, &count)) return kUnsupportedDimension;
-  // the contraction's result: 16-bin blocks (128-byte pieces for the inverse transform's row copies)
-  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0, 16);
+  // the contraction's result: one stored row per block (one bulk copy per row in the inverse transform)
+  const CplxView sv = spectrum_view(spec, n, blocked ? count : 0, n);
   if (n <= 32) return fft2d_small_inverse(n, sv, v, count, padL, padU, s);
   return fft2d_large_inverse(n, sv, v, count, padL, padU, s);
 }
@@ -115,9 +115,9 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
              long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s) {
   const long long X = bins_of(n);
   if (blocked) {
-    // operands in 4-bin blocks (plane stride 4 complex), result in 16-bin blocks
-    return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * 16, d_pn * 16, M, N, K, (int)X,
-                    inv_norm, false, s, a_planes * 4, b_planes * 4, d_planes * 16, 4, 4);
+    // operands in 4-bin blocks (plane stride 4 complex), result in blocks of one stored row (n bins)
+    return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K, (int)X,
+                    inv_norm, false, s, a_planes * 4, b_planes * 4, d_planes * n, 4, 4, n);
   }
   // natural layout: D[m][n] = sum_k opA(A[m][k]) opB(B[n][k]) = cgemm_bins with A' = A (rows m),
   // B' = B^T: C[i=m][j=n] = sum_k opA(A[i][k]) * opB'(B'[k][j]), B'[k][j] = B[j][k] -> "conj-transposed" flag

@@ -122,7 +122,7 @@ __device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
 template <int N, bool IN_BULK, bool FULL = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
-                                                                                int padU, long long blk_planes, int blk_bins) {
+                                                                                int padU, long long blk_planes) {
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
@@ -285,20 +285,13 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     fence_async_smem();
     block_sync<T>();
     float* dst = out + (long long)b * out_sb;
-    if (blk_planes && blk_bins == 4) {
+    if (blk_planes) {
       // 4-bin blocks (contraction operands): 32-byte pieces, planes adjacent; two lanes per piece
       constexpr int QR = N / 4;
       for (int i = threadIdx.x; i < (H + 1) * QR * 2; i += T) {
         const int half = i & 1, piece = i >> 1;
         const float4 v = *reinterpret_cast<const float4*>(tile + (piece / QR) * PO + (piece % QR) * 4 + half * 2);
         *reinterpret_cast<float4*>(out + ((long long)piece * blk_planes + b) * 8 + half * 4) = v;
-      }
-    } else if (blk_planes) {
-      // bin-blocked layout (convolution workspace): 128-byte pieces, planes adjacent
-      constexpr int CB = N / 16;
-      for (int i = threadIdx.x; i < (H + 1) * CB; i += T) {
-        const int kx = i / CB, cb = i % CB;
-        bulk_s2g(out + ((long long)i * blk_planes + b) * 32, smem_u32(tile + kx * PO + cb * 16), 128);
       }
     } else {
       for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
@@ -345,11 +338,9 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)((H + 1) * N * 8));
     block_sync<T>();
     if (blk_planes) {
-      constexpr int CB = N / 16;
-      for (int i = threadIdx.x; i < (H + 1) * CB; i += T) {
-        const int kx = i / CB, cb = i % CB;
-        bulk_g2s(smem_u32(tile + kx * PO + cb * 16), in + ((long long)i * blk_planes + b) * 32, 128, bar);
-      }
+      // row blocks: stored row kx of plane b sits at ((kx * planes + b) * N) complex values
+      for (int kx = threadIdx.x; kx <= H; kx += T)
+        bulk_g2s(smem_u32(tile + kx * PO), in + ((long long)kx * blk_planes + b) * (2 * N), N * 8, bar);
     } else {
       const float* src = in + (long long)b * in_sb;
       for (int kx = threadIdx.x; kx <= H; kx += T) bulk_g2s(smem_u32(tile + kx * PO), src + (long long)kx * (2 * N), N * 8, bar);
@@ -488,11 +479,11 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
   if (in_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
-    fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
+    fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   } else if (in_bulk) {
-    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
+    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   } else {
-    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, out.blk_bins);
+    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
@@ -528,11 +519,13 @@ bool fft2d_coop_supported(int n, const CplxView& c) {
 }
 
 int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (out.blk_planes && out.blk_bins != 4) return kUnsupportedDimension;  // forward transforms write 4-bin blocks
   if (n == 64) return launch_fwd<64>(in, out, B, padL, padU, s);
   return launch_fwd<128>(in, out, B, padL, padU, s);
 }
 
 int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
+  if (in.blk_planes && in.blk_bins != n) return kUnsupportedDimension;  // inverse transforms read row blocks
   if (n == 64) return launch_inv<64>(in, out, B, padL, padU, s);
   return launch_inv<128>(in, out, B, padL, padU, s);
 }

@@ -24,7 +24,7 @@ constexpr int kMaxSupport = 8;
 template <int N>
 __device__ __forceinline__ long long bin_offset(const CplxView& v, long long P, int r, int c) {
   if (v.blk_planes) {
-    const int x = r * N + c, sh = v.blk_bins == 4 ? 2 : 4;  // blocks of 4 or 16 bins
+    const int x = r * N + c, sh = 31 - __clz(v.blk_bins);  // blocks of 4 or N bins (powers of two)
     return ((((long long)(x >> sh) * v.blk_planes + P) << sh) + (x & ((1 << sh) - 1))) * 2;
   }
   return P * v.sb + (long long)r * v.sr + (long long)c * v.sc;

@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
     if (OUT_BULK) {
       fence_async_smem();
       __syncwarp();
-      if (N >= 16 && out.blk_planes && out.blk_bins == 4) {
+      if (N >= 16 && out.blk_planes) {
         // 4-bin blocks: every 32-byte piece of a row goes next to the same piece of the neighbouring
         // planes; two lanes per piece, the images of the warp adjacent in memory
         constexpr int QR = N / 4;
@@ -155,17 +155,6 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
           }
         }
         __syncwarp();
-      } else if (N >= 16 && out.blk_planes) {
-        // bin-blocked layout: every 16-bin (128-byte) piece of a row goes next to the same piece
-        // of the neighbouring planes
-        constexpr int CB = N >= 16 ? N / 16 : 1;
-        for (int r = lane; r < IPW * ROWS * CB; r += 32) {
-          const int img = r / (ROWS * CB), rem = r % (ROWS * CB), row = rem / CB, cb = rem % CB;
-          const int bb = task * IPW + img;
-          if (bb < B)
-            bulk_s2g(out.p + ((long long)(row * CB + cb) * out.blk_planes + bb) * 32,
-                     smem_u32(buf + img * IS + row * RS + cb * 16), 128);
-        }
       } else if (RS == N) {
         // rows are contiguous in shared memory: one copy per image
         if (lane < IPW && task * IPW + lane < B)
@@ -226,11 +215,11 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
     if (lane == 0) mbar_expect_tx(bar, (unsigned)(imgs * ROWS * N * 8));
     __syncwarp();
     if (N >= 16 && in.blk_planes) {
-      constexpr int CB = N >= 16 ? N / 16 : 1;
-      for (int r = lane; r < imgs * ROWS * CB; r += 32) {
-        const int img = r / (ROWS * CB), rem = r % (ROWS * CB), row = rem / CB, cb = rem % CB;
-        bulk_g2s(smem_u32(dstbuf + img * IS + row * RS + cb * 16),
-                 in.p + ((long long)(row * CB + cb) * in.blk_planes + task * IPW + img) * 32, 128, bar);
+      // row blocks: stored row `row` of plane b sits at ((row * planes + b) * N) complex values
+      for (int r = lane; r < imgs * ROWS; r += 32) {
+        const int img = r / ROWS, row = r % ROWS;
+        bulk_g2s(smem_u32(dstbuf + img * IS + row * RS),
+                 in.p + ((long long)row * in.blk_planes + task * IPW + img) * (2 * N), N * 8, bar);
       }
     } else if (RS == N) {
       // rows are contiguous in shared memory: one copy per image
@@ -382,6 +371,7 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
 
 int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
   if (B <= 0) return kSuccess;
+  if (out.blk_planes && out.blk_bins != 4) return kUnsupportedDimension;  // forward transforms write 4-bin blocks
   switch (n) {
     case 8:
       return launch_fwd<8>(in, out, B, padL, padU, s);
@@ -396,6 +386,7 @@ int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, i
 
 int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
   if (B <= 0) return kSuccess;
+  if (in.blk_planes && in.blk_bins != n) return kUnsupportedDimension;  // inverse transforms read row blocks
   switch (n) {
     case 8:
       return launch_inv<8>(in, out, B, padL, padU, s);

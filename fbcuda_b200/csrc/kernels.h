@@ -58,14 +58,14 @@ bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const fl
 int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
              bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
              bool accumulate, cudaStream_t s, long long a_bs = 16, long long b_bs = 16, long long d_bs = 16, int a_qb = 16,
-             int b_qb = 16);
+             int b_qb = 16, int d_qb = 16);
 // persistent TMA-fed version (cgemm_tma.cu); returns -1 when a tensor map cannot be encoded
 bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,
                          long long b_ks, long long b_bs, const float* d, long long d_ms, long long d_ns, long long d_bs,
-                         int M, int N, int K, int X);
+                         int d_qb, int M, int N, int K, int X);
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
-              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb);
+              bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb);
 int read_device_error_tma();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only
 void set_contraction_mode(int mode);
