@@ -8,9 +8,11 @@ One JSON line on stdout (rank 0).  A step is one pass of the hot path over one
 batch of synthetic input:
 
 * workload "fft2d" (default): one batched fbfft2D call over 1 GiB of fp32 images
-  per GPU (the N = 32 point of the BASELINE size sweep; other points with
-  --fft-size).  Metric: algorithmic GB/s, (4*h*w + 8*N*(N/2+1)) bytes per image.
-  The batch shards over GPUs with no communication (weak scaling).
+  per GPU.  Default shape: 27x27 images zero-padded to FFT size 32 (the shape of the
+  batched-2D configuration, its 128 x 64 planes scaled up until the input exceeds
+  L2 by far); --fft-size N selects a point of the size sweep (N x N images).
+  Metric: algorithmic GB/s, (4*h*w + 8*N*(N/2+1)) bytes per image.  The batch
+  shards over GPUs with no communication (weak scaling).
 * workload "conv": updateOutput + updateGradInput + accGradParameters of the
   FFT-64 layer (B=64, C=O=128, 56x56, 3x3, pad 1), batch sharded over GPUs,
   frequency-domain weight gradient all-reduced with NCCL.  Metric: images/s.
@@ -37,7 +39,7 @@ if ROOT not in sys.path:
 GIB = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the
 # ncu capture summarised in profiles/ (captured on 65536 images, scaled by images per launch)
-NCU_TRAFFIC_BYTES_PER_IMAGE = {32: 7609.0, 64: 30170.0}
+NCU_TRAFFIC_BYTES_PER_IMAGE = {(32, 32): 7609.0, (64, 64): 30170.0}
 
 
 def measured_peak_gbs():
@@ -105,8 +107,20 @@ def fft_bytes_per_image(n, h, w):
     return 4 * h * w + 8 * n * (n // 2 + 1)
 
 
+def image_hw(args):
+    """27x27 (zero-padded to 32) for the default size, full N x N images for the other sweep points."""
+    if args.image_hw:
+        return args.image_hw
+    return 27 if args.fft_size == 32 else args.fft_size
+
+
+def workload_name(n, hw, b):
+    pad = f" zero-padded to {n}x{n}" if hw != n else ""
+    return f"fbfft2D N={n}, 1 GiB fp32 input per GPU ([{b}][{hw}][{hw}]{pad} -> [{b}][{n // 2 + 1}][{n}] complex)"
+
+
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_fft2d_sample(n, seconds_target=12.0):
+def cpu_fft2d_sample(n, hw, seconds_target=12.0):
     """Times the scalar restatement of the reference algorithm on all host cores on a
     bounded sample of the workload; returns (GB/s, cores, description)."""
     import numpy as np
@@ -114,7 +128,7 @@ def cpu_fft2d_sample(n, seconds_target=12.0):
     cores = max(1, cpuref.hardware_threads())
     rng = np.random.default_rng(1)
     b = max(cores * 64, 4096 * 32 * 32 // (n * n))
-    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    x = rng.uniform(-1, 1, (b, hw, hw)).astype(np.float32)
     out = np.zeros((b, n // 2 + 1, n, 2), np.float32)
     cpuref.fbfft2d(x, n, threads=cores, out=out)       # warm-up, page faults
     times = []
@@ -124,8 +138,8 @@ def cpu_fft2d_sample(n, seconds_target=12.0):
         cpuref.fbfft2d(x, n, threads=cores, out=out)
         times.append(time.perf_counter() - t0)
     med = statistics.median(times)
-    gbs = b * fft_bytes_per_image(n, n, n) / med / 1e9
-    return gbs, cores, f"fbfft2D N={n} over {b} images of {n}x{n} (median of {len(times)} runs, {med*1e3:.1f} ms each)", med
+    gbs = b * fft_bytes_per_image(n, hw, hw) / med / 1e9
+    return gbs, cores, f"fbfft2D N={n} over {b} images of {hw}x{hw} (median of {len(times)} runs, {med*1e3:.1f} ms each)", med
 
 
 def run_reference(args):
@@ -164,9 +178,10 @@ def run_reference(args):
     import numpy as np
     from oracle import cpuref
     cores = max(1, cpuref.hardware_threads())
+    hw = image_hw(args)
     b = max(cores * 64, 8192 * 32 * 32 // (n * n))
     rng = np.random.default_rng(1)
-    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    x = rng.uniform(-1, 1, (b, hw, hw)).astype(np.float32)
     out = np.zeros((b, n // 2 + 1, n, 2), np.float32)
     times = []
     for it in range(args.warmup + args.steps):
@@ -175,14 +190,14 @@ def run_reference(args):
         if it >= args.warmup:
             times.append(time.perf_counter() - t0)
     ms = statistics.mean(times) * 1e3
-    gbs = b * fft_bytes_per_image(n, n, n) / (ms / 1e3) / 1e9
+    gbs = b * fft_bytes_per_image(n, hw, hw) / (ms / 1e3) / 1e9
     line = {"impl": "reference", "metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"fbfft2D N={n}, 1 GiB fp32 input per GPU ([{GIB // (4 * n * n)}][{n}][{n}])",
+            "config": {"workload": workload_name(n, hw, GIB // (4 * hw * hw)),
                        "sample": f"{b} images per step on {cores} host threads"},
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                             "sample": f"{b} images of {n}x{n} per step"},
+                             "sample": f"{b} images of {hw}x{hw} per step"},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
@@ -244,15 +259,16 @@ def run_fft2d(args, world, rank, local):
     import torch
     import fbcuda_b200 as fb
     n = args.fft_size
-    b = GIB // (4 * n * n)
+    hw = image_hw(args)
+    b = GIB // (4 * hw * hw)
     if args.profile_case:
         # small case for an ncu capture: 256 MiB of input (still larger than L2), the
         # timed launches only
         b //= 4
     gen = torch.Generator(device="cuda").manual_seed(1 + rank)
-    x = torch.rand((b, n, n), device="cuda", generator=gen) * 2 - 1
+    x = torch.rand((b, hw, hw), device="cuda", generator=gen) * 2 - 1
     spec = torch.empty((b, n // 2 + 1, n, 2), device="cuda")
-    per_image = fft_bytes_per_image(n, n, n)
+    per_image = fft_bytes_per_image(n, hw, hw)
 
     def step():
         fb.fft2d_r2c(n, x, spec)
@@ -274,11 +290,11 @@ def run_fft2d(args, world, rank, local):
     gbs = world * b * per_image / (ms / 1e3) / 1e9
     if args.profile_case:
         return {"metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
-                "config": {"workload": f"profile case: fbfft2D N={n} over {b} images"}, "clocks": clocks}
+                "config": {"workload": f"profile case: fbfft2D N={n} over {b} images of {hw}x{hw}"}, "clocks": clocks}
 
     # end to end through the public call with HOST buffers: H2D of the images, the
     # transform, D2H of the spectrum, every step
-    xh = torch.empty((b, n, n), dtype=torch.float32).pin_memory()
+    xh = torch.empty((b, hw, hw), dtype=torch.float32).pin_memory()
     xh.copy_(x.cpu())
     sh = torch.empty((b, n // 2 + 1, n, 2), dtype=torch.float32).pin_memory()
 
@@ -289,13 +305,13 @@ def run_fft2d(args, world, rank, local):
 
     ms_e2e = time_steps(step_e2e, max(2, args.steps // 4), 3, world)
     e2e = {"value": world * b * per_image / (ms_e2e / 1e3) / 1e9, "unit": "GB/s",
-           "h2d_bytes_per_step": b * n * n * 4, "d2h_bytes_per_step": b * (n // 2 + 1) * n * 8,
+           "h2d_bytes_per_step": b * hw * hw * 4, "d2h_bytes_per_step": b * (n // 2 + 1) * n * 8,
            "ms_per_step": ms_e2e}
     del xh, sh
 
     peak, how = measured_peak_gbs()
     achieved = b * per_image / (ms / 1e3) / 1e9      # per GPU; one launch per step
-    traffic = NCU_TRAFFIC_BYTES_PER_IMAGE.get(n)
+    traffic = NCU_TRAFFIC_BYTES_PER_IMAGE.get((n, hw))
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {how}", "frac_of_8TBs": achieved / 8000.0,
                 "traffic": traffic * b if traffic else None, "algorithmic_bytes_per_launch": b * per_image,
@@ -303,29 +319,35 @@ def run_fft2d(args, world, rank, local):
                 "traffic_source": "ncu capture on the profile case (profiles/), scaled by images per launch" if traffic else None}
     extra = {}
     if args.extras and rank == 0 and world == 1:
-        extra = run_extras(args, x, spec, n)
+        extra = run_extras(args, x, spec, n, hw)
     line = {"metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"fbfft2D N={n}, 1 GiB fp32 input per GPU ([{b}][{n}][{n}] -> [{b}][{n // 2 + 1}][{n}] complex)",
+            "config": {"workload": workload_name(n, hw, b),
                        "l2": "inputs (1 GiB) and outputs exceed the 126 MB L2, no flush needed",
                        "parallelism": f"batch sharded over {world} GPU(s), no collective"},
             "e2e": e2e, "gpu_launches": args.steps, "roofline": roofline, "clocks": clocks}
     if rank == 0 and world == 1:
-        gb, cores, sample, _ = cpu_fft2d_sample(n)
+        gb, cores, sample, _ = cpu_fft2d_sample(n, hw)
         line["cpu_baseline"] = {"value": gb, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
     if extra:
         line["extra"] = extra
     return line
 
 
-def run_extras(args, x, spec, n0):
-    """Size sweep forward + inverse (1 GiB input each) on one GPU, for the record."""
+def run_extras(args, x, spec, n0, hw0):
+    """The inverse of the default workload (fbifft2D with crop back to the image size), then the
+    size sweep forward + inverse (1 GiB of N x N input each) on one GPU, for the record."""
     import torch
     import fbcuda_b200 as fb
-    del x, spec
-    torch.cuda.empty_cache()
     peak, _ = measured_peak_gbs()
+    back = torch.empty_like(x)
+    ms_i = time_steps(lambda: fb.fft2d_c2r(n0, spec, back), 10, 3, 1)
+    inv_gbs = x.shape[0] * fft_bytes_per_image(n0, hw0, hw0) / ms_i / 1e6
+    inverse = {"workload": f"fbifft2D N={n0} -> [{x.shape[0]}][{hw0}][{hw0}]", "us": ms_i * 1e3, "gbs": inv_gbs,
+               "frac_of_measured": inv_gbs / peak}
+    del x, spec, back
+    torch.cuda.empty_cache()
     sweep = {}
     for n in (8, 16, 32, 64, 128, 256):
         b = GIB // (4 * n * n)
@@ -343,7 +365,7 @@ def run_extras(args, x, spec, n0):
         sweep[str(n)] = entry
         del x, spec, back
         torch.cuda.empty_cache()
-    return {"sweep_1GiB": sweep}
+    return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep}
 
 
 def run_conv(args, world, rank, local):
@@ -434,6 +456,7 @@ def main():
     ap.add_argument("--conv-config", default="conv4", choices=["conv3", "conv4", "conv5"])
     ap.add_argument("--dw-mode", default="frequency", choices=["frequency", "spatial"])
     ap.add_argument("--fft-size", type=int, default=32)
+    ap.add_argument("--image-hw", type=int, default=0, help="image height = width (default: 27 for FFT size 32, else the FFT size)")
     ap.add_argument("--extras", type=int, default=1)
     ap.add_argument("--profile-case", action="store_true", help="small fft2d case for profiler captures")
     ap.add_argument("--inverse", action="store_true", help="profile case: time fbifft2D instead of fbfft2D")
