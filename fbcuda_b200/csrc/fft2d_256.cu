@@ -1,0 +1,164 @@
+// Forward 2-D real-to-complex FFT for N = 256 on contiguous tensors, in the reference's layout
+// for this size class: transposed spectrum [B][kx in 0..128][ky in 0..255] (what its two calls,
+// fbfft/FBFFT2D-inl.cuh:597-617 then :627-669, leave behind).
+//
+// A 256 x 256 image and its spectrum (264 KB) do not fit one SM's shared memory, so the transform
+// keeps the reference's two passes, but without its separate [B][N][N/2+1] buffer: the row pass
+// writes its result transposed straight into the output tensor, the column pass transforms the
+// output's lines in place.  Both passes hold every line in registers, shared by 4 neighbouring lane
+// groups of a warp (radix-4 step, one all-to-all by __shfl_xor_sync, 64-point FFT per lane with
+// compile-time twiddles: coop_fft.cuh).
+//   rows     a block takes 64 consecutive rows of one image; rows 2l and 2l+1 travel as re/im of one
+//            complex line (a warp holds 8 lines); the lines' transforms Z are parked in shared
+//            memory, then thread (kx, l) separates the two real spectra, A = (Z[kx] + conj Z[N-kx])/2
+//            and B = (Z[kx] - conj Z[N-kx])/2i, and stores both as 16 bytes at out[kx][2l..2l+1]:
+//            a warp writes 512 contiguous bytes.
+//   columns  a warp takes 8 lines out[kx][*] (2 KB each, contiguous), transforms them and stores
+//            X[4k + q] from lane group q: every store instruction fills whole 32-byte sectors.
+// HBM traffic is twice the algorithmic bytes (the spectrum is written, read and written again).
+#include "coop_fft.cuh"
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+constexpr int N256 = 256, R256 = 64, Q256 = 4, P256 = R256 / Q256, LP256 = 32 / Q256;
+constexpr int kRowsThreads = 128;                       // 4 warps x 8 lines = 32 lines = 64 rows
+constexpr int kLinesPerBlock = (kRowsThreads / 32) * LP256;
+constexpr int PZ = N256 + 2;                            // line pitch in shared memory (complex values)
+
+// FULL: the images are contiguous 256 x 256 without padding (16-byte loads, no predicates)
+template <bool FULL>
+__global__ void __launch_bounds__(kRowsThreads, 3) fft256_rows_kernel(RealView in, float* __restrict__ out, long long out_sb,
+                                                                       int B, int padL, int padU) {
+  extern __shared__ __align__(16) float2 zs[];  // [32 lines][PZ]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP256, line = warp * LP256 + (lane % LP256);
+  float2 lf[Q256];
+  lane_factors<Q256, false>(q, lf);
+  const int bands = N256 / (2 * kLinesPerBlock);  // 4
+  for (long long work = blockIdx.x; work < (long long)B * bands; work += gridDim.x) {
+    const long long b = work / bands;
+    const int band = (int)(work % bands);
+    const int y0 = band * 2 * kLinesPerBlock + 2 * line;  // canvas rows y0 (re) and y0 + 1 (im)
+    float2 a[R256];
+    const float* src = in.p + b * in.sb;
+    if constexpr (FULL) {
+      const float4* r0 = reinterpret_cast<const float4*>(src + (long long)y0 * N256 + P256 * q);
+      const float4* r1 = reinterpret_cast<const float4*>(src + (long long)(y0 + 1) * N256 + P256 * q);
+#pragma unroll
+      for (int m = 0; m < Q256; ++m) {
+#pragma unroll
+        for (int j4 = 0; j4 < P256 / 4; ++j4) {
+          const float4 u = __ldg(r0 + m * (R256 / 4) + j4), v = __ldg(r1 + m * (R256 / 4) + j4);
+          a[m * P256 + j4 * 4 + 0] = make_float2(u.x, v.x);
+          a[m * P256 + j4 * 4 + 1] = make_float2(u.y, v.y);
+          a[m * P256 + j4 * 4 + 2] = make_float2(u.z, v.z);
+          a[m * P256 + j4 * 4 + 3] = make_float2(u.w, v.w);
+        }
+      }
+    } else {
+      const unsigned ya = (unsigned)(y0 - padU), yb = (unsigned)(y0 + 1 - padU);
+      const bool oka = ya < (unsigned)in.h, okb = yb < (unsigned)in.h;
+      const float* r0 = src + (long long)ya * in.sy;
+      const float* r1 = src + (long long)yb * in.sy;
+#pragma unroll
+      for (int m = 0; m < Q256; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P256; ++jl) {
+          const unsigned x = (unsigned)(jl + P256 * q + R256 * m - padL);
+          const bool okx = x < (unsigned)in.w;
+          a[m * P256 + jl].x = (oka && okx) ? __ldg(r0 + (long long)x * in.sx) : 0.f;
+          a[m * P256 + jl].y = (okb && okx) ? __ldg(r1 + (long long)x * in.sx) : 0.f;
+        }
+      }
+    }
+    coop_fft<N256, R256, Q256, false>(a, q, lf);
+    __syncthreads();  // the previous band's lines have been read
+    static_for<R256>([&](auto kc) {
+      constexpr int k = decltype(kc)::value;
+      zs[line * PZ + Q256 * k + q] = a[brev(k, R256)];
+    });
+    __syncthreads();
+    // out[b][kx][y0 .. y0+1] for the block's 32 lines: line fastest, 16 bytes per thread
+    float* dst = out + b * out_sb + (long long)band * 4 * kLinesPerBlock;  // 2 rows x 2 floats per line
+    for (int e = threadIdx.x; e < (N256 / 2 + 1) * kLinesPerBlock; e += kRowsThreads) {
+      const int kx = e / kLinesPerBlock, l = e % kLinesPerBlock;
+      const float2 z = zs[l * PZ + kx], m = zs[l * PZ + ((N256 - kx) & (N256 - 1))];
+      const float4 v = make_float4(0.5f * (z.x + m.x), 0.5f * (z.y - m.y), 0.5f * (z.y + m.y), 0.5f * (m.x - z.x));
+      *reinterpret_cast<float4*>(dst + (long long)kx * (2 * N256) + 4 * l) = v;
+    }
+  }
+}
+
+// in-place transform of `lines` contiguous lines of 256 complex values
+__global__ void __launch_bounds__(128, 3) fft256_cols_kernel(float* __restrict__ data, long long lines) {
+  const int lane = threadIdx.x & 31, q = lane / LP256;
+  float2 lf[Q256];
+  lane_factors<Q256, false>(q, lf);
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w * LP256 < lines; w += warps) {
+    const long long l = w * LP256 + (lane % LP256);
+    const bool live = l < lines;
+    float2 a[R256];
+    float* base = data + (live ? l : 0) * (2 * N256);
+    const float4* src = reinterpret_cast<const float4*>(base + 2 * P256 * q);
+#pragma unroll
+    for (int m = 0; m < Q256; ++m) {
+#pragma unroll
+      for (int j2 = 0; j2 < P256 / 2; ++j2) {
+        const float4 u = src[m * R256 / 2 + j2];  // two complex values
+        a[m * P256 + 2 * j2] = make_float2(u.x, u.y);
+        a[m * P256 + 2 * j2 + 1] = make_float2(u.z, u.w);
+      }
+    }
+    coop_fft<N256, R256, Q256, false>(a, q, lf);
+    if (live) {
+      float2* dst = reinterpret_cast<float2*>(base) + q;
+      static_for<R256>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        dst[Q256 * k] = a[brev(k, R256)];
+      });
+    }
+  }
+}
+
+}  // namespace
+
+bool fft2d_256_supported(const RealView& in, const CplxView& out, int B) {
+  if (out.blk_planes) return false;
+  const bool out_ok = out.sz == 1 && out.sc == 2 && out.sr == 2 * N256 && out.sb == (long long)(N256 / 2 + 1) * 2 * N256 &&
+                      aligned16(out.p);
+  return out_ok && B >= 1 && in.h <= N256 && in.w <= N256;
+}
+
+int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int smem = kLinesPerBlock * PZ * (int)sizeof(float2);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(fft256_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(fft256_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured[dev] = true;
+  }
+  const long long work = (long long)B * 4;
+  const int cap = sm_count() * 3;
+  const int grid = work < cap ? (int)work : cap;
+  const bool full = in.sx == 1 && in.sy == N256 && in.h == N256 && in.w == N256 && padL == 0 && padU == 0 &&
+                    (in.sb % 4) == 0 && aligned16(in.p);
+  if (full) {
+    fft256_rows_kernel<true><<<grid, kRowsThreads, smem, s>>>(in, out.p, out.sb, B, padL, padU);
+  } else {
+    fft256_rows_kernel<false><<<grid, kRowsThreads, smem, s>>>(in, out.p, out.sb, B, padL, padU);
+  }
+  if (cudaPeekAtLastError() != cudaSuccess) return kCudaError;
+  const long long lines = (long long)B * (N256 / 2 + 1);
+  const long long wblocks = (lines + 4 * LP256 - 1) / (4 * LP256);
+  const int grid2 = wblocks < cap ? (int)wblocks : cap;
+  fft256_cols_kernel<<<grid2, 128, 0, s>>>(out.p, lines);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+}  // namespace fbfft_b200

@@ -20,6 +20,7 @@
 //            The finished tile leaves through cp.async.bulk row stores.
 //   inverse  the same two passes backwards; the spectrum rows arrive through
 //            cp.async.bulk copies completing on an mbarrier (bounded wait).
+#include "coop_fft.cuh"
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "kernels.h"
 
@@ -41,59 +42,6 @@ struct CoopCfg<128> {
   static constexpr int R = 64, Q = 2, PM = 66, PO = 130, BLOCKS_PER_SM = 3, MIN_BLOCKS = 3;
 };
 
-// Length-N = R*Q complex FFT shared by Q lanes (lane index bits above log2(32/Q)
-// select q; Q = 1 is a plain in-register FFT).  In: a[m*P + jl] = x[jl + P*q + R*m],
-// P = R/Q.  Out: a[brev(k, R)] = X[Q*k + q].  lf[qq] = exp(-+2*pi*i*q*qq/(Q*Q)) is
-// the part of the twiddle that depends on the lane.
-template <int N, int R, int Q, bool INV, bool PK = INV>
-__device__ __forceinline__ void coop_fft(float2 (&a)[R], int q, const float2 (&lf)[Q]) {
-  if constexpr (Q == 1) {
-    fft_bitrev<R, INV, PK>(a);
-  } else {
-    constexpr int P = R / Q;
-    constexpr int LP = 32 / Q;  // lanes per q group
-    constexpr int LOGQ = ilog2c(Q);
-    // radix-Q step over m for every jl: output qq lands at a[brev(qq, Q)*P + jl]
-    static_for<P>([&](auto jc) {
-      constexpr int jl = decltype(jc)::value;
-      Dif<Q, jl, P, INV, R, PK>::run(a);
-    });
-    float2 c[R];
-    static_for<Q>([&](auto qc) {
-      constexpr int qq = decltype(qc)::value;
-      static_for<P>([&](auto jc) {
-        constexpr int jl = decltype(jc)::value;
-        float2 v = mul_tw<jl * qq, N, INV>(a[brev(qq, Q) * P + jl]);
-        if (qq > 0) v = cmul(v, lf[qq]);
-        c[qq * P + jl] = v;
-      });
-    });
-    // all-to-all between the Q lanes: block qq goes to lane qq; afterwards block i holds
-    // what lane i sent, i.e. c[i*P + jl] is element j = jl + P*i of this lane's R-point input
-    static_for<LOGQ>([&](auto tc) {
-      constexpr int t = decltype(tc)::value;
-      const bool mybit = (q >> t) & 1;
-      static_for<Q / 2>([&](auto ic) {
-        constexpr int idx = decltype(ic)::value;
-        constexpr int i0 = ((idx >> t) << (t + 1)) | (idx & ((1 << t) - 1));
-        constexpr int i1 = i0 | (1 << t);
-        static_for<P>([&](auto jc) {
-          constexpr int jl = decltype(jc)::value;
-          const float2 lo = c[i0 * P + jl], hi = c[i1 * P + jl];
-          const float sx = mybit ? lo.x : hi.x, sy = mybit ? lo.y : hi.y;
-          const float rx = __shfl_xor_sync(0xffffffffu, sx, LP << t);
-          const float ry = __shfl_xor_sync(0xffffffffu, sy, LP << t);
-          c[i0 * P + jl] = mybit ? make_float2(rx, ry) : lo;
-          c[i1 * P + jl] = mybit ? hi : make_float2(rx, ry);
-        });
-      });
-    });
-    fft_bitrev<R, INV, PK>(c);
-#pragma unroll
-    for (int i = 0; i < R; ++i) a[i] = c[i];
-  }
-}
-
 // block-wide barrier; a one-warp block only needs the warp to reconverge
 template <int THREADS>
 __device__ __forceinline__ void block_sync() {
@@ -101,16 +49,6 @@ __device__ __forceinline__ void block_sync() {
     __syncwarp();
   } else {
     __syncthreads();
-  }
-}
-
-template <int Q, bool INV>
-__device__ __forceinline__ void lane_factors(int q, float2 (&lf)[Q]) {
-#pragma unroll
-  for (int qq = 0; qq < Q; ++qq) {
-    float s, c;
-    sincospif((INV ? 2.0f : -2.0f) * (float)(q * qq) / (float)(Q * Q), &s, &c);
-    lf[qq] = make_float2(c, s);
   }
 }
 

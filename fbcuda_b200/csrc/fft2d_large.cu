@@ -187,8 +187,9 @@ int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, i
   if (fft2d_coop_supported(n, out)) return fft2d_coop_forward(n, in, out, B, padL, padU, s);
   if (n == 64) return launch_fwd<64>(in, out, B, padL, padU, s);
   if (n == 128) return launch_fwd<128>(in, out, B, padL, padU, s);
+  if (n == 256 && fft2d_256_supported(in, out, B)) return fft2d_256_forward(in, out, B, padL, padU, s);
   if (n == 256) {
-    // row pass straight into the output tensor, transposed: out[b][kx][y]; then
+    // (strided or unaligned output) row pass straight into the output tensor, transposed: out[b][kx][y]; then
     // every line out[b][kx][*] is transformed in place
     CplxView t = out;
     t.sr = out.sc;

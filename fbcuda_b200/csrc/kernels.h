@@ -21,6 +21,9 @@ bool fft2d_coop_supported(int n, const CplxView& c);
 int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 int read_device_error_coop();
+// N = 256 forward on a contiguous spectrum: two register passes, no intermediate buffer (fft2d_256.cu)
+bool fft2d_256_supported(const RealView& in, const CplxView& out, int B);
+int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 // forward transform by direct evaluation for images with a support of at most 8 x 8, N in {16, 32, 64, 128} (fft2d_pruned.cu)
 bool fft2d_pruned_supported(int n, const RealView& real, const CplxView& cplx, int padL, int padU);
 int fft2d_pruned_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
