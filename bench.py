@@ -37,9 +37,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GIB = 1 << 30
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the forward kernel, from the
-# ncu capture summarised in profiles/ (captured on 65536 images, scaled by images per launch)
-NCU_TRAFFIC_BYTES_PER_IMAGE = {(32, 32): 7609.0, (64, 64): 30170.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per image of the forward kernel, keyed by (FFT size,
+# image size), from the ncu captures summarised in profiles/ (profile case: a quarter of the bench
+# batch; traffic grows in proportion to the images, so it is scaled by images per launch)
+NCU_TRAFFIC_BYTES_PER_IMAGE = {(32, 27): 6655.6, (32, 32): 7609.0, (64, 64): 30072.0, (128, 128): 119034.0}
 
 
 def measured_peak_gbs():
