@@ -57,7 +57,8 @@ int fbfft_b200_device_status(void);
  * 0 (default) tensor cores -- tcgen05 MMAs on a 3xTF32 split of the fp32 operands,
  * accumulating in fp32 -- whenever the operands qualify (bin count a multiple of 4,
  * 16-byte aligned bases, even strides), FP32 CUDA cores otherwise; 1 FP32 CUDA cores
- * always. */
+ * always; 2 tensor cores through the earlier gather kernel only (comparison point;
+ * needs 32-byte aligned operands and strides that are multiples of 4). */
 int fbfft_b200_set_contraction_mode(int mode);
 
 /* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
