@@ -299,15 +299,31 @@ def run_fft2d(args, world, rank, local):
     xh.copy_(x.cpu())
     sh = torch.empty((b, n // 2 + 1, n, 2), dtype=torch.float32).pin_memory()
 
+    # The batch goes through in chunks on three streams, so that the upload of one chunk, the
+    # transform of the previous and the download of the one before overlap (PCIe is full duplex);
+    # the side streams fork from and join the timed stream inside every step.
+    n_chunks = 8
+    bounds = [(i * b // n_chunks, (i + 1) * b // n_chunks) for i in range(n_chunks)]
+    side = [torch.cuda.Stream() for _ in range(3)]
+
     def step_e2e():
-        x.copy_(xh, non_blocking=True)
-        fb.fft2d_r2c(n, x, spec)
-        sh.copy_(spec, non_blocking=True)
+        cur = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for i, (lo, hi) in enumerate(bounds):
+            st = side[i % len(side)]
+            st.wait_event(fork)
+            with torch.cuda.stream(st):
+                x[lo:hi].copy_(xh[lo:hi], non_blocking=True)
+                fb.fft2d_r2c(n, x[lo:hi], spec[lo:hi])
+                sh[lo:hi].copy_(spec[lo:hi], non_blocking=True)
+        for st in side:
+            cur.wait_stream(st)
 
     ms_e2e = time_steps(step_e2e, max(2, args.steps // 4), 3, world)
     e2e = {"value": world * b * per_image / (ms_e2e / 1e3) / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": b * hw * hw * 4, "d2h_bytes_per_step": b * (n // 2 + 1) * n * 8,
-           "ms_per_step": ms_e2e}
+           "ms_per_step": ms_e2e, "pipeline": f"{n_chunks} chunks on {len(side)} streams (H2D, transform, D2H overlapped)"}
     del xh, sh
 
     peak, how = measured_peak_gbs()

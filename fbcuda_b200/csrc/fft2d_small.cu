@@ -191,12 +191,15 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
 // IN_BULK: complex input contiguous and 16-byte aligned; rows are fetched with bulk
 // copies one task ahead into the second of two work buffers.
 // FULL   : the output images are contiguous N x N without crop offset
-template <int N, bool IN_BULK, bool FULL = false>
-__global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxView in, RealView out, int B, int padL,
+// SINGLE : (with IN_BULK) one work buffer per warp instead of two: the next task's rows are fetched
+//          into it as soon as the column pass holds the current task in registers.  Shorter
+//          prefetch distance, but 5 resident blocks per SM instead of 3.
+template <int N, bool IN_BULK, bool FULL = false, bool SINGLE = false>
+__global__ void __launch_bounds__(kSmallThreads, SINGLE ? 5 : 3) fft2d_small_inv_kernel(CplxView in, RealView out, int B, int padL,
                                                                           int padU, int ntasks) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
   constexpr int RS = SmallCfg<N>::RS, IS = SmallCfg<N>::IS;
-  constexpr int NBUF = IN_BULK ? 2 : 1;
+  constexpr int NBUF = (IN_BULK && !SINGLE) ? 2 : 1;
   extern __shared__ __align__(16) float2 smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float2* wbuf = smem + warp * (NBUF * IPW * IS);
@@ -249,7 +252,7 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
     float2* buf = wbuf + cur * (IPW * IS);
     float2* ib = buf + li * IS;
     if (IN_BULK) {
-      if (task + stride < ntasks) fetch(task + stride, cur ^ 1);
+      if (!SINGLE && task + stride < ntasks) fetch(task + stride, cur ^ 1);
       if (!mbar_wait(smem_u32(bars + warp * 2 + cur), phase[cur], kErrInvWait)) return;
       phase[cur] ^= 1;
     } else {
@@ -269,7 +272,13 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
     inv_pack_rows<N>(ib, l);
     {
       float2 z[N];
-      inv_columns<N>(ib, l, z);
+      inv_columns_load<N>(ib, l, z);
+      if (IN_BULK && SINGLE) {
+        // the whole task is in registers: its buffer takes the next task's rows
+        __syncwarp();
+        if (task + stride < ntasks) fetch(task + stride, 0);
+      }
+      fft_bitrev<N, true, true>(z);
       const int b = task * IPW + li;
       if (b < B) {
         if constexpr (FULL) {
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_inv_kernel(CplxV
       }
     }
     __syncwarp();
-    cur ^= IN_BULK ? 1 : 0;
+    cur ^= (IN_BULK && !SINGLE) ? 1 : 0;
   }
 }
 
@@ -357,6 +366,12 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
     if (full) {
       allow_smem(fft2d_small_inv_kernel<N, true, true>, smem);
       fft2d_small_inv_kernel<N, true, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);
+    } else if (N == 8 || (N == 32 && (out.h < N || out.w < N))) {
+      // (measured: the single-buffer variant gains at N = 8, 0.79 -> 0.82, and for cropped outputs at
+      // N = 32, 27x27: 0.82 -> 0.92; it loses for full 32x32 outputs, 0.89 -> 0.86)
+      const int smem1 = base + kWarps * 16;
+      allow_smem(fft2d_small_inv_kernel<N, true, false, true>, smem1);
+      fft2d_small_inv_kernel<N, true, false, true><<<grid_for(ntasks, 5), kSmallThreads, smem1, s>>>(in, out, B, padL, padU, ntasks);
     } else {
       allow_smem(fft2d_small_inv_kernel<N, true>, smem);
       fft2d_small_inv_kernel<N, true><<<grid_for(ntasks, 3), kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks);

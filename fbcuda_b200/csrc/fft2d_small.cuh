@@ -150,7 +150,7 @@ __device__ __forceinline__ void inv_pack_rows(float2* ib, int l) {
 // Hermitian extension G[N-r] = conj G[r]; afterwards z[brev(y, N)] = N*N * (P[y][l],
 // P[y][l+T]).
 template <int N>
-__device__ __forceinline__ void inv_columns(const float2* ib, int l, float2 (&z)[N]) {
+__device__ __forceinline__ void inv_columns_load(const float2* ib, int l, float2 (&z)[N]) {
   constexpr int T = N / 2, RS = SmallCfg<N>::RS;
   {
     const float2 g0 = ib[l], g1 = ib[l + T];
@@ -163,6 +163,10 @@ __device__ __forceinline__ void inv_columns(const float2* ib, int l, float2 (&z)
     z[r] = make_float2(g0.x - g1.y, g0.y + g1.x);
     z[N - r] = make_float2(g0.x + g1.y, g1.x - g0.y);
   });
+}
+template <int N>
+__device__ __forceinline__ void inv_columns(const float2* ib, int l, float2 (&z)[N]) {
+  inv_columns_load<N>(ib, l, z);
   fft_bitrev<N, true, true>(z);
 }
 
