@@ -40,6 +40,8 @@ GIB = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per image of the forward kernel, keyed by (FFT size,
 # image size), from the ncu captures summarised in profiles/ (profile case: a quarter of the bench
 # batch; traffic grows in proportion to the images, so it is scaled by images per launch)
+# the same for one launch of the contraction kernel (config 4), profiles/cgemm_tma_conv4.md
+NCU_CONTRACTION_TRAFFIC = {"conv4": 524.8e6}
 NCU_TRAFFIC_BYTES_PER_IMAGE = {(32, 27): 6655.6, (32, 32): 7609.0, (64, 64): 30072.0, (128, 128): 119034.0}
 
 
@@ -447,6 +449,14 @@ def run_conv(args, world, rank, local):
     ms_e2e = time_steps(step_e2e, max(2, args.steps // 2), 3, world)
     bins = (n // 2 + 1) * n
     flops = 3 * 8.0 * bg * c * o * bins
+    # the dominant kernel alone: the weight-gradient contraction on the spectra already in the
+    # workspace (operands read once + result written once = its algorithmic bytes)
+    ms_con = time_steps(lambda: fb.conv_acc_grad_parameters(
+        n, x, gw, go, ws, inPad=ip, flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM |
+        api.STOP_AFTER_CONTRACTION), args.steps, 3, world)
+    con_bytes = 8.0 * bins * (b * c + b * o + o * c)
+    peak = measured_peak_gbs()
+    traffic = NCU_CONTRACTION_TRAFFIC.get(args.conv_config) if world == 1 else None
     line = {"metric": "FFT-conv layer fwd+bwd images/s", "value": ips, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -457,9 +467,13 @@ def run_conv(args, world, rank, local):
                     "h2d_bytes_per_step": (x.numel() + go.numel()) * 4, "d2h_bytes_per_step": gw.numel() * 4,
                     "ms_per_step": ms_e2e},
             "gpu_launches": args.steps * 9, "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": None, "peak": measured_peak_gbs()[0], "unit": "GB/s", "frac": None,
-                         "traffic": None, "contraction_tflops": flops / world / (ms / 1e3) / 1e12,
-                         "note": "per-step time covers 6 transform batches and 3 contractions; see profiles/"}}
+            "roofline": {"bound": "hbm", "achieved": con_bytes / (ms_con / 1e3) / 1e9, "peak": peak[0], "unit": "GB/s",
+                         "frac": con_bytes / (ms_con / 1e3) / 1e9 / peak[0], "peak_source": f"of {peak[1]}",
+                         "traffic": traffic, "algorithmic_bytes_per_launch": con_bytes,
+                         "kernel": "cgemm_tma_kernel (one of the step's three contractions, timed alone: "
+                                   f"{ms_con * 1e3:.1f} us)",
+                         "contraction_tflops_fp32_equivalent": flops / 3 / world / (ms_con / 1e3) / 1e12,
+                         "note": "the step covers 6 transform batches and 3 contractions; shares in profiles/"}}
     return line
 
 

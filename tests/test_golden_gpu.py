@@ -48,7 +48,7 @@ def test_golden_2d(tag):
     assert rel(gpu_ifft2d(floats(want), n, h, w, pl, pu), inv) < FFT_TOL
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 def test_golden_transpose_mm(mode):
     fb.set_contraction_mode(mode)
     try:

@@ -192,6 +192,12 @@ def test_iterated_convolution_tiled_input():
         assert orc.rel_l2(host(t), want) < CONV_TOL
 
 
+def test_contraction_mode_rejects_unknown_value():
+    with pytest.raises(Exception):
+        fb.set_contraction_mode(3)
+    fb.set_contraction_mode(0)
+
+
 def test_iterated_convolution_rejects_unknown():
     x = torch.zeros((1, 1, 8, 8), device="cuda")
     t = _tiles([(x, 0, 0)])
@@ -199,11 +205,12 @@ def test_iterated_convolution_rejects_unknown():
     assert fb.FFTIteratedConvolution(8, t, t, torch.zeros((1, 1, 3, 3), device="cuda"), 3, 1.0, 1) is False
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 @pytest.mark.parametrize("conj_a,conj_b", [(False, True), (True, False), (False, False)])
 @pytest.mark.parametrize("ikj", [(64, 128, 128), (8, 96, 96), (130, 20, 70), (96, 5, 40)])
 def test_transpose_mm_both_contraction_modes(mode, conj_a, conj_b, ikj):
-    """Tensor-core (3xTF32, mode 0) and FP32 CUDA-core (mode 1) contractions against float64,
+    """Tensor-core (3xTF32; mode 0 persistent kernel, mode 2 gather kernel) and FP32 CUDA-core (mode 1)
+    contractions against float64,
     on shapes that need row, column and k padding of the MMA tiles."""
     i, k, j = ikj
     rows, cols = 3, 8
@@ -226,14 +233,18 @@ def test_transpose_mm_both_contraction_modes(mode, conj_a, conj_b, ikj):
     assert fb.device_status() == 0
 
 
-def test_conv_passes_fp32_mode_matches():
-    """The convolution passes give the same answer with the FP32 CUDA-core contraction."""
-    n, b, c, o, hw, k, pad = 32, 4, 6, 5, 27, 5, 0
+@pytest.mark.parametrize("mode,shape", [(1, (32, 4, 6, 5, 27, 5, 0)), (2, (32, 4, 6, 5, 27, 5, 0)),
+                                        (2, (64, 3, 20, 17, 40, 3, 1)), (1, (64, 3, 20, 17, 40, 3, 1))])
+def test_conv_passes_other_contraction_modes_match(mode, shape):
+    """The convolution passes give the same answer with the FP32 CUDA-core contraction (natural
+    workspace layout) and with the gather tensor-core kernel (blocked layouts)."""
+    n, b, c, o, hw, k, pad = shape
     rng = np.random.default_rng(12)
     x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
     w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
-    go = rng.normal(size=(b, o, hw - k + 1, hw - k + 1)).astype(np.float32)
-    fb.set_contraction_mode(1)
+    oh = hw + 2 * pad - k + 1
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    fb.set_contraction_mode(mode)
     try:
         out, gi, gw = run_passes(n, x, w, go, pad)
     finally:
