@@ -100,7 +100,10 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     }
   };
   if (IN_BULK) {
-    if (threadIdx.x == 0) mbar_init(bar, 1);
+    if (threadIdx.x == 0) {
+      mbar_init(bar, 1);
+      smem[REGION + 1] = make_float2(0.f, 0.f);  // the zero word out-of-image lanes read
+    }
     fence_async_smem();
     block_sync<T>();
     if (blockIdx.x < B) fetch(blockIdx.x);
@@ -112,11 +115,18 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       // ---- pass A: columns item and item+H, rows y = jl + P*q + R*m
       const float* src = in.p + (long long)b * in.sb;
       long long sy = in.sy, sx = in.sx;
-      if (IN_BULK && staged) {
-        if (!mbar_wait(bar, phase, kErrCoopFwdWait)) return;
-        phase ^= 1;
-        src = reinterpret_cast<const float*>(smem) + ((((long long)b * img_bytes) & 15) >> 2);
-        sy = in.w, sx = 1;
+      int soff = 0;  // float offset of the image inside the staging region
+      if (IN_BULK) {
+        if (staged) {
+          if (!mbar_wait(bar, phase, kErrCoopFwdWait)) return;
+          phase ^= 1;
+          soff = (int)((((long long)b * img_bytes) & 15) >> 2);
+        } else {
+          // (the last images of a tensor whose size is not a multiple of 16 bytes) plain copy
+          float* st = reinterpret_cast<float*>(smem);
+          for (int i = threadIdx.x; i < in.h * in.w; i += T) st[i] = src[i];
+          block_sync<T>();
+        }
       }
       if constexpr (FULL) {
         const float* p0 = reinterpret_cast<const float*>(smem) + item + P * q * N;
@@ -126,6 +136,29 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           for (int jl = 0; jl < P; ++jl) {
             a[m * P + jl].x = p0[(jl + R * m) * N];
             a[m * P + jl].y = p0[(jl + R * m) * N + H];
+          }
+        }
+      } else if constexpr (IN_BULK) {
+        // staged image, row pitch in.w, 32-bit offsets: one uniform bounds test per row; lanes whose
+        // column lies outside the image read the zero word behind the region through a zero stride
+        const float* st = reinterpret_cast<const float*>(smem) + soff;
+        const float* zero = reinterpret_cast<const float*>(smem + REGION + 1);  // the float2 behind the mbarrier
+        const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
+        const bool ok0 = x0 < (unsigned)in.w, ok1 = x1 < (unsigned)in.w;
+        const int s0 = ok0 ? in.w : 0, s1 = ok1 ? in.w : 0;
+        const int ybase = P * q - padU;
+        const float* p0 = ok0 ? st + (int)x0 + ybase * in.w : zero;
+        const float* p1 = ok1 ? st + (int)x1 + ybase * in.w : zero;
+#pragma unroll
+        for (int m = 0; m < Q; ++m) {
+#pragma unroll
+          for (int jl = 0; jl < P; ++jl) {
+            const int yo = jl + R * m;
+            a[m * P + jl] = make_float2(0.f, 0.f);
+            if ((unsigned)(ybase + yo) < (unsigned)in.h) {
+              a[m * P + jl].x = p0[yo * s0];
+              a[m * P + jl].y = p1[yo * s1];
+            }
           }
         }
       } else {

@@ -51,6 +51,10 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) +
                                                                    kWarps * slot_floats);
   const unsigned bar = smem_u32(bars + warp);
+  __shared__ float zero_storage;
+  if (threadIdx.x == 0) zero_storage = 0.f;
+  __syncthreads();
+  const float* zero_word = &zero_storage;
   const long long img_floats = (long long)in.h * in.w;
   const long long total_bytes = (long long)B * img_floats * 4;
 
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
         if constexpr (FULL) {
           load_columns_full<N>(slot + li * (N * N + N / 2), l, a);  // per-image slots of pitch N*N + N/2
         } else {
-          load_columns<N>(slot + off0 + li * slot_pitch, in.w, 1, in.h, in.w, padL, padU, valid, l, a);
+          load_columns_staged<N>(slot + off0 + li * slot_pitch, zero_word, in.h, in.w, padL, padU, l, a);
         }
       } else {
         load_columns<N>(in.p + (long long)(valid ? b : 0) * in.sb, in.sy, in.sx, in.h, in.w, padL, padU, valid, l, a);

@@ -57,6 +57,28 @@ __device__ __forceinline__ void load_columns(const float* src, long long sy, lon
   }
 }
 
+// The same for an image staged in shared memory with row pitch w (32-bit offsets): one uniform
+// bounds test per row, and lanes whose column lies outside the image read a zero word through a
+// zero stride instead of carrying a predicate.  `zero` points at a float that holds 0.
+template <int N>
+__device__ __forceinline__ void load_columns_staged(const float* src, const float* zero, int h, int w, int padL, int padU,
+                                                    int l, float2 (&a)[N]) {
+  constexpr int T = N / 2;
+  const unsigned x0 = (unsigned)(l - padL), x1 = (unsigned)(l + T - padL);
+  const bool ok0 = x0 < (unsigned)w, ok1 = x1 < (unsigned)w;
+  const int s0 = ok0 ? w : 0, s1 = ok1 ? w : 0;
+  const float* p0 = ok0 ? src + (int)x0 - padU * w : zero;
+  const float* p1 = ok1 ? src + (int)x1 - padU * w : zero;
+#pragma unroll
+  for (int y = 0; y < N; ++y) {
+    a[y] = make_float2(0.f, 0.f);
+    if ((unsigned)(y - padU) < (unsigned)h) {
+      a[y].x = p0[y * s0];
+      a[y].y = p1[y * s1];
+    }
+  }
+}
+
 // The same for a contiguous N x N image without padding: compile-time offsets, no predicates.
 template <int N>
 __device__ __forceinline__ void load_columns_full(const float* src, int l, float2 (&a)[N]) {
