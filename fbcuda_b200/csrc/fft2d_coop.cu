@@ -281,8 +281,9 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 
 // ------------------------------------------------------------------ inverse
 // FULL: the output images are contiguous N x N with no crop offset (compile-time strides, no
-// bounds predicates on the stores)
-template <int N, bool FULL = false>
+// bounds predicates on the stores).  SKIP: small outputs such as weight gradients: a warp none of
+// whose columns is kept by the crop skips its column transforms.
+template <int N, bool FULL = false, bool SKIP = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
                                                                                 long long in_sb, RealView out, int B,
                                                                                 int padL, int padU, long long blk_planes) {
@@ -393,9 +394,9 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       if (b + gridDim.x < B) fetch(b + gridDim.x);
       const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
       const bool ok0 = x0 < (unsigned)out.w, ok1 = x1 < (unsigned)out.w;
-      // a warp none of whose columns is kept by the crop (small outputs such as weight gradients)
-      // skips its transforms
-      if (__all_sync(0xffffffffu, !ok0 && !ok1)) continue;
+      if constexpr (SKIP) {
+        if (__all_sync(0xffffffffu, !ok0 && !ok1)) continue;
+      }
       coop_fft<N, R, Q, true>(a, q, lf);
       float* dst = out.p + (long long)b * out.sb;
       if constexpr (FULL) {
@@ -444,6 +445,7 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
@@ -470,12 +472,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
     cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+    cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
   // (measured: the predicate-free stores gain at N = 128, 0.57 -> 0.78 of the copy bandwidth, and lose at N = 64)
   if (N == 128 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0) {
     fft2d_coop_inv_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  } else if (N == 128 && (out.w + padL) * 2 <= N) {
+    // at most half of the column pairs survive the crop (measured on 13x13 weight gradients: 297 -> 227 us)
+    fft2d_coop_inv_kernel<N, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   } else {
     fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   }
