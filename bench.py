@@ -304,7 +304,7 @@ def run_fft2d(args, world, rank, local):
     # The batch goes through in chunks on three streams, so that the upload of one chunk, the
     # transform of the previous and the download of the one before overlap (PCIe is full duplex);
     # the side streams fork from and join the timed stream inside every step.
-    n_chunks = 8
+    n_chunks = 32
     bounds = [(i * b // n_chunks, (i + 1) * b // n_chunks) for i in range(n_chunks)]
     side = [torch.cuda.Stream() for _ in range(3)]
 
