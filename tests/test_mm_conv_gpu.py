@@ -233,6 +233,28 @@ def test_transpose_mm_both_contraction_modes(mode, conj_a, conj_b, ikj):
     assert fb.device_status() == 0
 
 
+def test_transpose_mm_random_shapes_tensor_core():
+    """Random operand shapes through the persistent tensor-core kernel: row, column and k counts
+    that are not multiples of the tile sizes, bin counts that are multiples of 4 but not of 16,
+    every conjugation convention, with and without accumulation."""
+    rng = np.random.default_rng(2024)
+    for trial in range(24):
+        i, k, j = (int(v) for v in rng.integers(1, 200, 3))
+        if i * k * j < 4096:
+            i += 64
+        rows, cols = int(rng.integers(1, 4)), 4 * int(rng.integers(1, 6))
+        conj_a, conj_b = [(False, True), (True, False), (False, False)][trial % 3]
+        a = rng.normal(size=((k, i) if conj_a else (i, k)) + (rows, cols, 2)).astype(np.float32)
+        b = rng.normal(size=((j, k) if conj_b else (k, j)) + (rows, cols, 2)).astype(np.float32)
+        want = orc.transpose_mm(a, b, None, conj_a, conj_b, False, 0.25)
+        c = torch.full(want.shape, 3.0, device="cuda")
+        fb.transposeMM(dev(a), dev(b), c, 0.25, conj_a, conj_b, False)
+        assert orc.rel_l2(host(c), want) < 5e-6, (trial, i, k, j, rows, cols)
+        fb.transposeMM(dev(a), dev(b), c, 0.25, conj_a, conj_b, True)
+        assert orc.rel_l2(host(c), 2 * want) < 5e-6, (trial, i, k, j, rows, cols)
+    assert fb.device_status() == 0
+
+
 @pytest.mark.parametrize("mode,shape", [(1, (32, 4, 6, 5, 27, 5, 0)), (2, (32, 4, 6, 5, 27, 5, 0)),
                                         (2, (64, 3, 20, 17, 40, 3, 1)), (1, (64, 3, 20, 17, 40, 3, 1))])
 def test_conv_passes_other_contraction_modes_match(mode, shape):
