@@ -6,10 +6,10 @@
 //
 //   forward   S[r][c] = sum_b w^(c (b + pb)) * G[r][b],   G[r][b] = sum_a w^(r (a + pa)) * img[a][b]
 //             (a, b = the image coordinates that pair with r and c; w = exp(-2 pi i / N)).
-//             G is (N/2+1) x support values per plane in shared memory; thread c keeps its
-//             `support` twiddles in registers and walks r: `support` complex multiply-adds per
+//             G is (N/2+1) x support values per plane in shared memory; a thread keeps the
+//             `support` twiddles of two adjacent columns in registers and walks r: `support` complex multiply-adds per
 //             bin instead of a share of two N-point FFTs, so the kernel is bound by its stores.
-// One block handles 128 / N planes at a time (N = 128: one).
+// One block handles 256 / N planes at a time.
 #include "fft2d_small.cuh"
 #include "kernels.h"
 
@@ -33,12 +33,13 @@ __device__ __forceinline__ long long bin_offset(const CplxView& v, long long P, 
 // MB: compile-time bound of the support along b (4 or 8)
 template <int N, int MB>
 __global__ void __launch_bounds__(kThreadsP) pruned_fwd_kernel(RealView in, CplxView out, int planes, int padL, int padU) {
-  constexpr int G = kThreadsP / N, HR = N / 2 + 1;
+  constexpr int TPP = N / 2;  // threads per plane: each takes two adjacent columns (16-byte stores)
+  constexpr int G = kThreadsP / TPP, HR = N / 2 + 1;
   constexpr bool TR = N >= 64;  // stored rows are kx: the roles of x and y swap
   __shared__ float2 tw[N];
   __shared__ float img[G][kMaxSupport * kMaxSupport];
   __shared__ float2 gs[G][HR][MB];
-  const int tid = threadIdx.x, g = tid / N, c = tid % N;
+  const int tid = threadIdx.x, g = tid / TPP, c = 2 * (tid % TPP);
   // extents along a (pairs with r) and b (pairs with c), and their offsets inside the canvas
   const int na = TR ? in.w : in.h, nb = TR ? in.h : in.w, pa = TR ? padL : padU, pb = TR ? padU : padL;
   for (int i = tid; i < N; i += kThreadsP) {
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(kThreadsP) pruned_fwd_kernel(RealView in, Cplx
     sincospif(-2.0f * (float)i / (float)N, &sn, &cs);
     tw[i] = make_float2(cs, sn);
   }
-  float2 twc[MB];
+  float2 twc[MB], twd[MB];  // twiddles of columns c and c + 1
   for (int p0 = blockIdx.x * G; p0 < planes; p0 += gridDim.x * G) {
     __syncthreads();  // the previous planes' G and image are consumed (and the table is written)
     for (int i = tid; i < G * na * nb; i += kThreadsP) {
@@ -69,7 +70,10 @@ __global__ void __launch_bounds__(kThreadsP) pruned_fwd_kernel(RealView in, Cplx
       gs[gg][r][b] = acc;
     }
 #pragma unroll
-    for (int b = 0; b < MB; ++b) twc[b] = (b < nb) ? tw[(c * (b + pb)) & (N - 1)] : make_float2(0.f, 0.f);
+    for (int b = 0; b < MB; ++b) {
+      twc[b] = (b < nb) ? tw[(c * (b + pb)) & (N - 1)] : make_float2(0.f, 0.f);
+      twd[b] = (b < nb) ? tw[((c + 1) * (b + pb)) & (N - 1)] : make_float2(0.f, 0.f);
+    }
     __syncthreads();
     const long long P = p0 + g;
     if (P < planes) {
@@ -77,16 +81,18 @@ __global__ void __launch_bounds__(kThreadsP) pruned_fwd_kernel(RealView in, Cplx
       float* dst = out.p + bin_offset<N>(out, P, 0, c);
       const long long rstride = bin_offset<N>(out, P, 1, c) - bin_offset<N>(out, P, 0, c);
       for (int r = 0; r < HR; ++r, dst += rstride) {
-        float2 acc = make_float2(0.f, 0.f);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int b = 0; b < MB; ++b) {
           if (b < nb) {
             const float2 v = gs[g][r][b];
             acc.x += v.x * twc[b].x - v.y * twc[b].y;
             acc.y += v.x * twc[b].y + v.y * twc[b].x;
+            acc.z += v.x * twd[b].x - v.y * twd[b].y;
+            acc.w += v.x * twd[b].y + v.y * twd[b].x;
           }
         }
-        *reinterpret_cast<float2*>(dst) = acc;
+        *reinterpret_cast<float4*>(dst) = acc;
       }
     }
   }
@@ -94,7 +100,7 @@ __global__ void __launch_bounds__(kThreadsP) pruned_fwd_kernel(RealView in, Cplx
 
 bool view_ok(const CplxView& v) {
   if (v.blk_planes) return aligned16(v.p);
-  return v.sz == 1 && v.sc == 2 && (v.sr % 2) == 0 && (v.sb % 2) == 0 && (reinterpret_cast<uintptr_t>(v.p) & 7u) == 0;
+  return v.sz == 1 && v.sc == 2 && (v.sr % 4) == 0 && (v.sb % 4) == 0 && aligned16(v.p);
 }
 
 }  // namespace
@@ -111,7 +117,7 @@ bool fft2d_pruned_supported(int n, const RealView& real, const CplxView& cplx, i
 
 template <int N>
 static void launch_pruned(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
-  const int per = kThreadsP / N;
+  const int per = kThreadsP / (N / 2);
   const int want = (B + per - 1) / per, cap = sm_count() * 8;
   const int grid = want < cap ? want : cap;
   const int nb = N >= 64 ? in.h : in.w;
