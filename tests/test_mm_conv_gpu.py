@@ -233,6 +233,37 @@ def test_transpose_mm_both_contraction_modes(mode, conj_a, conj_b, ikj):
     assert fb.device_status() == 0
 
 
+def test_conv_passes_are_graph_capturable():
+    """The three passes allocate nothing and synchronise nothing: after one eager step they can be
+    captured into a CUDA graph, and the replay gives bit-identical results."""
+    n, b, c, o, hw, k, pad = 64, 4, 24, 20, 40, 3, 1
+    rng = np.random.default_rng(21)
+    x, w = dev(rng.normal(size=(b, c, hw, hw))), dev(rng.normal(size=(o, c, k, k)))
+    go = dev(rng.normal(size=(b, o, hw, hw)))
+    out, gi, gw = torch.empty_like(go), torch.empty_like(x), torch.empty_like(w)
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+
+    def step():
+        fb.conv_update_output(n, x, w, out, ws, inPad=(pad, pad))
+        fb.conv_update_grad_input(n, gi, w, go, ws, inPad=(pad, pad), flags=api.REUSE_WEIGHT_SPECTRUM)
+        fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=(pad, pad),
+                                    flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
+
+    step()
+    torch.cuda.synchronize()
+    want = (out.clone(), gi.clone(), gw.clone())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for t in (out, gi, gw):
+        t.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, ref in zip((out, gi, gw), want):
+        assert torch.equal(got, ref)
+    assert fb.device_status() == 0
+
+
 def test_transpose_mm_random_shapes_tensor_core():
     """Random operand shapes through the persistent tensor-core kernel: row, column and k counts
     that are not multiples of the tile sizes, bin counts that are multiples of 4 but not of 16,
