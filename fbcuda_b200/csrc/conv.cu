@@ -115,7 +115,17 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
              long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s) {
   const long long X = bins_of(n);
   if (blocked) {
-    // operands in 4-bin blocks (plane stride 4 complex), result in blocks of one stored row (n bins)
+    // operands in 4-bin blocks (plane stride 4 complex), result in blocks of one stored row (n bins).
+    // The MMA tile is 128 rows of m by 16 / 32 / 64 columns of n: the two operands swap roles
+    // (complex products commute) when that pads less, e.g. 64 planes against a batch of 128.
+    auto padded = [](long long rows, long long cols) {
+      const long long bn = cols <= 16 ? 16 : (cols <= 32 ? 32 : 64);
+      return ((rows + 127) / 128 * 128) * ((cols + bn - 1) / bn * bn);
+    };
+    if (padded(N, M) < padded(M, N)) {
+      return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, d_pn * n, d_pm * n, N, M, K, (int)X,
+                      inv_norm, false, s, b_planes * 4, a_planes * 4, d_planes * n, 4, 4, n);
+    }
     return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K, (int)X,
                     inv_norm, false, s, a_planes * 4, b_planes * 4, d_planes * n, 4, 4, n);
   }
