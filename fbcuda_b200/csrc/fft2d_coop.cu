@@ -57,7 +57,11 @@ __device__ __forceinline__ void block_sync() {
 // shared memory by one cp.async.bulk (into the region the image's own mid/tile reuse afterwards).
 // FULL (with IN_BULK): the images are N x N with no padding, so pass A reads the staged image
 // with compile-time strides and no bounds predicates.
-template <int N, bool IN_BULK, bool FULL = false>
+// SMALLW (N = 128, without IN_BULK): images of at most 16 x 16 that sit in the first 16 canvas
+// columns (convolution weights).  The column pass is evaluated directly -- thread ky sums the image's
+// rows against its 16 twiddles, 16 columns at a time -- instead of transforming 64 column pairs of
+// zeros, and the row pass reads only those 16 columns.
+template <int N, bool IN_BULK, bool FULL = false, bool SMALLW = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
                                                                                 int padU, long long blk_planes) {
@@ -109,9 +113,58 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     if (blockIdx.x < B) fetch(blockIdx.x);
   }
 
+  // SMALLW: behind the region (and its barrier / zero word): the image as [16][16] floats, then N roots
+  float* simg = reinterpret_cast<float*>(smem + REGION + 2);
+  float2* stw = reinterpret_cast<float2*>(simg + 256);
+  if constexpr (SMALLW) {
+    static_assert(!SMALLW || (N == 128 && T == N && !IN_BULK && !FULL), "one thread per ky");
+    for (int i = threadIdx.x; i < N; i += T) {
+      float sn, cs;
+      sincospif(-2.0f * (float)i / (float)N, &sn, &cs);
+      stw[i] = make_float2(cs, sn);
+    }
+  }
+
   for (int b = blockIdx.x; b < B; b += gridDim.x) {
     float2 a[R];
-    {
+    if constexpr (SMALLW) {
+      // ---- pass A by direct evaluation: mid[ky][x] = sum_y img[y][x - padL] w^(ky (y + padU)), x < 16
+      const float* src = in.p + (long long)b * in.sb;
+      for (int i = threadIdx.x; i < 256; i += T) {
+        const int y = i >> 4, xx = (i & 15) - padL;
+        simg[i] = (y < in.h && (unsigned)xx < (unsigned)in.w) ? src[(long long)y * in.sy + (long long)xx * in.sx] : 0.f;
+      }
+      // the previous image's rows may still be leaving the tile that mid aliases
+      bulk_wait_read();
+      block_sync<T>();
+      const int ky = threadIdx.x;
+      float2 acc[16];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) acc[x] = make_float2(0.f, 0.f);
+#pragma unroll 4
+      for (int y = 0; y < 16; ++y) {
+        const float2 w = stw[(ky * (y + padU)) & (N - 1)];
+        const float4* row = reinterpret_cast<const float4*>(simg + y * 16);
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4) {
+          const float4 v = row[x4];
+          acc[4 * x4 + 0].x += v.x * w.x, acc[4 * x4 + 0].y += v.x * w.y;
+          acc[4 * x4 + 1].x += v.y * w.x, acc[4 * x4 + 1].y += v.y * w.y;
+          acc[4 * x4 + 2].x += v.z * w.x, acc[4 * x4 + 2].y += v.z * w.y;
+          acc[4 * x4 + 3].x += v.w * w.x, acc[4 * x4 + 3].y += v.w * w.y;
+        }
+      }
+#pragma unroll
+      for (int x = 0; x < 16; x += 2)
+        *reinterpret_cast<float4*>(mid + ky * PM + x) = make_float4(acc[x].x, acc[x].y, acc[x + 1].x, acc[x + 1].y);
+      block_sync<T>();
+      if (threadIdx.x < 16) {
+        // rows 0 and H travel packed: the same combination the butterfly path stores (see below)
+        const float2 u = mid[threadIdx.x], v = mid[H * PM + threadIdx.x];
+        mid[threadIdx.x] = make_float2(u.x - v.y, u.y + v.x);
+        mid[H * PM + threadIdx.x] = make_float2(u.x + v.y, u.y - v.x);
+      }
+    } else {
       // ---- pass A: columns item and item+H, rows y = jl + P*q + R*m
       const float* src = in.p + (long long)b * in.sb;
       long long sy = in.sy, sx = in.sx;
@@ -210,7 +263,19 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
         a0 = make_float2(0.5f * (u.x + v.x), 0.5f * (u.y - v.y)), b0 = make_float2(0.5f * (u.y + v.y), 0.5f * (v.x - u.x));
         a1 = make_float2(0.5f * (u.z + v.z), 0.5f * (u.w - v.w)), b1 = make_float2(0.5f * (u.w + v.w), 0.5f * (v.z - u.z));
       };
-      if constexpr (Q == 1) {
+      if constexpr (SMALLW) {
+        // only canvas columns 0..15 are non-zero, and no column has a partner in the second half
+#pragma unroll
+        for (int i = 0; i < R; ++i) a[i] = make_float2(0.f, 0.f);
+        if (q == 0) {
+#pragma unroll
+          for (int p = 0; p < 16; p += 2) {
+            const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
+            float2 b0, b1;
+            take(u, v, a[p], a[p + 1], b0, b1);
+          }
+        }
+      } else if constexpr (Q == 1) {
 #pragma unroll
         for (int p = 0; p < H; p += 2) {
           const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
@@ -451,6 +516,19 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
+  if constexpr (N == 128) {
+    if (in.h <= 16 && in.w + padL <= 16 && padL >= 0 && padU >= 0 && in.h + padU <= N) {
+      // small images in the canvas' first 16 columns (convolution weights): direct column pass
+      const int smem = fwd_smem<N>() + 1024 + N * 8 + 16;
+      static bool small_configured[64];
+      if (dev >= 0 && dev < 64 && !small_configured[dev]) {
+        cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        small_configured[dev] = true;
+      }
+      fft2d_coop_fwd_kernel<N, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, smem, s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+      return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+    }
+  }
   if (in_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
     fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
   } else if (in_bulk) {
