@@ -54,9 +54,9 @@ template <int BN>
 struct Cfg {
   static constexpr int NR = 4;                       // raw stages (4 values of k each; a k-step of 8 needs two)
   static constexpr int NH = 2;                       // converted half stages (2 bins x 8 k each)
-  static constexpr int NACC = (BN == 64) ? 1 : 2;    // accumulator sets in tensor memory
+  static constexpr int NACC = (BN >= 48) ? 1 : 2;    // accumulator sets in tensor memory
   static constexpr int ACC_COLS = XB * 2 * BN;
-  static constexpr int TMEM_COLS = NACC * ACC_COLS;  // 512, 512, 256
+  static constexpr int TMEM_COLS = (NACC * ACC_COLS > 256) ? 512 : 256;  // a power of two >= the accumulators
   // raw stage: [k][row][32 bytes] per operand, the k slices 32 bytes further apart than their size so that
   // copies issued k-fastest do not all land in the same banks
   static constexpr int A_KSTRIDE = BM * 32 + 32, B_KSTRIDE = BN * 32 + 32;
@@ -561,7 +561,8 @@ bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long lo
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
               bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb) {
-  const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : 64);
+  // column tile: 16 / 32 for small n; otherwise 48 when that pads less than 64 (e.g. n = 96)
+  const int BN = N <= 16 ? 16 : (N <= 32 ? 32 : (((N + 47) / 48) * 48 < ((N + 63) / 64) * 64 ? 48 : 64));
   alignas(64) CUtensorMap md;
   if (!make_map(&md, d, d_ms, d_ns, d_bs, d_qb, M, N, X, 32, 4)) {
     return -1;  // the caller falls back to the gather kernel
@@ -576,6 +577,7 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
   if (BN == 16) return launch_tma<16>(md, t, s);
   if (BN == 32) return launch_tma<32>(md, t, s);
+  if (BN == 48) return launch_tma<48>(md, t, s);
   return launch_tma<64>(md, t, s);
 }
 

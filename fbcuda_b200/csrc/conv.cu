@@ -119,8 +119,9 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
     // The MMA tile is 128 rows of m by 16 / 32 / 64 columns of n: the two operands swap roles
     // (complex products commute) when that pads less, e.g. 64 planes against a batch of 128.
     auto padded = [](long long rows, long long cols) {
-      const long long bn = cols <= 16 ? 16 : (cols <= 32 ? 32 : 64);
-      return ((rows + 127) / 128 * 128) * ((cols + bn - 1) / bn * bn);
+      const long long p48 = (cols + 47) / 48 * 48, p64 = (cols + 63) / 64 * 64;
+      const long long pc = cols <= 16 ? 16 : (cols <= 32 ? 32 : (p48 < p64 ? p48 : p64));
+      return ((rows + 127) / 128 * 128) * pc;
     };
     if (padded(N, M) < padded(M, N)) {
       return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, d_pn * n, d_pm * n, N, M, K, (int)X,
