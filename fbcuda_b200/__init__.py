@@ -27,5 +27,7 @@ from .api import (  # noqa: F401
     conv_update_output,
     conv_update_grad_input,
     conv_acc_grad_parameters,
+    plan_tiles,
+    plan_tiles_layout,
 )
 from . import api  # noqa: F401,E402

@@ -63,6 +63,8 @@ def lib() -> ctypes.CDLL:
         L.fbfft_b200_fft2d_r2c.argtypes = [ctypes.c_int] + t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
         L.fbfft_b200_fft2d_c2r.argtypes = [ctypes.c_int] + t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
         L.fbfft_b200_transpose_mm.argtypes = [ctypes.c_int] * 4 + t4 * 3 + [ctypes.c_float, _vp]
+        L.fbfft_b200_plan_tiles.argtypes = [ctypes.c_int] * 6 + [_vp, _ip, _ip] * 2 + [_vp, _vp, ctypes.c_size_t]
+        L.fbfft_b200_plan_tiles.restype = ctypes.c_int
         L.fbfft_b200_iterated_convolution.argtypes = [ctypes.c_int, _vp, _vp, _vp, _ip, _ip, ctypes.c_int,
                                                       ctypes.c_float, ctypes.c_int, ctypes.c_size_t, _vp]
         sz = ctypes.c_size_t
@@ -207,9 +209,62 @@ class TiledDeviceTensor:
         self.device_array = host.to(tiles[0][0].device)
         self.count = len(tiles)
 
+    @classmethod
+    def _from_descriptors(cls, arr, count, device):
+        import torch
+        self = cls.__new__(cls)
+        self.tiles = None
+        raw = bytes(arr)[: count * ctypes.sizeof(_Tiled)]
+        self.device_array = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+        self.count = count
+        return self
+
     @property
     def ptr(self):
         return _vp(self.device_array.data_ptr())
+
+
+def plan_tiles(fftSize: int, input, output, kernel, pad=(0, 0), style: int = 0):
+    """Overlap-save tile lists for FFTIteratedConvolution on images larger than the transform
+    (the step the reference's caller performed, fbfft/FFTIteratedConvolution.cuh:70-95).
+    input [B][C][H][W], output [B][O][OH][OW]; kernel = (kh, kw), pad = (pad_h, pad_w);
+    style 0 for updateOutput / accGradParameters, 1 for updateGradInput.
+    Returns (ins, outs) as device descriptor arrays."""
+    ins, outs, count = _plan_tiles_raw(fftSize, input.data_ptr(), input.shape, input.stride(), output.data_ptr(),
+                                       output.shape, output.stride(), kernel, pad, style)
+    return (TiledDeviceTensor._from_descriptors(ins, count, input.device),
+            TiledDeviceTensor._from_descriptors(outs, count, input.device))
+
+
+def _plan_tiles_raw(fftSize, in_ptr, in_shape, in_stride, out_ptr, out_shape, out_stride, kernel, pad, style):
+    kh, kw = kernel
+    ph, pw = pad
+    L = lib()
+    args = (int(fftSize), int(kh), int(kw), int(ph), int(pw), int(style), _vp(in_ptr), _ints(in_shape), _ints(in_stride),
+            _vp(out_ptr), _ints(out_shape), _ints(out_stride))
+    count = L.fbfft_b200_plan_tiles(*args, None, None, 0)
+    if count < 0:
+        raise FbfftError(ErrorCode.UnsupportedDimension, last_error())
+    ins, outs = (_Tiled * count)(), (_Tiled * count)()
+    L.fbfft_b200_plan_tiles(*args, ins, outs, count)
+    return ins, outs, count
+
+
+def plan_tiles_layout(fftSize: int, in_shape, out_shape, kernel, pad=(0, 0), style: int = 0):
+    """The same plan for contiguous tensors, as plain numbers (no device needed): two lists of
+    (element offset into the tensor, (h, w) of the tile view, padL, padU)."""
+    def strides(shape):
+        st, acc = [], 1
+        for d in reversed(shape):
+            st.append(acc)
+            acc *= d
+        return list(reversed(st))
+    base_in, base_out = 1 << 30, 1 << 31   # stand-in addresses: only offsets are read back
+    ins, outs, count = _plan_tiles_raw(fftSize, base_in, in_shape, strides(in_shape), base_out, out_shape,
+                                       strides(out_shape), kernel, pad, style)
+    def unpack(arr, base):
+        return [((arr[i].data - base) // 4, (arr[i].size[2], arr[i].size[3]), arr[i].padL, arr[i].padU) for i in range(count)]
+    return unpack(ins, base_in), unpack(outs, base_out)
 
 
 def FFTIteratedConvolution(fftSize: int, ins: TiledDeviceTensor, outs: TiledDeviceTensor, weight, conv_pass: int,

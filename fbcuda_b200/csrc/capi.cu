@@ -277,4 +277,65 @@ int fbfft_b200_iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins
                               num_tiles, static_cast<cudaStream_t>(stream));
 }
 
+int fbfft_b200_plan_tiles(int fft_size, int kernel_h, int kernel_w, int pad_h, int pad_w, int style, float* input,
+                          const int* in_size, const int* in_stride, float* output, const int* out_size,
+                          const int* out_stride, fbfft_tiled_tensor4* ins_host, fbfft_tiled_tensor4* outs_host,
+                          size_t capacity) {
+  if (!in_size || !in_stride || !out_size || !out_stride || (style != 0 && style != 1)) {
+    set_last_error("plan_tiles: null argument or unknown style");
+    return -1;
+  }
+  const int n = fft_size, H = in_size[2], W = in_size[3], OH = out_size[2], OW = out_size[3];
+  if (n < 2 || kernel_h < 1 || kernel_w < 1 || kernel_h > n || kernel_w > n || pad_h < 0 || pad_w < 0 ||
+      OH != H + 2 * pad_h - kernel_h + 1 || OW != W + 2 * pad_w - kernel_w + 1 || OH < 1 || OW < 1 ||
+      in_size[0] != out_size[0]) {
+    set_last_error("plan_tiles: sizes do not describe a stride-1 convolution that fits the transform");
+    return -1;
+  }
+  // a window [lo, lo + len) of an axis of extent `extent`: the part inside, and the pad that puts
+  // the window's first element at canvas position 0
+  struct Span { int begin, count, pad; };
+  auto clip = [](int lo, int len, int extent) {
+    Span s;
+    s.begin = lo < 0 ? 0 : lo;
+    const int end = lo + len < extent ? lo + len : extent;
+    s.count = end > s.begin ? end - s.begin : 0;
+    s.pad = lo < 0 ? -lo : 0;
+    return s;
+  };
+  auto emit = [&](fbfft_tiled_tensor4* dst, float* base, const int* size, const int* stride, Span y, Span x, int padU,
+                  int padL) {
+    dst->padL = padL;
+    dst->padU = padU;
+    dst->data = base ? base + (long long)y.begin * stride[2] + (long long)x.begin * stride[3] : nullptr;
+    for (int d = 0; d < 4; ++d) dst->stride[d] = stride[d];
+    dst->size[0] = size[0], dst->size[1] = size[1], dst->size[2] = y.count, dst->size[3] = x.count;
+  };
+  const int th = n - kernel_h + 1, tw = n - kernel_w + 1;  // outputs (style 0) / gradInput rows (style 1) per tile
+  const int ext_y = style == 0 ? OH : H, ext_x = style == 0 ? OW : W;
+  int count = 0;
+  for (int y0 = 0; y0 < ext_y; y0 += th) {
+    for (int x0 = 0; x0 < ext_x; x0 += tw) {
+      const int hh = ext_y - y0 < th ? ext_y - y0 : th, ww = ext_x - x0 < tw ? ext_x - x0 : tw;
+      if ((size_t)count < capacity && ins_host && outs_host) {
+        if (style == 0) {
+          // outputs [y0, y0 + hh) need input rows [y0 - pad, y0 - pad + hh + k - 1)
+          const Span iy = clip(y0 - pad_h, hh + kernel_h - 1, H), ix = clip(x0 - pad_w, ww + kernel_w - 1, W);
+          emit(ins_host + count, input, in_size, in_stride, iy, ix, iy.pad, ix.pad);
+          emit(outs_host + count, output, out_size, out_stride, Span{y0, hh, 0}, Span{x0, ww, 0}, 0, 0);
+        } else {
+          // gradInput rows [y0, y0 + hh) need gradOutput rows [y0 + pad - (k - 1), y0 + pad + hh) and
+          // sit at canvas rows k - 1 ... of the full convolution
+          const Span gy = clip(y0 + pad_h - (kernel_h - 1), hh + kernel_h - 1, OH),
+                     gx = clip(x0 + pad_w - (kernel_w - 1), ww + kernel_w - 1, OW);
+          emit(ins_host + count, input, in_size, in_stride, Span{y0, hh, 0}, Span{x0, ww, 0}, kernel_h - 1, kernel_w - 1);
+          emit(outs_host + count, output, out_size, out_stride, gy, gx, gy.pad, gx.pad);
+        }
+      }
+      ++count;
+    }
+  }
+  return count;
+}
+
 }  // extern "C"

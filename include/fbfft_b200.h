@@ -145,6 +145,25 @@ int fbfft_b200_iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins
                                     float* weight, const int* weight_size, const int* weight_stride, int pass,
                                     float scale, int batch_size, size_t num_tiles, void* stream);
 
+/* Tile lists for FFTIteratedConvolution when the image exceeds the transform: overlap-save
+ * tiles of (fft_size - kernel + 1) outputs.  The reference's caller built these lists
+ * (the descriptors and their pads: fbfft/FFTIteratedConvolution.cuh:70-95, 105-114); this
+ * is that host-side step.  Host code only: nothing is launched or copied.
+ *
+ * input  [B][C][H][W], output [B][O][OH][OW] with OH = H + 2*pad_h - kernel_h + 1 (same for W);
+ * both given as pointer, sizes and strides in elements (device pointers are only offset).
+ * style 0 (updateOutput, accGradParameters): input tiles overlap by kernel - 1 and carry the
+ *   image padding as (padU, padL); output tiles are disjoint.
+ * style 1 (updateGradInput): input (gradInput) tiles are disjoint and are cropped at
+ *   (kernel_h - 1, kernel_w - 1) of the canvas; output (gradOutput) tiles overlap.
+ * ins_host / outs_host receive `capacity` descriptors at most (may be NULL to count only).
+ * Returns the number of tiles, or -1 for bad arguments (kernel larger than the transform,
+ * mismatching sizes).  Copy the descriptors to device memory before the convolution call. */
+int fbfft_b200_plan_tiles(int fft_size, int kernel_h, int kernel_w, int pad_h, int pad_w, int style, float* input,
+                          const int* in_size, const int* in_stride, float* output, const int* out_size,
+                          const int* out_stride, fbfft_tiled_tensor4* ins_host, fbfft_tiled_tensor4* outs_host,
+                          size_t capacity);
+
 /* ---- Convolution passes over a caller-owned workspace ------------------------
  * The transform -> per-bin contraction -> inverse transform chain for one tile of
  * any transform size in {8, 16, 32, 64, 128}.  The reference ships the chain only

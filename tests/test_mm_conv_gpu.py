@@ -198,6 +198,36 @@ def test_contraction_mode_rejects_unknown_value():
     fb.set_contraction_mode(0)
 
 
+@pytest.mark.parametrize("case", [(16, 30, 23, 5, 3, 2, 1), (32, 70, 45, 5, 5, 2, 2), (8, 19, 11, 3, 3, 1, 1)])
+def test_planned_tiles_drive_the_iterated_convolution(case):
+    """Images larger than the transform: fbfft_b200_plan_tiles builds the overlap-save tile lists
+    and FFTIteratedConvolution runs the three passes over them."""
+    n, h, w, kh, kw, ph, pw = case
+    b, c, o = 2, 3, 4
+    rng = np.random.default_rng(sum(case))
+    x = rng.normal(size=(b, c, h, w)).astype(np.float32)
+    wt = (rng.normal(size=(o, c, kh, kw)) / np.sqrt(c * kh * kw)).astype(np.float32)
+    oh, ow = h + 2 * ph - kh + 1, w + 2 * pw - kw + 1
+    go = rng.normal(size=(b, o, oh, ow)).astype(np.float32)
+    xp = np.zeros((b, c, h + 2 * ph, w + 2 * pw))
+    xp[:, :, ph:ph + h, pw:pw + w] = x
+    xd, wd, god = dev(x), dev(wt), dev(go)
+    out = torch.full(go.shape, 7.0, device="cuda")
+    ins, outs = fb.plan_tiles(n, xd, out, (kh, kw), (ph, pw), 0)
+    assert fb.FFTIteratedConvolution(n, ins, outs, wd, 0, 1.0, b)
+    assert orc.rel_l2(host(out), orc.conv_update_output(xp, wt)) < CONV_TOL
+    gw = torch.zeros_like(wd)
+    ins, gouts = fb.plan_tiles(n, xd, god, (kh, kw), (ph, pw), 0)
+    assert fb.FFTIteratedConvolution(n, ins, gouts, gw, 2, 1.0, b)
+    assert orc.rel_l2(host(gw), orc.conv_acc_grad_parameters(xp, go, kh, kw)) < CONV_TOL
+    gi = torch.full(x.shape, 7.0, device="cuda")
+    gins, gouts = fb.plan_tiles(n, gi, god, (kh, kw), (ph, pw), 1)
+    assert fb.FFTIteratedConvolution(n, gins, gouts, wd, 1, 1.0, b)
+    want_gi = orc.conv_update_grad_input(go, wt, h + 2 * ph, w + 2 * pw)[:, :, ph:ph + h, pw:pw + w]
+    assert orc.rel_l2(host(gi), want_gi) < CONV_TOL
+    assert fb.device_status() == 0
+
+
 def test_iterated_convolution_rejects_unknown():
     x = torch.zeros((1, 1, 8, 8), device="cuda")
     t = _tiles([(x, 0, 0)])
