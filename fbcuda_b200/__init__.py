@@ -29,5 +29,8 @@ from .api import (  # noqa: F401
     conv_acc_grad_parameters,
     plan_tiles,
     plan_tiles_layout,
+    tiled_conv_update_output,
+    tiled_conv_update_grad_input,
+    tiled_conv_acc_grad_parameters,
 )
 from . import api  # noqa: F401,E402

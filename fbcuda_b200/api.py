@@ -283,6 +283,7 @@ REUSE_OUTPUT_SPECTRUM = 2
 REUSE_WEIGHT_SPECTRUM = 4
 STOP_AFTER_CONTRACTION = 8
 START_FROM_SPECTRUM = 16
+ACCUMULATE_RESULT = 32
 REGION_INPUT, REGION_OUTPUT, REGION_WEIGHT, REGION_RESULT = 0, 1, 2, 3
 
 
@@ -323,3 +324,59 @@ def conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, 
     return _check(lib().fbfft_b200_conv_acc_grad_parameters(fftSize, *_t(input), inPad[0], inPad[1],
                                                             *_t(gradWeight), *_t(gradOutput), outPad[0], outPad[1],
                                                             float(scale), *_ws(workspace), flags, _stream(stream)))
+
+
+# ---- images larger than the transform: the workspace passes, tile by tile -----------------
+def _tile_windows(fftSize, in_shape, out_shape, kernel, pad, style):
+    """[(input window, input pads), (output window, output pads)] per tile; a window is
+    (y, x, h, w) into the last two axes, pads are (padL, padU)."""
+    ins, outs = plan_tiles_layout(fftSize, in_shape, out_shape, kernel, pad, style)
+    def window(entry, width):
+        off, (h, w), padL, padU = entry
+        return (off // width, off % width, h, w), (padL, padU)
+    return [(window(i, in_shape[3]), window(o, out_shape[3])) for i, o in zip(ins, outs)]
+
+
+def _crop(t, win):
+    y, x, h, w = win
+    return t[:, :, y:y + h, x:x + w]
+
+
+def tiled_conv_update_output(fftSize, input, weight, output, workspace, pad=(0, 0), stream=None):
+    """updateOutput of a stride-1 convolution whose image is larger than the transform: the tiles of
+    plan_tiles (style 0) through conv_update_output, the weight spectrum computed once.
+    pad = (padH, padW) of implicit zeros around the input; the workspace is sized for one tile."""
+    kernel = (weight.shape[2], weight.shape[3])
+    flags = 0
+    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, input.shape, output.shape, kernel, pad, 0):
+        conv_update_output(fftSize, _crop(input, iw), weight, _crop(output, ow), workspace, ipad, opad, flags, stream)
+        flags = REUSE_WEIGHT_SPECTRUM
+    return ErrorCode(0)
+
+
+def tiled_conv_update_grad_input(fftSize, gradInput, weight, gradOutput, workspace, pad=(0, 0), stream=None):
+    """updateGradInput over the tiles of plan_tiles (style 1): every gradInput tile is the crop at
+    (k - 1, k - 1) of the full convolution of its gradOutput window with the weight."""
+    kernel = (weight.shape[2], weight.shape[3])
+    flags = 0
+    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, gradInput.shape, gradOutput.shape, kernel, pad, 1):
+        conv_update_grad_input(fftSize, _crop(gradInput, iw), weight, _crop(gradOutput, ow), workspace, ipad, opad,
+                               flags, stream)
+        flags = REUSE_WEIGHT_SPECTRUM
+    return ErrorCode(0)
+
+
+def tiled_conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, scale=1.0, pad=(0, 0),
+                                   stream=None):
+    """accGradParameters over the tiles of plan_tiles (style 0): the per-tile contractions add up in
+    the workspace's result region (ACCUMULATE_RESULT), one inverse transform at the end."""
+    kernel = (gradWeight.shape[2], gradWeight.shape[3])
+    flags = STOP_AFTER_CONTRACTION
+    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, input.shape, gradOutput.shape, kernel, pad, 0):
+        conv_acc_grad_parameters(fftSize, _crop(input, iw), gradWeight, _crop(gradOutput, ow), workspace, scale, ipad,
+                                 opad, flags, stream)
+        flags = STOP_AFTER_CONTRACTION | ACCUMULATE_RESULT
+    win = (0, 0, min(input.shape[2], fftSize), min(input.shape[3], fftSize))
+    owin = (0, 0, 1, 1)
+    return conv_acc_grad_parameters(fftSize, _crop(input, win), gradWeight, _crop(gradOutput, owin), workspace, scale,
+                                    (0, 0), (0, 0), START_FROM_SPECTRUM, stream)

@@ -112,7 +112,8 @@ bool use_blocked(int n, long long B, long long C, long long O) {
 // plane a_pm*m + a_pk*k of a spectrum region of a_planes planes (same for B and D)
 int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk, long long a_planes, bool conjA,
              const float* b, long long b_pn, long long b_pk, long long b_planes, bool conjB, float* d, long long d_pm,
-             long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s) {
+             long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s,
+             bool accumulate = false) {
   const long long X = bins_of(n);
   if (blocked) {
     // operands in 4-bin blocks (plane stride 4 complex), result in blocks of one stored row (n bins).
@@ -125,10 +126,10 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
     };
     if (padded(N, M) < padded(M, N)) {
       return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, d_pn * n, d_pm * n, N, M, K, (int)X,
-                      inv_norm, false, s, b_planes * 4, a_planes * 4, d_planes * n, 4, 4, n);
+                      inv_norm, accumulate, s, b_planes * 4, a_planes * 4, d_planes * n, 4, 4, n);
     }
     return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K, (int)X,
-                    inv_norm, false, s, a_planes * 4, b_planes * 4, d_planes * n, 4, 4, n);
+                    inv_norm, accumulate, s, a_planes * 4, b_planes * 4, d_planes * n, 4, 4, n);
   }
   // natural layout: D[m][n] = sum_k opA(A[m][k]) opB(B[n][k]) = cgemm_bins with A' = A (rows m),
   // B' = B^T: C[i=m][j=n] = sum_k opA(A[i][k]) * opB'(B'[k][j]), B'[k][j] = B[j][k] -> "conj-transposed" flag
@@ -137,14 +138,14 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
   if (conjA && !conjB) {
     // cgemm_bins conjugates only together with a transposition: op(A)[i][k] = conj(A[k][i]) with
     // strides (as0 for k, as1 for i)
-    return cgemm_bins(true, false, false, a, a_pk * X, a_pm * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
+    return cgemm_bins(true, false, accumulate, a, a_pk * X, a_pm * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
                       (int)X, inv_norm, s);
   }
   if (!conjA && conjB) {
-    return cgemm_bins(false, true, false, a, a_pm * X, a_pk * X, b, b_pn * X, b_pk * X, d, d_pm * X, d_pn * X, M, N, K,
+    return cgemm_bins(false, true, accumulate, a, a_pm * X, a_pk * X, b, b_pn * X, b_pk * X, d, d_pm * X, d_pn * X, M, N, K,
                       (int)X, inv_norm, s);
   }
-  return cgemm_bins(false, false, false, a, a_pm * X, a_pk * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
+  return cgemm_bins(false, false, accumulate, a, a_pm * X, a_pk * X, b, b_pk * X, b_pn * X, d, d_pm * X, d_pn * X, M, N, K,
                     (int)X, inv_norm, s);
 }
 
@@ -295,7 +296,7 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
   const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
   if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
     if (B == 0) {
-      if (cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
+      if (!(flags & FBFFT_CONV_ACCUMULATE_RESULT) && cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
     } else {
       if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
         return rc;
@@ -304,7 +305,8 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
         return rc;
       // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]      (m = o, n = c, k = b)
       rc = contract(n, blk, ws + r.out_off, 1, O, (long long)B * O, true, ws + r.in_off, 1, C, (long long)B * C, false,
-                    ws + r.res_off, C, 1, (long long)O * C, O, C, B, scale / ((float)n * (float)n), s);
+                    ws + r.res_off, C, 1, (long long)O * C, O, C, B, scale / ((float)n * (float)n), s,
+                    (flags & FBFFT_CONV_ACCUMULATE_RESULT) != 0);
       if (rc) return rc;
     }
   }

@@ -188,7 +188,10 @@ enum {
   FBFFT_CONV_REUSE_OUTPUT_SPECTRUM = 2,
   FBFFT_CONV_REUSE_WEIGHT_SPECTRUM = 4,
   FBFFT_CONV_STOP_AFTER_CONTRACTION = 8,
-  FBFFT_CONV_START_FROM_SPECTRUM = 16
+  FBFFT_CONV_START_FROM_SPECTRUM = 16,
+  /* accGradParameters: add this call's contraction to the result region instead of overwriting it
+   * (the weight gradient summed over the tiles of an image larger than the transform) */
+  FBFFT_CONV_ACCUMULATE_RESULT = 32
 };
 enum {
   FBFFT_CONV_REGION_INPUT = 0,
