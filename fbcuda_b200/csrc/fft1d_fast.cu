@@ -1,0 +1,210 @@
+// Batched 1-D real-to-complex / complex-to-real FFTs for N = 8 ... 64 on contiguous tensors
+// (fbfft1D / fbifft1D, fbfft/FBFFT.cuh:11-23; the reference's warp-level kernels are
+// fbfft/FBFFT-inl.cuh:19-150 over fbfft/FBFFTCommon.cuh:307-430).
+//
+// As in the reference two real signals travel as the real and imaginary part of one complex
+// line and are separated afterwards (fbfft/FBFFTCommon.cuh:323-350,397-429).  Here a thread holds
+// the whole line in registers (fully unrolled length-N FFT with compile-time twiddles,
+// fft_regs.cuh) and a warp never synchronises with other warps:
+//   task     32 consecutive signal pairs = 64 signals, owned by one warp
+//   forward  one cp.async.bulk brings the task's 64*N floats into the warp's slot (completion on
+//            the warp's mbarrier, bounded wait); lane t reads pair t with 16-byte loads, transforms,
+//            separates the two spectra and writes them back into the slot at the pitch of the
+//            output tensor, 2*(N+2) floats per pair, which is free of bank conflicts; the slot
+//            leaves through one bulk store.
+//   inverse  the mirror image: one bulk load of 32 * 2*(N+2) floats, Z = A + iB rebuilt with its
+//            Hermitian half in registers, unnormalised inverse FFT, one bulk store of 64*N floats.
+// Leftover signals (B mod 64) and every other shape go through the shared-memory line kernels.
+#include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
+#include "fft_regs.cuh"
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+enum : int { kErrFft1dWait = 105 };
+
+template <int N>
+struct Fast1dCfg {  // slots per warp, warps per block, resident blocks per SM
+  static constexpr int NSLOT = 2, WARPS = 4, BLOCKS = 3;
+};
+template <>
+struct Fast1dCfg<8> {
+  static constexpr int NSLOT = 2, WARPS = 8, BLOCKS = 4;
+};
+template <>
+struct Fast1dCfg<16> {
+  static constexpr int NSLOT = 2, WARPS = 8, BLOCKS = 3;
+};
+template <>
+struct Fast1dCfg<64> {
+  static constexpr int NSLOT = 1, WARPS = 4, BLOCKS = 3;
+};
+
+template <int N>
+constexpr int slot_floats() {
+  return 32 * (2 * N + 4);
+}
+template <int N>
+constexpr int fast1d_smem() {
+  return Fast1dCfg<N>::WARPS * (Fast1dCfg<N>::NSLOT * slot_floats<N>() * 4 + 16);
+}
+
+// INV = false: src real [tasks*64][N], dst complex [tasks*64][N/2+1][2];  INV = true: the reverse
+template <int N, bool INV>
+__global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS)
+    fft1d_fast_kernel(const float* __restrict__ src, float* __restrict__ dst, long long tasks) {
+  constexpr int NSLOT = Fast1dCfg<N>::NSLOT, WARPS = Fast1dCfg<N>::WARPS;
+  constexpr int PC = 2 * N + 4, PR = 2 * N;          // floats per pair: complex side, real side
+  constexpr int PIN = INV ? PC : PR, POUT = INV ? PR : PC;
+  constexpr int SLOT = slot_floats<N>();
+  extern __shared__ __align__(16) float smem1d[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* slots = smem1d + warp * NSLOT * SLOT;
+  const unsigned bars = smem_u32(smem1d + WARPS * NSLOT * SLOT) + warp * 16;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < NSLOT; ++i) mbar_init(bars + 8 * i, 1);
+  }
+  fence_async_smem();
+  __syncwarp();
+  const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
+  auto issue = [&](long long task, int slot) {
+    if (lane == 0) {
+      bulk_wait_read();  // the slot's previous result has left
+      fence_async_smem();
+      mbar_expect_tx(bars + 8 * slot, 32 * PIN * 4);
+      bulk_g2s(smem_u32(slots + slot * SLOT), src + task * (32 * PIN), 32 * PIN * 4, bars + 8 * slot);
+    }
+  };
+  unsigned phases = 0;
+  long long t = gw;
+  if (t < tasks) issue(t, 0);
+  for (int i = 0; t < tasks; t += nw, ++i) {
+    const int slot = (NSLOT == 2) ? (i & 1) : 0;
+    if (NSLOT == 2 && t + nw < tasks) issue(t + nw, slot ^ 1);
+    if (!mbar_wait(bars + 8 * slot, (phases >> slot) & 1, kErrFft1dWait)) return;
+    phases ^= 1u << slot;
+    float* base = slots + slot * SLOT;
+    float2 a[N];
+    if constexpr (!INV) {
+      const float4* s0 = reinterpret_cast<const float4*>(base + lane * PR);
+#pragma unroll
+      for (int j = 0; j < N / 4; ++j) {
+        const float4 u = s0[j], v = s0[N / 4 + j];
+        a[4 * j + 0] = make_float2(u.x, v.x);
+        a[4 * j + 1] = make_float2(u.y, v.y);
+        a[4 * j + 2] = make_float2(u.z, v.z);
+        a[4 * j + 3] = make_float2(u.w, v.w);
+      }
+      __syncwarp();  // the output pitch differs: lanes overwrite one another's input
+      fft_bitrev<N, false>(a);
+      float* o = base + lane * PC;
+      // A[k] = (Z[k] + conj Z[N-k]) / 2 at o[2k], B[k] = (Z[k] - conj Z[N-k]) / 2i at o[N+2+2k]
+      auto sepA = [&](int zk, int mk) {
+        return make_float2(0.5f * (a[zk].x + a[mk].x), 0.5f * (a[zk].y - a[mk].y));
+      };
+      auto sepB = [&](int zk, int mk) {
+        return make_float2(0.5f * (a[zk].y + a[mk].y), 0.5f * (a[mk].x - a[zk].x));
+      };
+      static_for<N / 4>([&](auto kc) {
+        constexpr int k = 2 * decltype(kc)::value;
+        const float2 p = sepA(brev(k, N), brev((N - k) % N, N)), q = sepA(brev(k + 1, N), brev(N - k - 1, N));
+        *reinterpret_cast<float4*>(o + 2 * k) = make_float4(p.x, p.y, q.x, q.y);
+      });
+      *reinterpret_cast<float2*>(o + N) = sepA(brev(N / 2, N), brev(N / 2, N));
+      *reinterpret_cast<float2*>(o + N + 2) = sepB(brev(0, N), brev(0, N));
+      static_for<N / 4>([&](auto kc) {
+        constexpr int k = 2 * decltype(kc)::value + 1;
+        const float2 p = sepB(brev(k, N), brev(N - k, N)), q = sepB(brev(k + 1, N), brev(N - k - 1, N));
+        *reinterpret_cast<float4*>(o + N + 2 + 2 * k) = make_float4(p.x, p.y, q.x, q.y);
+      });
+    } else {
+      const float* o = base + lane * PC;
+      // Z[k] = A[k] + i B[k] for k <= N/2, Z[N-k] = conj A[k] + i conj B[k] for 0 < k < N/2
+      auto put = [&](int k, float2 A, float2 Bv) {
+        a[k] = make_float2(A.x - Bv.y, A.y + Bv.x);
+        if (k > 0 && k < N / 2) a[(N - k) % N] = make_float2(A.x + Bv.y, Bv.x - A.y);
+      };
+      float2 A[N / 2 + 1], Bv[N / 2 + 1];
+      static_for<N / 4>([&](auto kc) {
+        constexpr int k = 2 * decltype(kc)::value;
+        const float4 u = *reinterpret_cast<const float4*>(o + 2 * k);
+        A[k] = make_float2(u.x, u.y), A[k + 1] = make_float2(u.z, u.w);
+      });
+      A[N / 2] = *reinterpret_cast<const float2*>(o + N);
+      Bv[0] = *reinterpret_cast<const float2*>(o + N + 2);
+      static_for<N / 4>([&](auto kc) {
+        constexpr int k = 2 * decltype(kc)::value + 1;
+        const float4 u = *reinterpret_cast<const float4*>(o + N + 2 + 2 * k);
+        Bv[k] = make_float2(u.x, u.y), Bv[k + 1] = make_float2(u.z, u.w);
+      });
+      static_for<N / 2 + 1>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        put(k, A[k], Bv[k]);
+      });
+      __syncwarp();
+      fft_bitrev<N, true>(a);
+      float4* s0 = reinterpret_cast<float4*>(base + lane * PR);
+      static_for<N / 4>([&](auto jc) {
+        constexpr int j = decltype(jc)::value;
+        const float2 z0 = a[brev(4 * j, N)], z1 = a[brev(4 * j + 1, N)], z2 = a[brev(4 * j + 2, N)], z3 = a[brev(4 * j + 3, N)];
+        s0[j] = make_float4(z0.x, z1.x, z2.x, z3.x);
+        s0[N / 4 + j] = make_float4(z0.y, z1.y, z2.y, z3.y);
+      });
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      bulk_s2g(dst + t * (32 * POUT), smem_u32(base), 32 * POUT * 4);
+      bulk_commit();
+    }
+    if (NSLOT == 1 && t + nw < tasks) issue(t + nw, 0);
+  }
+  if (lane == 0) bulk_wait_read();
+}
+
+template <int N, bool INV>
+int launch_fast(const float* src, float* dst, long long tasks, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(fft1d_fast_kernel<N, INV>, cudaFuncAttributeMaxDynamicSharedMemorySize, fast1d_smem<N>());
+    configured[dev] = true;
+  }
+  constexpr int W = Fast1dCfg<N>::WARPS;
+  const long long want = (tasks + W - 1) / W, cap = (long long)sm_count() * Fast1dCfg<N>::BLOCKS;
+  fft1d_fast_kernel<N, INV><<<(int)(want < cap ? want : cap), W * 32, fast1d_smem<N>(), s>>>(src, dst, tasks);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+}  // namespace
+
+// contiguous [B][N] real and [B][N/2+1][2] complex tensors, 16-byte aligned, no padding
+bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, const float* cplx, long long cs0, int cs1,
+                          int cs2, int padL) {
+  if (n != 8 && n != 16 && n != 32 && n != 64) return false;
+  return padL == 0 && rs1 == 1 && rs0 == n && cs2 == 1 && cs1 == 2 && cs0 == n + 2 && aligned16(real) && aligned16(cplx);
+}
+
+// transforms the first `tasks` * 64 signals
+int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s) {
+  if (tasks <= 0) return kSuccess;
+  switch (n) {
+    case 8: return inverse ? launch_fast<8, true>(src, dst, tasks, s) : launch_fast<8, false>(src, dst, tasks, s);
+    case 16: return inverse ? launch_fast<16, true>(src, dst, tasks, s) : launch_fast<16, false>(src, dst, tasks, s);
+    case 32: return inverse ? launch_fast<32, true>(src, dst, tasks, s) : launch_fast<32, false>(src, dst, tasks, s);
+    case 64: return inverse ? launch_fast<64, true>(src, dst, tasks, s) : launch_fast<64, false>(src, dst, tasks, s);
+    default: return kUnsupportedSize;
+  }
+}
+
+int read_device_error_fft1d() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace fbfft_b200

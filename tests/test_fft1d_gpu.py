@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("n", [8, 16, 32, 64, 128, 256])
-@pytest.mark.parametrize("b", [1, 2, 3, 5, 64, 4096])
+@pytest.mark.parametrize("b", [1, 2, 3, 5, 64, 65, 1000, 4096])
 def test_fbfft1d_roundtrip(n, b):
     rng = np.random.default_rng(1000 * n + b)
     x = rng.uniform(-1, 1, (b, n)).astype(np.float32)
@@ -32,6 +32,33 @@ def test_fbfft1d_roundtrip(n, b):
         assert orc.rel_l2(got[:, : n - pad], want_back[:, : n - pad]) < FFT_TOL, (n, b, pad)
         if pad:
             assert np.all(got[:, n - pad:] == 7.0)   # columns the shifted window never reaches are untouched
+
+
+@pytest.mark.parametrize("n,b", [(8, 700001), (16, 300030), (32, 200001), (64, 100003)])
+def test_fbfft1d_many_signals(n, b):
+    """More groups of 64 signals than resident warps (every warp loops over several groups and
+    reuses its shared-memory slots), plus a tail that is not a multiple of 64."""
+    rng = np.random.default_rng(n + b)
+    x = rng.uniform(-1, 1, (b, n)).astype(np.float32)
+    raw, out = canary_alloc((b, n // 2 + 1, 2))
+    assert fb.fbfft1D(dev(x), out) == fb.ErrorCode.Success
+    torch.cuda.synchronize()
+    check_canary(raw, out.numel())
+    want = np.fft.rfft(x.astype(np.float64), axis=1)
+    got = host(out).astype(np.float64)
+    got = got[..., 0] + 1j * got[..., 1]
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < FFT_TOL
+    # every signal, not only the norm: the worst one
+    per = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+    assert per.max() < 10 * FFT_TOL, int(per.argmax())
+    raw2, back = canary_alloc((b, n))
+    assert fb.fbifft1D(back, out) == fb.ErrorCode.Success
+    torch.cuda.synchronize()
+    check_canary(raw2, back.numel())
+    got_back = host(back).astype(np.float64) / n
+    per = np.linalg.norm(got_back - x, axis=1) / np.linalg.norm(x, axis=1)
+    assert per.max() < 10 * FFT_TOL, int(per.argmax())
+    assert fb.device_status() == 0
 
 
 def test_config1_signals():
