@@ -283,6 +283,21 @@ def run_fft2d(args, world, rank, local):
         def step():  # noqa: F811
             fb.fft2d_c2r(n, spec, back)
 
+    if args.profile_case and args.one_d:
+        # fbfft1D / fbifft1D on 256 MiB of signals of length N
+        b = GIB // 4 // (4 * n)
+        x = torch.rand((b, n), device="cuda", generator=gen) * 2 - 1
+        spec = torch.empty((b, n // 2 + 1, 2), device="cuda")
+        per_image = 4 * n + 8 * (n // 2 + 1)
+        hw = 1
+        fb.fbfft1D(x, spec)
+
+        def step():  # noqa: F811
+            if args.inverse:
+                fb.fbifft1D(x, spec)
+            else:
+                fb.fbfft1D(x, spec)
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -293,7 +308,8 @@ def run_fft2d(args, world, rank, local):
     gbs = world * b * per_image / (ms / 1e3) / 1e9
     if args.profile_case:
         return {"metric": "batched fbfft2D GB/s", "value": gbs, "unit": "GB/s", "ms_per_step": ms,
-                "config": {"workload": f"profile case: fbfft2D N={n} over {b} images of {hw}x{hw}"}, "clocks": clocks}
+                "config": {"workload": (f"profile case: fbfft1D N={n} over {b} signals" if args.one_d else
+                                        f"profile case: fbfft2D N={n} over {b} images of {hw}x{hw}")}, "clocks": clocks}
 
     # end to end through the public call with HOST buffers: H2D of the images, the
     # transform, D2H of the spectrum, every step
@@ -356,7 +372,8 @@ def run_fft2d(args, world, rank, local):
 
 def run_extras(args, x, spec, n0, hw0):
     """The inverse of the default workload (fbifft2D with crop back to the image size), then the
-    size sweep forward + inverse (1 GiB of N x N input each) on one GPU, for the record."""
+    size sweep forward + inverse (1 GiB of N x N input each) and the 1-D sweep (1 GiB of signals
+    of length N each) on one GPU, for the record."""
     import torch
     import fbcuda_b200 as fb
     peak, _ = measured_peak_gbs()
@@ -384,7 +401,21 @@ def run_extras(args, x, spec, n0, hw0):
         sweep[str(n)] = entry
         del x, spec, back
         torch.cuda.empty_cache()
-    return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep}
+    # fbfft1D / fbifft1D on 1 GiB of signals: 4N bytes in, 8(N/2+1) bytes out per signal
+    sweep1d = {}
+    for n in (8, 16, 32, 64, 128, 256):
+        b = GIB // (4 * n)
+        x = torch.rand((b, n), device="cuda") * 2 - 1
+        spec = torch.empty((b, n // 2 + 1, 2), device="cuda")
+        back = torch.empty_like(x)
+        byts = b * (4 * n + 8 * (n // 2 + 1))
+        ms_f = time_steps(lambda: fb.fbfft1D(x, spec), 10, 3, 1)
+        ms_i = time_steps(lambda: fb.fbifft1D(back, spec), 10, 3, 1)
+        sweep1d[str(n)] = {"fwd_us": ms_f * 1e3, "fwd_gbs": byts / ms_f / 1e6, "fwd_frac_of_measured": byts / ms_f / 1e6 / peak,
+                           "inv_us": ms_i * 1e3, "inv_gbs": byts / ms_i / 1e6, "inv_frac_of_measured": byts / ms_i / 1e6 / peak}
+        del x, spec, back
+        torch.cuda.empty_cache()
+    return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d}
 
 
 def run_conv(args, world, rank, local):
@@ -528,6 +559,7 @@ def main():
     ap.add_argument("--extras", type=int, default=1)
     ap.add_argument("--profile-case", action="store_true", help="small fft2d case for profiler captures")
     ap.add_argument("--inverse", action="store_true", help="profile case: time fbifft2D instead of fbfft2D")
+    ap.add_argument("--one-d", action="store_true", help="profile case: fbfft1D / fbifft1D on signals of length --fft-size")
     args = ap.parse_args()
 
     if args.impl == "reference":

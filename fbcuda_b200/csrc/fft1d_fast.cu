@@ -8,7 +8,8 @@
 // fft_regs.cuh) and a warp never synchronises with other warps:
 //   task     32 consecutive signal pairs = 64 signals, owned by one warp
 //   forward  one cp.async.bulk brings the task's 64*N floats into the warp's slot (completion on
-//            the warp's mbarrier, bounded wait); lane t reads pair t with 16-byte loads, transforms,
+//            the warp's mbarrier, bounded wait; at N = 64 one copy per lane, to a conflict-free
+//            pitch); lane t reads pair t with 16-byte loads, transforms,
 //            separates the two spectra and writes them back into the slot at the pitch of the
 //            output tensor, 2*(N+2) floats per pair, which is free of bank conflicts; the slot
 //            leaves through one bulk store.
@@ -16,6 +17,7 @@
 //            Hermitian half in registers, unnormalised inverse FFT, one bulk store of 64*N floats.
 // Leftover signals (B mod 64) and every other shape go through the shared-memory line kernels.
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
+#include "coop_fft.cuh"
 #include "fft_regs.cuh"
 #include "kernels.h"
 
@@ -26,20 +28,24 @@ namespace {
 enum : int { kErrFft1dWait = 105 };
 
 template <int N>
-struct Fast1dCfg {  // slots per warp, warps per block, resident blocks per SM
+struct Fast1dCfg {  // slots per warp, warps per block, resident blocks per SM, per-lane input copies
   static constexpr int NSLOT = 2, WARPS = 4, BLOCKS = 3;
+  static constexpr bool PADIN = false;
 };
 template <>
 struct Fast1dCfg<8> {
   static constexpr int NSLOT = 2, WARPS = 8, BLOCKS = 4;
+  static constexpr bool PADIN = false;
 };
 template <>
 struct Fast1dCfg<16> {
   static constexpr int NSLOT = 2, WARPS = 8, BLOCKS = 3;
+  static constexpr bool PADIN = false;
 };
 template <>
 struct Fast1dCfg<64> {
   static constexpr int NSLOT = 1, WARPS = 4, BLOCKS = 3;
+  static constexpr bool PADIN = true  /* measured: 0.80 -> 0.88; no gain at N = 32 */;
 };
 
 template <int N>
@@ -70,12 +76,19 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
   fence_async_smem();
   __syncwarp();
   const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
+  // PADIN (forward): every lane copies its own pair to the output pitch, so that the 16-byte reads
+  // below are free of bank conflicts (the dense layout puts all lanes on the same four banks)
+  constexpr bool PADIN = !INV && Fast1dCfg<N>::PADIN;
   auto issue = [&](long long task, int slot) {
     if (lane == 0) {
       bulk_wait_read();  // the slot's previous result has left
       fence_async_smem();
       mbar_expect_tx(bars + 8 * slot, 32 * PIN * 4);
-      bulk_g2s(smem_u32(slots + slot * SLOT), src + task * (32 * PIN), 32 * PIN * 4, bars + 8 * slot);
+      if (!PADIN) bulk_g2s(smem_u32(slots + slot * SLOT), src + task * (32 * PIN), 32 * PIN * 4, bars + 8 * slot);
+    }
+    if (PADIN) {
+      __syncwarp();
+      bulk_g2s(smem_u32(slots + slot * SLOT + lane * PC), src + task * (32 * PR) + lane * PR, PR * 4, bars + 8 * slot);
     }
   };
   unsigned phases = 0;
@@ -89,7 +102,7 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
     float* base = slots + slot * SLOT;
     float2 a[N];
     if constexpr (!INV) {
-      const float4* s0 = reinterpret_cast<const float4*>(base + lane * PR);
+      const float4* s0 = reinterpret_cast<const float4*>(base + lane * (PADIN ? PC : PR));
 #pragma unroll
       for (int j = 0; j < N / 4; ++j) {
         const float4 u = s0[j], v = s0[N / 4 + j];
@@ -165,6 +178,148 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
   if (lane == 0) bulk_wait_read();
 }
 
+// ---- N = 128, 256: a line shared by Q = N/64 lanes (coop_fft.cuh), 32/Q pairs per warp ------------
+// Same slot protocol with one slot per warp.  Forward: one bulk copy per pair to the output pitch;
+// lane (q, l) loads its quarter-runs of pair l, the transform leaves Z[Q*k + q] in lane q, the line is
+// parked in the pair's own region, every lane separates the bins k = q, q + Q, ... <= N/2 into
+// registers and (after the warp has read everything) writes A and B in the output layout; one bulk
+// store per task.  Inverse: one bulk load per task, Z[x] rebuilt while loading (mirrored for
+// x > N/2), one bulk store per pair.
+template <int N>
+constexpr int coop1d_smem() {
+  return 4 * ((32 / (N / 64)) * (2 * N + 4) * 4 + 16);
+}
+
+template <int N, bool INV>
+__global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                            long long tasks) {
+  constexpr int R = 64, Q = N / R, P = R / Q, LP = 32 / Q, WARPS = 4;
+  constexpr int PC = 2 * N + 4, PR = 2 * N, SLOT = LP * PC;
+  extern __shared__ __align__(16) float smem1d[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane / LP, l = lane % LP;
+  float* slot = smem1d + warp * SLOT;
+  float* region = slot + l * PC;
+  const unsigned bar = smem_u32(smem1d + WARPS * SLOT) + warp * 16;
+  if (lane == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  __syncwarp();
+  float2 lf[Q];
+  lane_factors<Q, INV>(q, lf);
+  const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
+  auto issue = [&](long long task) {
+    if (INV && lane < LP) bulk_wait_read();  // this lane's pair has left the slot
+    __syncwarp();
+    if (lane == 0) {
+      if (!INV) bulk_wait_read();
+      fence_async_smem();
+      mbar_expect_tx(bar, LP * (INV ? PC : PR) * 4);
+      if (INV) bulk_g2s(smem_u32(slot), src + task * SLOT, SLOT * 4, bar);
+    }
+    if (!INV) {
+      __syncwarp();
+      if (lane < LP) bulk_g2s(smem_u32(region), src + (task * LP + l) * PR, PR * 4, bar);
+    }
+  };
+  unsigned phase = 0;
+  long long t = gw;
+  if (t < tasks) issue(t);
+  for (; t < tasks; t += nw) {
+    if (!mbar_wait(bar, phase, kErrFft1dWait)) return;
+    phase ^= 1;
+    float2 a[R];
+    if constexpr (!INV) {
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int j4 = 0; j4 < P / 4; ++j4) {
+          const float4 u = *reinterpret_cast<const float4*>(region + P * q + R * m + 4 * j4);
+          const float4 v = *reinterpret_cast<const float4*>(region + N + P * q + R * m + 4 * j4);
+          a[m * P + 4 * j4 + 0] = make_float2(u.x, v.x);
+          a[m * P + 4 * j4 + 1] = make_float2(u.y, v.y);
+          a[m * P + 4 * j4 + 2] = make_float2(u.z, v.z);
+          a[m * P + 4 * j4 + 3] = make_float2(u.w, v.w);
+        }
+      }
+      coop_fft<N, R, Q, false>(a, q, lf);
+      __syncwarp();
+      float2* zl = reinterpret_cast<float2*>(region);
+      static_for<R>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        zl[Q * k + q] = a[brev(k, R)];
+      });
+      __syncwarp();
+      // bins k = q + Q*i <= N/2 (a[] is dead from here on)
+      constexpr int NB = N / 2 / Q + 1;
+      float2 sa[NB], sb[NB];
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const int k = q + Q * i;
+        if (k <= N / 2) {
+          const float2 z = zl[k], m = zl[(N - k) & (N - 1)];
+          sa[i] = make_float2(0.5f * (z.x + m.x), 0.5f * (z.y - m.y));
+          sb[i] = make_float2(0.5f * (z.y + m.y), 0.5f * (m.x - z.x));
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < NB; ++i) {
+        const int k = q + Q * i;
+        if (k <= N / 2) {
+          zl[k] = sa[i];
+          zl[N / 2 + 1 + k] = sb[i];
+        }
+      }
+    } else {
+      const float2* zl = reinterpret_cast<const float2*>(region);
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) {
+          const int x = jl + P * q + R * m;
+          const bool low = x <= N / 2;
+          const int k = low ? x : N - x;
+          const float2 A = zl[k], Bv = zl[N / 2 + 1 + k];
+          a[m * P + jl] = low ? make_float2(A.x - Bv.y, A.y + Bv.x) : make_float2(A.x + Bv.y, Bv.x - A.y);
+        }
+      }
+      coop_fft<N, R, Q, true>(a, q, lf);
+      __syncwarp();
+      static_for<R>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
+        region[Q * k + q] = a[brev(k, R)].x;
+        region[N + Q * k + q] = a[brev(k, R)].y;
+      });
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (INV) {
+      if (lane < LP) {
+        bulk_s2g(dst + (t * LP + l) * PR, smem_u32(region), PR * 4);
+        bulk_commit();
+      }
+    } else if (lane == 0) {
+      bulk_s2g(dst + t * SLOT, smem_u32(slot), SLOT * 4);
+      bulk_commit();
+    }
+    if (t + nw < tasks) issue(t + nw);
+  }
+  bulk_wait_read();
+}
+
+template <int N, bool INV>
+int launch_coop1d(const float* src, float* dst, long long tasks, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(fft1d_coop_kernel<N, INV>, cudaFuncAttributeMaxDynamicSharedMemorySize, coop1d_smem<N>());
+    configured[dev] = true;
+  }
+  const long long want = (tasks + 3) / 4, cap = (long long)sm_count() * 3;
+  fft1d_coop_kernel<N, INV><<<(int)(want < cap ? want : cap), 128, coop1d_smem<N>(), s>>>(src, dst, tasks);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
 template <int N, bool INV>
 int launch_fast(const float* src, float* dst, long long tasks, cudaStream_t s) {
   static bool configured[64];
@@ -185,11 +340,14 @@ int launch_fast(const float* src, float* dst, long long tasks, cudaStream_t s) {
 // contiguous [B][N] real and [B][N/2+1][2] complex tensors, 16-byte aligned, no padding
 bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, const float* cplx, long long cs0, int cs1,
                           int cs2, int padL) {
-  if (n != 8 && n != 16 && n != 32 && n != 64) return false;
+  if (n != 8 && n != 16 && n != 32 && n != 64 && n != 128 && n != 256) return false;
   return padL == 0 && rs1 == 1 && rs0 == n && cs2 == 1 && cs1 == 2 && cs0 == n + 2 && aligned16(real) && aligned16(cplx);
 }
 
-// transforms the first `tasks` * 64 signals
+// signals per task (a warp's unit of work)
+int fft1d_fast_group(int n) { return n <= 64 ? 64 : 64 / (n / 64); }
+
+// transforms the first `tasks` * fft1d_fast_group(n) signals
 int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s) {
   if (tasks <= 0) return kSuccess;
   switch (n) {
@@ -197,6 +355,8 @@ int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long task
     case 16: return inverse ? launch_fast<16, true>(src, dst, tasks, s) : launch_fast<16, false>(src, dst, tasks, s);
     case 32: return inverse ? launch_fast<32, true>(src, dst, tasks, s) : launch_fast<32, false>(src, dst, tasks, s);
     case 64: return inverse ? launch_fast<64, true>(src, dst, tasks, s) : launch_fast<64, false>(src, dst, tasks, s);
+    case 128: return inverse ? launch_coop1d<128, true>(src, dst, tasks, s) : launch_coop1d<128, false>(src, dst, tasks, s);
+    case 256: return inverse ? launch_coop1d<256, true>(src, dst, tasks, s) : launch_coop1d<256, false>(src, dst, tasks, s);
     default: return kUnsupportedSize;
   }
 }

@@ -307,9 +307,9 @@ int dispatch_size(int n, F&& f) {
 int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,
                   cudaStream_t s) {
   if (B >= 64 && fft1d_fast_supported(n, real, rs0, rs1, cplx, cs0, cs1, cs2, padL)) {
-    // whole groups of 64 signals through the register kernel, the rest below
-    const int done = (B / 64) * 64;
-    if (int rc = fft1d_fast(n, false, real, cplx, B / 64, s)) return rc;
+    // whole groups of signals through the register kernels, the rest below
+    const int g = fft1d_fast_group(n), done = (B / g) * g;
+    if (int rc = fft1d_fast(n, false, real, cplx, B / g, s)) return rc;
     if (done == B) return kSuccess;
     real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
   }
@@ -326,8 +326,8 @@ int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int c
 int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* real, int rs0, int rs1, int B, int padL,
                   cudaStream_t s) {
   if (B >= 64 && fft1d_fast_supported(n, real, rs0, rs1, cplx, cs0, cs1, cs2, padL)) {
-    const int done = (B / 64) * 64;
-    if (int rc = fft1d_fast(n, true, cplx, real, B / 64, s)) return rc;
+    const int g = fft1d_fast_group(n), done = (B / g) * g;
+    if (int rc = fft1d_fast(n, true, cplx, real, B / g, s)) return rc;
     if (done == B) return kSuccess;
     real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
   }

@@ -42,6 +42,7 @@ int fft_lines_inplace(int n, const CplxView& t, int B, int lines, bool inverse, 
 // register-resident fast path for contiguous tensors, N <= 64 (fft1d_fast.cu)
 bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, const float* cplx, long long cs0, int cs1,
                           int cs2, int padL);
+int fft1d_fast_group(int n);
 int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s);
 int read_device_error_fft1d();
 int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,

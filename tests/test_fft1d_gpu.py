@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("n", [8, 16, 32, 64, 128, 256])
-@pytest.mark.parametrize("b", [1, 2, 3, 5, 64, 65, 1000, 4096])
+@pytest.mark.parametrize("b", [1, 2, 3, 5, 64, 65, 100, 1000, 4096])
 def test_fbfft1d_roundtrip(n, b):
     rng = np.random.default_rng(1000 * n + b)
     x = rng.uniform(-1, 1, (b, n)).astype(np.float32)
@@ -34,7 +34,7 @@ def test_fbfft1d_roundtrip(n, b):
             assert np.all(got[:, n - pad:] == 7.0)   # columns the shifted window never reaches are untouched
 
 
-@pytest.mark.parametrize("n,b", [(8, 700001), (16, 300030), (32, 200001), (64, 100003)])
+@pytest.mark.parametrize("n,b", [(8, 700001), (16, 300030), (32, 200001), (64, 100003), (128, 150001), (256, 80001)])
 def test_fbfft1d_many_signals(n, b):
     """More groups of 64 signals than resident warps (every warp loops over several groups and
     reuses its shared-memory slots), plus a tail that is not a multiple of 64."""
