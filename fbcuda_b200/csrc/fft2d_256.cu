@@ -8,15 +8,17 @@
 // output's lines in place.  Both passes hold every line in registers, shared by 4 neighbouring lane
 // groups of a warp (radix-4 step, one all-to-all by __shfl_xor_sync, 64-point FFT per lane with
 // compile-time twiddles: coop_fft.cuh).
-//   rows     a block takes 64 consecutive rows of one image; rows 2l and 2l+1 travel as re/im of one
-//            complex line (a warp holds 8 lines); the lines' transforms Z are parked in shared
+//   rows     a block takes 64 consecutive rows of one image (contiguous images: 32 bulk copies of one
+//            row pair each into shared memory, completion on an mbarrier with a bounded wait);
+//            rows 2l and 2l+1 travel as re/im of one complex line (a warp holds 8 lines); the lines' transforms Z are parked in shared
 //            memory, then thread (kx, l) separates the two real spectra, A = (Z[kx] + conj Z[N-kx])/2
 //            and B = (Z[kx] - conj Z[N-kx])/2i, and stores both as 16 bytes at out[kx][2l..2l+1]:
 //            a warp writes 512 contiguous bytes.
-//   columns  a warp takes 8 lines out[kx][*] (2 KB each, contiguous), transforms them and stores
-//            X[4k + q] from lane group q: every store instruction fills whole 32-byte sectors.
+//   columns  a warp takes 8 lines out[kx][*] (2 KB each, contiguous) through its shared-memory slot:
+//            bulk copies in, transform in registers, bulk copies out.
 // HBM traffic is twice the algorithmic bytes (the spectrum is written, read and written again).
 #include "coop_fft.cuh"
+#include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "kernels.h"
 
 namespace fbfft_b200 {
@@ -27,12 +29,20 @@ constexpr int N256 = 256, R256 = 64, Q256 = 4, P256 = R256 / Q256, LP256 = 32 / 
 constexpr int kRowsThreads = 128;                       // 4 warps x 8 lines = 32 lines = 64 rows
 constexpr int kLinesPerBlock = (kRowsThreads / 32) * LP256;
 constexpr int PZ = N256 + 2;                            // line pitch in shared memory (complex values)
+enum : int { kErrColsWait = 106, kErrRowsWait = 107 };
 
 // FULL: the images are contiguous 256 x 256 without padding (16-byte loads, no predicates)
 template <bool FULL>
 __global__ void __launch_bounds__(kRowsThreads, 3) fft256_rows_kernel(RealView in, float* __restrict__ out, long long out_sb,
                                                                        int B, int padL, int padU) {
-  extern __shared__ __align__(16) float2 zs[];  // [32 lines][PZ]
+  extern __shared__ __align__(16) float2 zs[];  // [32 lines][PZ], then the mbarrier (FULL)
+  const unsigned bar = smem_u32(zs + kLinesPerBlock * PZ);
+  unsigned phase = 0;
+  if (FULL) {
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    fence_async_smem();
+    __syncthreads();
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = lane / LP256, line = warp * LP256 + (lane % LP256);
   float2 lf[Q256];
@@ -45,13 +55,21 @@ __global__ void __launch_bounds__(kRowsThreads, 3) fft256_rows_kernel(RealView i
     float2 a[R256];
     const float* src = in.p + b * in.sb;
     if constexpr (FULL) {
-      const float4* r0 = reinterpret_cast<const float4*>(src + (long long)y0 * N256 + P256 * q);
-      const float4* r1 = reinterpret_cast<const float4*>(src + (long long)(y0 + 1) * N256 + P256 * q);
+      // the band's 64 rows arrive as 32 bulk copies of one row pair (2 KB) each into the lines'
+      // own regions (pitch 258 complex values: the 16-byte reads below are free of bank conflicts)
+      fence_async_smem();  // this thread's accesses to the lines precede the copies that overwrite them
+      if (threadIdx.x == 0) mbar_expect_tx(bar, kLinesPerBlock * 2 * N256 * 4);
+      __syncthreads();  // (also: the previous band's lines have been read)
+      if (q == 0) bulk_g2s(smem_u32(zs + line * PZ), src + (long long)y0 * N256, 2 * N256 * 4, bar);
+      if (!mbar_wait(bar, phase, kErrRowsWait)) return;
+      phase ^= 1;
+      const float* r0 = reinterpret_cast<const float*>(zs + line * PZ) + P256 * q;
 #pragma unroll
       for (int m = 0; m < Q256; ++m) {
 #pragma unroll
         for (int j4 = 0; j4 < P256 / 4; ++j4) {
-          const float4 u = __ldg(r0 + m * (R256 / 4) + j4), v = __ldg(r1 + m * (R256 / 4) + j4);
+          const float4 u = *reinterpret_cast<const float4*>(r0 + m * R256 + 4 * j4);
+          const float4 v = *reinterpret_cast<const float4*>(r0 + N256 + m * R256 + 4 * j4);
           a[m * P256 + j4 * 4 + 0] = make_float2(u.x, v.x);
           a[m * P256 + j4 * 4 + 1] = make_float2(u.y, v.y);
           a[m * P256 + j4 * 4 + 2] = make_float2(u.z, v.z);
@@ -75,7 +93,11 @@ __global__ void __launch_bounds__(kRowsThreads, 3) fft256_rows_kernel(RealView i
       }
     }
     coop_fft<N256, R256, Q256, false>(a, q, lf);
-    __syncthreads();  // the previous band's lines have been read
+    if constexpr (FULL) {
+      __syncwarp();  // the lanes of a line have read its staged rows
+    } else {
+      __syncthreads();  // the previous band's lines have been read
+    }
     static_for<R256>([&](auto kc) {
       constexpr int k = decltype(kc)::value;
       zs[line * PZ + Q256 * k + q] = a[brev(k, R256)];
@@ -92,36 +114,71 @@ __global__ void __launch_bounds__(kRowsThreads, 3) fft256_rows_kernel(RealView i
   }
 }
 
-// in-place transform of `lines` contiguous lines of 256 complex values
-__global__ void __launch_bounds__(128, 3) fft256_cols_kernel(float* __restrict__ data, long long lines) {
-  const int lane = threadIdx.x & 31, q = lane / LP256;
+// in-place transform of `lines` contiguous lines of 256 complex values.  A warp takes 8 lines at a
+// time: one cp.async.bulk per line into the warp's slot (pitch 258 complex values, so that the
+// 16-byte reads of the 8 lines fall on different banks; completion on the warp's mbarrier, bounded
+// wait), transform in registers, lines parked back in natural order, one bulk store per line.
+constexpr int kColsWarps = 4;
+constexpr int kColsSlot = LP256 * PZ;  // complex values per warp
+constexpr int kColsSmem = kColsWarps * (kColsSlot * (int)sizeof(float2) + 16);
+
+
+__global__ void __launch_bounds__(kColsWarps * 32, 3) fft256_cols_kernel(float* __restrict__ data, long long lines) {
+  extern __shared__ __align__(16) float2 cs[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, q = lane / LP256, l = lane % LP256;
+  float2* region = cs + warp * kColsSlot + l * PZ;
+  const unsigned bar = smem_u32(cs + kColsWarps * kColsSlot) + warp * 16;
+  if (lane == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  __syncwarp();
   float2 lf[Q256];
   lane_factors<Q256, false>(q, lf);
-  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w * LP256 < lines; w += warps) {
-    const long long l = w * LP256 + (lane % LP256);
-    const bool live = l < lines;
+  const long long tasks = (lines + LP256 - 1) / LP256;
+  const long long gw = (long long)blockIdx.x * kColsWarps + warp, nw = (long long)gridDim.x * kColsWarps;
+  auto issue = [&](long long task) {
+    const long long first = task * LP256;
+    const int valid = lines - first < LP256 ? (int)(lines - first) : LP256;
+    if (lane < LP256) bulk_wait_read();  // this lane's line has left the slot
+    __syncwarp();
+    if (lane == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, valid * N256 * 8);
+    }
+    __syncwarp();
+    if (lane < valid) bulk_g2s(smem_u32(region), data + (first + l) * (2 * N256), N256 * 8, bar);
+  };
+  unsigned phase = 0;
+  long long t = gw;
+  if (t < tasks) issue(t);
+  for (; t < tasks; t += nw) {
+    if (!mbar_wait(bar, phase, kErrColsWait)) return;
+    phase ^= 1;
     float2 a[R256];
-    float* base = data + (live ? l : 0) * (2 * N256);
-    const float4* src = reinterpret_cast<const float4*>(base + 2 * P256 * q);
 #pragma unroll
     for (int m = 0; m < Q256; ++m) {
 #pragma unroll
       for (int j2 = 0; j2 < P256 / 2; ++j2) {
-        const float4 u = src[m * R256 / 2 + j2];  // two complex values
+        const float4 u = *reinterpret_cast<const float4*>(region + P256 * q + R256 * m + 2 * j2);
         a[m * P256 + 2 * j2] = make_float2(u.x, u.y);
         a[m * P256 + 2 * j2 + 1] = make_float2(u.z, u.w);
       }
     }
     coop_fft<N256, R256, Q256, false>(a, q, lf);
-    if (live) {
-      float2* dst = reinterpret_cast<float2*>(base) + q;
-      static_for<R256>([&](auto kc) {
-        constexpr int k = decltype(kc)::value;
-        dst[Q256 * k] = a[brev(k, R256)];
-      });
+    __syncwarp();
+    static_for<R256>([&](auto kc) {
+      constexpr int k = decltype(kc)::value;
+      region[Q256 * k + q] = a[brev(k, R256)];
+    });
+    fence_async_smem();
+    __syncwarp();
+    const long long line = t * LP256 + l;
+    if (lane < LP256 && line < lines) {
+      bulk_s2g(data + line * (2 * N256), smem_u32(region), N256 * 8);
+      bulk_commit();
     }
+    if (t + nw < tasks) issue(t + nw);
   }
+  bulk_wait_read();
 }
 
 }  // namespace
@@ -137,10 +194,11 @@ int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, 
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  const int smem = kLinesPerBlock * PZ * (int)sizeof(float2);
+  const int smem = kLinesPerBlock * PZ * (int)sizeof(float2) + 16;
   if (dev >= 0 && dev < 64 && !configured[dev]) {
     cudaFuncSetAttribute(fft256_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cudaFuncSetAttribute(fft256_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(fft256_cols_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kColsSmem);
     configured[dev] = true;
   }
   const long long work = (long long)B * 4;
@@ -155,10 +213,16 @@ int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, 
   }
   if (cudaPeekAtLastError() != cudaSuccess) return kCudaError;
   const long long lines = (long long)B * (N256 / 2 + 1);
-  const long long wblocks = (lines + 4 * LP256 - 1) / (4 * LP256);
+  const long long wblocks = (lines + kColsWarps * LP256 - 1) / (kColsWarps * LP256);
   const int grid2 = wblocks < cap ? (int)wblocks : cap;
-  fft256_cols_kernel<<<grid2, 128, 0, s>>>(out.p, lines);
+  fft256_cols_kernel<<<grid2, kColsWarps * 32, kColsSmem, s>>>(out.p, lines);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+int read_device_error_256() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
 }
 
 }  // namespace fbfft_b200

@@ -45,6 +45,7 @@ bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, cons
 int fft1d_fast_group(int n);
 int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s);
 int read_device_error_fft1d();
+int read_device_error_256();
 int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,
                   cudaStream_t s);
 int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* real, int rs0, int rs1, int B, int padL,

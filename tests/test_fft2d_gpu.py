@@ -153,3 +153,17 @@ def test_config2_shapes_roundtrip():
 def test_no_device_error_recorded():
     """Bounded waits inside the kernels record an error instead of hanging; none may have fired."""
     assert fb.device_status() == 0
+
+
+def test_n256_many_images():
+    """More work than one wave of the two N = 256 passes (every block and warp loops and reuses its
+    shared-memory staging), against numpy's float64 transform, image by image."""
+    b, n = 300, 256
+    rng = np.random.default_rng(256)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    spec = gpu_fft2d(x, n, 0, 0).astype(np.float64)
+    got = spec[..., 0] + 1j * spec[..., 1]                                  # [b][kx][ky]
+    want = np.fft.rfft2(x.astype(np.float64)).transpose(0, 2, 1)            # [b][ky][kx] -> [b][kx][ky]
+    per = np.linalg.norm((got - want).reshape(b, -1), axis=1) / np.linalg.norm(want.reshape(b, -1), axis=1)
+    assert per.max() < FFT_TOL, int(per.argmax())
+    assert fb.device_status() == 0
