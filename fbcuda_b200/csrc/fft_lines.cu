@@ -344,6 +344,13 @@ int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* re
 int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, int B, int padL, int padU,
                              cudaStream_t s) {
   if (n < 64) return kUnsupportedSize;
+  // contiguous N x N images into a contiguous [B][N][N/2+1] buffer: the row pass is a batch of
+  // B * N 1-D transforms (whole groups of rows; N is a multiple of the group)
+  if (n <= 256 && padL == 0 && padU == 0 && in.h == n && in.w == n && in.sx == 1 && in.sy == n && !buffer.blk_planes &&
+      buffer.sz == 1 && buffer.sc == 2 && buffer.sr == n + 2 && (B <= 1 || (in.sb == (long long)n * n && buffer.sb == (long long)n * (n + 2))) &&
+      fft1d_fast_supported(n, in.p, n, 1, buffer.p, n + 2, 2, 1, 0)) {
+    return fft1d_fast(n, false, in.p, buffer.p, (long long)B * n / fft1d_fast_group(n), s);
+  }
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;
     if constexpr (N >= 64) {

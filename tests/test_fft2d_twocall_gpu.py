@@ -37,6 +37,21 @@ def test_two_call_forward_and_inverse(n, b):
     assert orc.rel_l2(host(back), n * n * x.astype(np.float64)) < FFT_TOL
 
 
+@pytest.mark.parametrize("n", [64, 128, 256])
+def test_two_call_forward_full_contiguous_images(n):
+    """Contiguous N x N images without padding: the row pass runs as a batch of 1-D transforms."""
+    b = 3
+    rng = np.random.default_rng(7 * n)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    buf = torch.zeros((b, n, n // 2 + 1, 2), device="cuda")
+    assert fb.fbfft2D(dev(x), buf) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(buf), orc.fbfft2d_rows(x, n, 0, 0)) < FFT_TOL
+    spec = torch.zeros((b, n // 2 + 1, n, 2), device="cuda")
+    assert fb.fbfft2D_c2c(buf, spec) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(spec), orc.fbfft2d(x, n, 0, 0)) < FFT_TOL
+    assert fb.device_status() == 0
+
+
 def test_two_call_errors():
     with pytest.raises(fb.FbfftError):
         # src and dst must differ
