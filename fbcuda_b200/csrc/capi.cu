@@ -101,8 +101,8 @@ const char* fbfft_b200_last_error(void) { return g_last_error; }
 
 int fbfft_b200_device_status(void) {
   const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc(), d = read_device_error_tma(),
-            e = read_device_error_fft1d(), f = read_device_error_256();
-  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : f))));
+            e = read_device_error_fft1d(), f = read_device_error_256(), g = read_device_error_cols();
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : g)))));
 }
 
 int fbfft_b200_set_contraction_mode(int mode) {

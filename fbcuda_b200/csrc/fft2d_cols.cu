@@ -1,0 +1,135 @@
+// Second call of the reference's two-call forward protocol for N = 64 and 128
+// (fbfft/FBFFT2D-inl.cuh:627-669): buffer[b][y][kx] (kx in 0..N/2) -> dst[b][kx][ky], a complex
+// transform along y written transposed, on contiguous tensors.
+//
+// One block owns one image.  The image (N x (N/2+1) complex values, contiguous) arrives by one
+// cp.async.bulk (completion on an mbarrier, bounded wait).  Column kx < N/2 belongs to Q = N/64
+// neighbouring lanes, which read it from shared memory (lanes run over kx: no bank conflicts) and
+// transform it in registers (coop_fft.cuh); the last column kx = N/2 has no lanes of its own, so it
+// is set aside and transformed in a second round by the lanes of column 0.  The results overwrite the
+// image as a [N/2+1][N] tile whose rows leave through bulk stores.
+#include "coop_fft.cuh"
+#include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
+#include "kernels.h"
+
+namespace fbfft_b200 {
+
+namespace {
+
+enum : int { kErrColsFwdWait = 108 };
+
+template <int N>
+struct ColsCfg {
+  static constexpr int R = 64, Q = N / 64, H = N / 2, HC = N / 2 + 1, T = H * Q, PO = N + 2;
+  static constexpr int REGION = HC * PO;                  // complex values: tile [HC][PO] >= image [N][HC]
+  static constexpr int SMEM = (REGION + N) * 8 + 16;      // + the set-aside column + the mbarrier
+  static constexpr int BLOCKS = N == 64 ? 12 : 3;
+};
+
+template <int N>
+__global__ void __launch_bounds__(ColsCfg<N>::T, ColsCfg<N>::BLOCKS) cols_fwd_kernel(const float* __restrict__ buf,
+                                                                                    float* __restrict__ dst, int B) {
+  using C = ColsCfg<N>;
+  constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, H = C::H, HC = C::HC, T = C::T, PO = C::PO;
+  extern __shared__ __align__(16) float2 sm[];
+  float2* img = sm;            // [N][HC]
+  float2* tile = sm;           // [HC][PO]
+  float2* last = sm + C::REGION;  // column N/2: [N]
+  const unsigned bar = smem_u32(sm + C::REGION + N);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP, kx = warp * LP + (lane % LP);
+  float2 lf[Q];
+  lane_factors<Q, false>(q, lf);
+  constexpr unsigned kImageBytes = N * HC * 8;
+  auto fetch = [&](int b) {
+    if (threadIdx.x == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, kImageBytes);
+      bulk_g2s(smem_u32(img), buf + (long long)b * (2 * N * HC), kImageBytes, bar);
+    }
+  };
+  if (threadIdx.x == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  __syncthreads();
+  unsigned phase = 0;
+  if (blockIdx.x < B) fetch(blockIdx.x);
+  for (int b = blockIdx.x; b < B; b += gridDim.x) {
+    if (!mbar_wait(bar, phase, kErrColsFwdWait)) return;
+    phase ^= 1;
+    float2 a[R];
+#pragma unroll
+    for (int m = 0; m < Q; ++m) {
+#pragma unroll
+      for (int jl = 0; jl < P; ++jl) a[m * P + jl] = img[(jl + P * q + R * m) * HC + kx];
+    }
+    for (int y = threadIdx.x; y < N; y += T) last[y] = img[y * HC + H];
+    __syncthreads();  // the image is in registers (and its last column set aside): the tile may overwrite it
+    coop_fft<N, R, Q, false>(a, q, lf);
+    static_for<R>([&](auto kc) {
+      constexpr int k = decltype(kc)::value;
+      tile[kx * PO + Q * k + q] = a[brev(k, R)];
+    });
+    if (warp == 0) {
+      // second round: column N/2 by the lanes of column 0 (the warp's other lanes only take part in
+      // the exchange)
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) a[m * P + jl] = last[jl + P * q + R * m];
+      }
+      coop_fft<N, R, Q, false>(a, q, lf);
+      if (kx == 0) {
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          tile[H * PO + Q * k + q] = a[brev(k, R)];
+        });
+      }
+    }
+    fence_async_smem();
+    __syncthreads();
+    float* out = dst + (long long)b * (2 * N * HC);
+    for (int r = threadIdx.x; r < HC; r += T) bulk_s2g(out + (long long)r * (2 * N), smem_u32(tile + r * PO), N * 8);
+    bulk_commit();
+    bulk_wait_read();
+    __syncthreads();
+    if (b + gridDim.x < B) fetch(b + gridDim.x);
+  }
+}
+
+template <int N>
+int launch_cols(const float* buf, float* dst, int B, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(cols_fwd_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, ColsCfg<N>::SMEM);
+    configured[dev] = true;
+  }
+  const int cap = sm_count() * ColsCfg<N>::BLOCKS;
+  cols_fwd_kernel<N><<<B < cap ? B : cap, ColsCfg<N>::T, ColsCfg<N>::SMEM, s>>>(buf, dst, B);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
+}  // namespace
+
+// contiguous [B][N][N/2+1][2] buffer and [B][N/2+1][N][2] destination, 16-byte aligned
+bool fft2d_cols_fast_supported(int n, const CplxView& buffer, const CplxView& dst, int B) {
+  if (n != 64 && n != 128) return false;
+  if (buffer.blk_planes || dst.blk_planes || buffer.sz != 1 || dst.sz != 1) return false;
+  const long long image = (long long)n * (n + 2);
+  return buffer.sc == 2 && buffer.sr == n + 2 && dst.sc == 2 && dst.sr == 2 * n &&
+         (B <= 1 || (buffer.sb == image && dst.sb == image)) && aligned16(buffer.p) && aligned16(dst.p);
+}
+
+int fft2d_cols_fast(int n, const CplxView& buffer, const CplxView& dst, int B, cudaStream_t s) {
+  if (n == 64) return launch_cols<64>(buffer.p, dst.p, B, s);
+  return launch_cols<128>(buffer.p, dst.p, B, s);
+}
+
+int read_device_error_cols() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace fbfft_b200

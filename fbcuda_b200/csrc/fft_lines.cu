@@ -375,6 +375,7 @@ int fft2d_large_cols_forward(int n, const CplxView& buffer, const CplxView& dst,
     set_last_error("complex tensors must interleave re/im");
     return kUnsupportedDimension;
   }
+  if (fft2d_cols_fast_supported(n, buffer, dst, B)) return fft2d_cols_fast(n, buffer, dst, B, s);
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;
     if constexpr (N >= 64) {

@@ -52,6 +52,23 @@ def test_two_call_forward_full_contiguous_images(n):
     assert fb.device_status() == 0
 
 
+@pytest.mark.parametrize("n,b", [(64, 4000), (128, 1000), (256, 40)])
+def test_column_pass_on_arbitrary_complex_buffers(n, b):
+    """The second call alone, on a buffer that is not the row pass of a real image (every column is
+    a general complex signal), with more images than resident blocks."""
+    rng = np.random.default_rng(n)
+    buf = rng.uniform(-1, 1, (b, n, n // 2 + 1, 2)).astype(np.float32)
+    spec = torch.zeros((b, n // 2 + 1, n, 2), device="cuda")
+    assert fb.fbfft2D_c2c(dev(buf), spec) == fb.ErrorCode.Success
+    z = buf[..., 0].astype(np.float64) + 1j * buf[..., 1]
+    want = np.fft.fft(z, axis=1).transpose(0, 2, 1)          # [b][ky][kx] -> [b][kx][ky]
+    got = host(spec).astype(np.float64)
+    got = got[..., 0] + 1j * got[..., 1]
+    per = np.linalg.norm((got - want).reshape(b, -1), axis=1) / np.linalg.norm(want.reshape(b, -1), axis=1)
+    assert per.max() < FFT_TOL, int(per.argmax())
+    assert fb.device_status() == 0
+
+
 def test_two_call_errors():
     with pytest.raises(fb.FbfftError):
         # src and dst must differ
