@@ -350,7 +350,7 @@ def run_fft2d(args, world, rank, local):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {how}", "frac_of_8TBs": achieved / 8000.0,
                 "traffic": traffic * b if traffic else None, "algorithmic_bytes_per_launch": b * per_image,
-                "kernel": "fft2d_small_fwd_kernel" if n <= 32 else ("fft2d_coop_fwd_kernel" if n <= 128 else "rows_fwd_kernel + lines_c2c_kernel"),
+                "kernel": "fft2d_small_fwd_kernel" if n <= 32 else ("fft2d_coop_fwd_kernel" if n <= 128 else "fft256_rows_kernel + fft256_cols_kernel"),
                 "traffic_source": "ncu capture on the profile case (profiles/), scaled by images per launch" if traffic else None}
     extra = {}
     if args.extras and rank == 0 and world == 1:
