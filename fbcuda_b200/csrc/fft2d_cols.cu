@@ -110,6 +110,101 @@ int launch_cols(const float* buf, float* dst, int B, cudaStream_t s) {
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
+// ---- second call of the inverse protocol (fbfft/FBIFFT2D-inl.cuh:529-742): buffer[p][kx][y] complex,
+// p < G = ceil(B/2) -> unnormalised inverse along kx; the real part is image p, the imaginary part
+// image p + G (when it exists); contiguous N x N outputs.  A block takes 64 consecutive y of one p:
+// N bulk copies of 512 bytes (one per kx) into shared memory, lanes run over y, transform in
+// registers, the two real tiles overwrite the input at a pitch of N + 4 floats and leave by one
+// bulk store per image row.
+template <int N>
+struct ColsInvCfg {
+  static constexpr int R = 64, Q = N / 64, YB = 64, T = YB * Q, PT = N + 4;
+  static constexpr int TILE = YB * PT;                               // floats per real tile
+  static constexpr int REGION = 2 * TILE > 2 * N * YB ? 2 * TILE : 2 * N * YB;  // floats
+  static constexpr int SMEM = REGION * 4 + 16;
+  static constexpr int BLOCKS = N == 64 ? 6 : 3;
+};
+
+template <int N>
+__global__ void __launch_bounds__(ColsInvCfg<N>::T, ColsInvCfg<N>::BLOCKS) cols_inv_kernel(const float* __restrict__ buf,
+                                                                                          float* __restrict__ out,
+                                                                                          int B, int G) {
+  using C = ColsInvCfg<N>;
+  constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, YB = C::YB, T = C::T, PT = C::PT;
+  extern __shared__ __align__(16) float smf[];
+  const float2* in = reinterpret_cast<const float2*>(smf);  // [N][YB]
+  float* tile_a = smf;                                      // [YB][PT]
+  float* tile_b = smf + C::TILE;
+  const unsigned bar = smem_u32(smf + C::REGION);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP, yi = warp * LP + (lane % LP);
+  float2 lf[Q];
+  lane_factors<Q, true>(q, lf);
+  constexpr int YBLOCKS = N / YB;
+  const long long work_total = (long long)G * YBLOCKS;
+  static_assert(T >= N || T * 2 >= N, "row copies are spread over the block's threads");
+  auto fetch = [&](long long work) {
+    const long long p = work / YBLOCKS;
+    const int y0 = (int)(work % YBLOCKS) * YB;
+    if (threadIdx.x == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, N * YB * 8);
+    }
+    __syncthreads();
+    for (int kx = threadIdx.x; kx < N; kx += T)
+      bulk_g2s(smem_u32(smf + kx * YB * 2), buf + (p * N + kx) * (2LL * N) + 2 * y0, YB * 8, bar);
+  };
+  if (threadIdx.x == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  __syncthreads();
+  unsigned phase = 0;
+  if (blockIdx.x < work_total) fetch(blockIdx.x);
+  for (long long work = blockIdx.x; work < work_total; work += gridDim.x) {
+    const long long p = work / YBLOCKS;
+    const int y0 = (int)(work % YBLOCKS) * YB;
+    if (!mbar_wait(bar, phase, kErrColsFwdWait)) return;
+    phase ^= 1;
+    float2 a[R];
+#pragma unroll
+    for (int m = 0; m < Q; ++m) {
+#pragma unroll
+      for (int jl = 0; jl < P; ++jl) a[m * P + jl] = in[(jl + P * q + R * m) * YB + yi];
+    }
+    __syncthreads();  // the input is in registers: the tiles may overwrite it
+    coop_fft<N, R, Q, true>(a, q, lf);
+    static_for<R>([&](auto kc) {
+      constexpr int k = decltype(kc)::value;
+      tile_a[yi * PT + Q * k + q] = a[brev(k, R)].x;
+      tile_b[yi * PT + Q * k + q] = a[brev(k, R)].y;
+    });
+    fence_async_smem();
+    __syncthreads();
+    const bool two = p + G < B;
+    for (int r = threadIdx.x; r < YB; r += T) {
+      bulk_s2g(out + (p * N + y0 + r) * (long long)N, smem_u32(tile_a + r * PT), N * 4);
+      if (two) bulk_s2g(out + ((p + G) * N + y0 + r) * (long long)N, smem_u32(tile_b + r * PT), N * 4);
+    }
+    bulk_commit();
+    bulk_wait_read();
+    if (work + gridDim.x < work_total) fetch(work + gridDim.x);
+  }
+}
+
+template <int N>
+int launch_cols_inv(const float* buf, float* out, int B, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(cols_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, ColsInvCfg<N>::SMEM);
+    configured[dev] = true;
+  }
+  const int G = (B + 1) / 2;
+  const long long work = (long long)G * (N / ColsInvCfg<N>::YB), cap = (long long)sm_count() * ColsInvCfg<N>::BLOCKS;
+  cols_inv_kernel<N><<<(int)(work < cap ? work : cap), ColsInvCfg<N>::T, ColsInvCfg<N>::SMEM, s>>>(buf, out, B, G);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
 }  // namespace
 
 // contiguous [B][N][N/2+1][2] buffer and [B][N/2+1][N][2] destination, 16-byte aligned
@@ -124,6 +219,19 @@ bool fft2d_cols_fast_supported(int n, const CplxView& buffer, const CplxView& ds
 int fft2d_cols_fast(int n, const CplxView& buffer, const CplxView& dst, int B, cudaStream_t s) {
   if (n == 64) return launch_cols<64>(buffer.p, dst.p, B, s);
   return launch_cols<128>(buffer.p, dst.p, B, s);
+}
+
+// contiguous [G][N][N][2] buffer and contiguous [B][N][N] images, 16-byte aligned, no crop
+bool fft2d_cols_inv_fast_supported(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU) {
+  if (n != 64 && n != 128) return false;
+  if (buffer.blk_planes || buffer.sz != 1 || padL != 0 || padU != 0) return false;
+  return buffer.sc == 2 && buffer.sr == 2 * n && (B <= 2 || buffer.sb == 2LL * n * n) && out.h == n && out.w == n &&
+         out.sx == 1 && out.sy == n && (B <= 1 || out.sb == (long long)n * n) && aligned16(buffer.p) && aligned16(out.p);
+}
+
+int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, cudaStream_t s) {
+  if (n == 64) return launch_cols_inv<64>(buffer.p, out.p, B, s);
+  return launch_cols_inv<128>(buffer.p, out.p, B, s);
 }
 
 int read_device_error_cols() {

@@ -69,6 +69,24 @@ def test_column_pass_on_arbitrary_complex_buffers(n, b):
     assert fb.device_status() == 0
 
 
+@pytest.mark.parametrize("n,b", [(64, 1), (64, 2), (64, 5), (64, 2001), (128, 3), (128, 1001)])
+def test_two_call_inverse_full_contiguous_images(n, b):
+    """Inverse protocol with uncropped contiguous outputs (the second call runs block-per-pair);
+    odd B leaves the last pair with one image; more pairs than resident blocks."""
+    rng = np.random.default_rng(n + b)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    spec = torch.empty((b, n // 2 + 1, n, 2), device="cuda")
+    assert fb.fft2d_r2c(n, dev(x), spec) == fb.ErrorCode.Success
+    mid = torch.zeros((b, n, n, 2), device="cuda")   # only the first ceil(B/2) slices are used
+    assert fb.fbifft2D_c2c(spec, mid) == fb.ErrorCode.Success
+    back = torch.full((b, n, n), 7.0, device="cuda")
+    assert fb.fbifft2D(mid, back) == fb.ErrorCode.Success
+    got = host(back).astype(np.float64) / (n * n)
+    per = np.linalg.norm((got - x).reshape(b, -1), axis=1) / np.linalg.norm(x.reshape(b, -1), axis=1)
+    assert per.max() < FFT_TOL, int(per.argmax())
+    assert fb.device_status() == 0
+
+
 def test_two_call_errors():
     with pytest.raises(fb.FbfftError):
         # src and dst must differ
