@@ -205,6 +205,123 @@ int launch_cols_inv(const float* buf, float* out, int B, cudaStream_t s) {
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
+// ---- first call of the inverse protocol (fbfft/FBIFFT2D-inl.cuh:252-521): spectra src[b][kx][ky],
+// kx in 0..N/2 -> buffer[p][r][y], r in 0..N-1, p < G = ceil(B/2): the unnormalised inverse along ky of
+//   A[r] + i B[r]                               for r <= N/2   (A, B = spectra of images p and p + G)
+//   conj A[N-r][-ky] + i conj B[N-r][-ky]       for r >  N/2   (Hermitian half), which equals
+//   conj(inverse of (A[N-r] - i B[N-r])).
+// A block takes 32 stored rows kx of one pair (and row N/2 with the first 32): bulk copies of the
+// rows of both spectra into shared memory at a pitch of N + 2 complex values, 64 lines -- side 0:
+// r = kx, side 1: r = N - kx (r = N/2 in place of kx = 0) -- each transformed in registers by Q lanes,
+// parked as a [64][N + 2] tile over the input and stored row by row with bulk copies.
+template <int N>
+struct RowsInvCfg {
+  static constexpr int R = 64, Q = N / 64, KB = 32, T = 2 * KB * Q, PT = N + 2;   // PT: complex values
+  static constexpr int IN = 2 * (KB + 1) * PT, OUT = 2 * KB * PT;
+  static constexpr int REGION = IN > OUT ? IN : OUT;                               // complex values
+  static constexpr int SMEM = REGION * 8 + 16;
+  static constexpr int BLOCKS = N == 64 ? 6 : 3;
+};
+
+template <int N>
+__global__ void __launch_bounds__(RowsInvCfg<N>::T, RowsInvCfg<N>::BLOCKS) rows_inv_kernel(const float* __restrict__ src,
+                                                                                          float* __restrict__ buf,
+                                                                                          int B, int G) {
+  using C = RowsInvCfg<N>;
+  constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, KB = C::KB, T = C::T, PT = C::PT, HC = N / 2 + 1;
+  extern __shared__ __align__(16) float2 smr[];
+  const float2* sa = smr;                     // rows of A: [KB + 1][PT]
+  const float2* sb = smr + (KB + 1) * PT;     // rows of B
+  float2* tile = smr;                         // [2 KB][PT]
+  const unsigned bar = smem_u32(smr + C::REGION);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q = lane / LP, li = warp * LP + (lane % LP);  // line 0..63
+  const int side = li / KB, kl = li % KB;
+  float2 lf[Q];
+  lane_factors<Q, true>(q, lf);
+  constexpr int KBLOCKS = (N / 2) / KB;
+  const long long work_total = (long long)G * KBLOCKS;
+  auto fetch = [&](long long work) {
+    const long long p = work / KBLOCKS;
+    const int kb = (int)(work % KBLOCKS);
+    const bool two = p + G < B;
+    const int rows = KB + (kb == 0 ? 1 : 0);
+    if (threadIdx.x == 0) {
+      fence_async_smem();
+      mbar_expect_tx(bar, (two ? 2 : 1) * rows * N * 8);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * rows; i += T) {
+      const int which = i / rows, slot = i % rows;
+      if (which == 1 && !two) continue;
+      const int kx = slot < KB ? kb * KB + slot : N / 2;
+      const long long img = which ? p + G : p;
+      bulk_g2s(smem_u32(smr + (which * (KB + 1) + slot) * PT), src + (img * HC + kx) * (2LL * N), N * 8, bar);
+    }
+  };
+  if (threadIdx.x == 0) mbar_init(bar, 1);
+  fence_async_smem();
+  __syncthreads();
+  unsigned phase = 0;
+  if (blockIdx.x < work_total) fetch(blockIdx.x);
+  for (long long work = blockIdx.x; work < work_total; work += gridDim.x) {
+    const long long p = work / KBLOCKS;
+    const int kb = (int)(work % KBLOCKS);
+    const bool two = p + G < B;
+    if (!mbar_wait(bar, phase, kErrColsFwdWait)) return;
+    phase ^= 1;
+    const int kx = kb * KB + kl;
+    // stored row 0 has no mirror: its side-1 line transforms r = N/2 instead
+    const bool nyq = side == 1 && kx == 0;
+    const int slot = nyq ? KB : kl;
+    const float sign = (side == 1 && !nyq) ? -1.f : 1.f;
+    const int r = side == 0 ? kx : (nyq ? N / 2 : N - kx);
+    float2 a[R];
+    const float2* ra = sa + slot * PT;
+    const float2* rb = sb + slot * PT;
+#pragma unroll
+    for (int m = 0; m < Q; ++m) {
+#pragma unroll
+      for (int jl = 0; jl < P; ++jl) {
+        const int c = jl + P * q + R * m;
+        const float2 A = ra[c];
+        const float2 Bv = two ? rb[c] : make_float2(0.f, 0.f);
+        a[m * P + jl] = make_float2(A.x - sign * Bv.y, A.y + sign * Bv.x);
+      }
+    }
+    __syncthreads();  // the rows are in registers: the tile may overwrite them
+    coop_fft<N, R, Q, true>(a, q, lf);
+    static_for<R>([&](auto kc) {
+      constexpr int k = decltype(kc)::value;
+      const float2 z = a[brev(k, R)];
+      tile[li * PT + Q * k + q] = make_float2(z.x, sign * z.y);
+    });
+    fence_async_smem();
+    __syncthreads();
+    if (q == 0) {
+      bulk_s2g(buf + (p * N + r) * (2LL * N), smem_u32(tile + li * PT), N * 8);
+      bulk_commit();
+    }
+    bulk_wait_read();
+    if (work + gridDim.x < work_total) fetch(work + gridDim.x);
+  }
+}
+
+template <int N>
+int launch_rows_inv(const float* src, float* buf, int B, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(rows_inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, RowsInvCfg<N>::SMEM);
+    configured[dev] = true;
+  }
+  const int G = (B + 1) / 2;
+  const long long work = (long long)G * ((N / 2) / RowsInvCfg<N>::KB), cap = (long long)sm_count() * RowsInvCfg<N>::BLOCKS;
+  rows_inv_kernel<N><<<(int)(work < cap ? work : cap), RowsInvCfg<N>::T, RowsInvCfg<N>::SMEM, s>>>(src, buf, B, G);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
 }  // namespace
 
 // contiguous [B][N][N/2+1][2] buffer and [B][N/2+1][N][2] destination, 16-byte aligned
@@ -232,6 +349,19 @@ bool fft2d_cols_inv_fast_supported(int n, const CplxView& buffer, const RealView
 int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, cudaStream_t s) {
   if (n == 64) return launch_cols_inv<64>(buffer.p, out.p, B, s);
   return launch_cols_inv<128>(buffer.p, out.p, B, s);
+}
+
+// contiguous [B][N/2+1][N][2] spectra and contiguous [.][N][N][2] buffer, 16-byte aligned
+bool fft2d_rows_inv_fast_supported(int n, const CplxView& src, const CplxView& buffer, int B) {
+  if (n != 64 && n != 128) return false;
+  if (src.blk_planes || buffer.blk_planes || src.sz != 1 || buffer.sz != 1) return false;
+  return src.sc == 2 && src.sr == 2 * n && (B <= 1 || src.sb == (long long)(n + 2) * n) && buffer.sc == 2 &&
+         buffer.sr == 2 * n && (B <= 2 || buffer.sb == 2LL * n * n) && aligned16(src.p) && aligned16(buffer.p);
+}
+
+int fft2d_rows_inv_fast(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s) {
+  if (n == 64) return launch_rows_inv<64>(src.p, buffer.p, B, s);
+  return launch_rows_inv<128>(src.p, buffer.p, B, s);
 }
 
 int read_device_error_cols() {

@@ -416,6 +416,7 @@ int fft_lines_inplace(int n, const CplxView& t, int B, int lines, bool inverse, 
 
 int fft2d_large_rows_inverse(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s) {
   if (n < 64) return kUnsupportedSize;
+  if (fft2d_rows_inv_fast_supported(n, src, buffer, B)) return fft2d_rows_inv_fast(n, src, buffer, B, s);
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;
     if constexpr (N >= 64) {
