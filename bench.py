@@ -415,7 +415,28 @@ def run_extras(args, x, spec, n0, hw0):
                            "inv_us": ms_i * 1e3, "inv_gbs": byts / ms_i / 1e6, "inv_frac_of_measured": byts / ms_i / 1e6 / peak}
         del x, spec, back
         torch.cuda.empty_cache()
-    return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d}
+    # the reference's two-call protocol for N >= 64 on 512 MiB of contiguous N x N images
+    two_call = {}
+    for n in (64, 128):
+        b = GIB // 2 // (4 * n * n)
+        x = torch.rand((b, n, n), device="cuda") * 2 - 1
+        buf = torch.empty((b, n, n // 2 + 1, 2), device="cuda")
+        spec = torch.empty((b, n // 2 + 1, n, 2), device="cuda")
+        mid = torch.empty((b, n, n, 2), device="cuda")
+        back = torch.empty_like(x)
+        r, c, m = 4 * n * n * b, 8 * n * (n // 2 + 1) * b, 8 * n * n * ((b + 1) // 2)
+        entry = {}
+        for name, fn, byts in (("fbfft2D_real_to_buffer", lambda: fb.fbfft2D(x, buf), r + c),
+                               ("fbfft2D_buffer_to_spectrum", lambda: fb.fbfft2D_c2c(buf, spec), 2 * c),
+                               ("fbifft2D_spectrum_to_buffer", lambda: fb.fbifft2D_c2c(spec, mid), c + m),
+                               ("fbifft2D_buffer_to_real", lambda: fb.fbifft2D(mid, back), m + r)):
+            ms = time_steps(fn, 10, 3, 1)
+            entry[name] = {"us": ms * 1e3, "gbs": byts / ms / 1e6, "frac_of_measured": byts / ms / 1e6 / peak}
+        two_call[str(n)] = entry
+        del x, buf, spec, mid, back
+        torch.cuda.empty_cache()
+    return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d,
+            "two_call_protocol_512MiB": two_call}
 
 
 def run_conv(args, world, rank, local):
