@@ -1,7 +1,7 @@
 """GPU parity of the per-bin contraction (transposeMM) and of the three
 convolution passes against float64 (direct convolution for small shapes, the
 float64 FFT convolution -- itself checked against the direct form on CPU -- for
-the BASELINE shapes)."""
+the benchmark configurations' shapes)."""
 import numpy as np
 import pytest
 import torch
