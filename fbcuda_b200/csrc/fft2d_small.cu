@@ -36,8 +36,10 @@ enum : int { kErrFwdWait = 101, kErrInvWait = 102 };
 // IN_BULK : real input is contiguous [B][h][w] with a 16-byte aligned base
 // OUT_BULK: complex output is contiguous [B][N/2+1][N][2] with a 16-byte aligned base
 // FULL    : (with IN_BULK) the images are N x N without padding: compile-time offsets, no predicates
-template <int N, bool IN_BULK, bool OUT_BULK, bool FULL = false>
-__global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
+// SINGLE  : (with IN_BULK and OUT_BULK) the staging slot aliases the warp's work buffer: the next task
+//           is fetched only after the current rows have left, but 4 blocks fit an SM instead of 3
+template <int N, bool IN_BULK, bool OUT_BULK, bool FULL = false, bool SINGLE = false>
+__global__ void __launch_bounds__(kSmallThreads, SINGLE ? 4 : 3) fft2d_small_fwd_kernel(RealView in, CplxView out, int B, int padL,
                                                                           int padU, int ntasks, int slot_floats, int slot_pitch) {
   constexpr int T = N / 2, IPW = 32 / T, ROWS = T + 1;
   constexpr int RS = SmallCfg<N>::RS, IS = SmallCfg<N>::IS;
@@ -47,9 +49,10 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
   const int li = lane / T, l = lane % T;
   float2* ib = buf + li * IS;
   // staging slots (IN_BULK) follow the work buffers; mbarriers follow the slots
-  float* slot = reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) + warp * slot_floats;
+  float* slot = SINGLE ? reinterpret_cast<float*>(buf)
+                       : reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) + warp * slot_floats;
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(reinterpret_cast<float*>(smem + kWarps * (IPW * IS)) +
-                                                                   kWarps * slot_floats);
+                                                                   (SINGLE ? 0 : kWarps * slot_floats));
   const unsigned bar = smem_u32(bars + warp);
   __shared__ float zero_storage;
   if (threadIdx.x == 0) zero_storage = 0.f;
@@ -125,13 +128,14 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
       } else {
         load_columns<N>(in.p + (long long)(valid ? b : 0) * in.sb, in.sy, in.sx, in.h, in.w, padL, padU, valid, l, a);
       }
-      if (IN_BULK) {
+      if (IN_BULK && !SINGLE) {
         // everything of this task is in registers: fetch the next task into the slot
         __syncwarp();
         const int next = task + stride;
         staged = false;
         if (next < ntasks) staged = issue(next);
       }
+      if (SINGLE) __syncwarp();  // every lane has read the slot that the work buffer overwrites
       fft_bitrev<N, false>(a);
       if (OUT_BULK) {
         // rows of the previous task may still be leaving the work buffer
@@ -173,6 +177,14 @@ __global__ void __launch_bounds__(kSmallThreads, 3) fft2d_small_fwd_kernel(RealV
         }
       }
       bulk_commit();
+      if constexpr (SINGLE) {
+        // the rows have left the work buffer: the next task may land in it
+        bulk_wait_read();
+        __syncwarp();
+        const int next = task + stride;
+        staged = false;
+        if (next < ntasks) staged = issue(next);
+      }
     } else {
       constexpr int PER = ROWS * N;
       for (int e = lane; e < IPW * PER; e += 32) {
@@ -336,7 +348,13 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
     const int smem = base + kWarps * slot_floats * 4 + kWarps * 8;
     const int grid = grid_for(ntasks, 3);
     // (measured: the predicate-free variant gains at N = 16 and loses a little at N = 8 and 32)
-    if (N == 16 && out_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
+    // (measured on full images: the single-buffer variant gains at N = 32, 0.85 -> 0.99 of the copy
+    // bandwidth with 16 instead of 12 resident warps, and loses at N = 8 and 16)
+    if (N == 32 && out_bulk && !out.blk_planes && hw % 4 == 0) {
+      const int smem1 = base + kWarps * 8;
+      allow_smem(fft2d_small_fwd_kernel<N, true, true, false, true>, smem1);
+      fft2d_small_fwd_kernel<N, true, true, false, true><<<grid_for(ntasks, 4), kSmallThreads, smem1, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
+    } else if (N == 16 && out_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
       allow_smem(fft2d_small_fwd_kernel<N, true, true, true>, smem);
       fft2d_small_fwd_kernel<N, true, true, true><<<grid, kSmallThreads, smem, s>>>(in, out, B, padL, padU, ntasks, slot_floats, slot_pitch);
     } else if (out_bulk) {

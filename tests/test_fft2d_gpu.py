@@ -167,3 +167,16 @@ def test_n256_many_images():
     per = np.linalg.norm((got - want).reshape(b, -1), axis=1) / np.linalg.norm(want.reshape(b, -1), axis=1)
     assert per.max() < FFT_TOL, int(per.argmax())
     assert fb.device_status() == 0
+
+
+@pytest.mark.parametrize("case", [(28, 28, 0, 0), (28, 28, 2, 3), (24, 20, 1, 2), (32, 32, 0, 0), (2, 2, 5, 7), (32, 4, 0, 3)])
+@pytest.mark.parametrize("b", [1, 3, 4000])
+def test_n32_images_of_whole_16_byte_units(case, b):
+    """N = 32 images whose size is a multiple of 16 bytes take the single-buffer forward kernel:
+    full, cropped and padded shapes, odd batch, more tasks than resident warps."""
+    h, w, pl, pu = case
+    rng = np.random.default_rng(b + 31 * h + w)
+    x = rng.uniform(-1, 1, (b, h, w)).astype(np.float32)
+    spec = gpu_fft2d(x, 32, pl, pu)
+    assert orc.rel_l2(spec, orc.fbfft2d(x, 32, pl, pu)) < FFT_TOL
+    assert fb.device_status() == 0
