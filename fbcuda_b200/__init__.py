@@ -19,6 +19,12 @@ from .api import (  # noqa: F401
     fft2d_r2c,
     last_error,
     device_status,
+    clear_device_status,
+    selftest_bounded_wait,
+    dp_shard,
+    comm_unique_id,
+    Communicator,
+    conv_acc_grad_parameters_dp,
     set_contraction_mode,
     lib,
     transposeMM,

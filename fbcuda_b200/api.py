@@ -77,7 +77,18 @@ def lib() -> ctypes.CDLL:
         L.fbfft_b200_conv_update_grad_input.argtypes = [ctypes.c_int] + tp + t4 + tp + [_vp, sz, ctypes.c_int, _vp]
         L.fbfft_b200_conv_acc_grad_parameters.argtypes = ([ctypes.c_int] + tp + t4 + tp +
                                                           [ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
-        for name in ("conv_update_output", "conv_update_grad_input", "conv_acc_grad_parameters"):
+        L.fbfft_b200_conv_acc_grad_parameters_dp.argtypes = ([_vp, ctypes.c_int, ctypes.c_int] + tp + t4 + tp +
+                                                             [ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
+        L.fbfft_b200_comm_unique_id.argtypes = [_vp]
+        L.fbfft_b200_comm_init.argtypes = [_vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_vp)]
+        L.fbfft_b200_comm_info.argtypes = [_vp, _ip, _ip]
+        L.fbfft_b200_comm_destroy.argtypes = [_vp]
+        ll = ctypes.c_longlong
+        L.fbfft_b200_dp_shard.argtypes = [ll, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ll), ctypes.POINTER(ll)]
+        L.fbfft_b200_selftest_bounded_wait.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong)]
+        for name in ("conv_update_output", "conv_update_grad_input", "conv_acc_grad_parameters",
+                     "conv_acc_grad_parameters_dp", "comm_unique_id", "comm_init", "comm_info", "comm_destroy",
+                     "dp_shard", "clear_device_status", "selftest_bounded_wait", "device_status"):
             getattr(L, "fbfft_b200_" + name).restype = ctypes.c_int
         for name in ("fbfft1d", "fbifft1d", "fbfft2d", "fbfft2d_c2c", "fbifft2d_c2c", "fbifft2d", "fft2d_r2c",
                      "fft2d_c2r", "transpose_mm", "iterated_convolution"):
@@ -89,6 +100,20 @@ def lib() -> ctypes.CDLL:
 def device_status() -> int:
     """0 when no kernel recorded a device-side error (synchronises)."""
     return int(lib().fbfft_b200_device_status())
+
+
+def clear_device_status() -> None:
+    """Resets the sticky device-side error code of the current device (synchronises)."""
+    _check(lib().fbfft_b200_clear_device_status())
+
+
+def selftest_bounded_wait(max_tries: int = 1024) -> int:
+    """Runs the bounded-wait self-test (a wait on a barrier nothing completes, limited to
+    `max_tries` attempts); returns the nanoseconds the wait took before it gave up.  Afterwards
+    device_status() reports 901 until clear_device_status()."""
+    ns = ctypes.c_ulonglong(0)
+    _check(lib().fbfft_b200_selftest_bounded_wait(int(max_tries), ctypes.byref(ns)))
+    return int(ns.value)
 
 
 def set_contraction_mode(mode: int) -> None:
@@ -284,6 +309,7 @@ REUSE_WEIGHT_SPECTRUM = 4
 STOP_AFTER_CONTRACTION = 8
 START_FROM_SPECTRUM = 16
 ACCUMULATE_RESULT = 32
+STOP_AFTER_TRANSFORMS = 64
 REGION_INPUT, REGION_OUTPUT, REGION_WEIGHT, REGION_RESULT = 0, 1, 2, 3
 
 
@@ -380,3 +406,49 @@ def tiled_conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, works
     owin = (0, 0, 1, 1)
     return conv_acc_grad_parameters(fftSize, _crop(input, win), gradWeight, _crop(gradOutput, owin), workspace, scale,
                                     (0, 0), (0, 0), START_FROM_SPECTRUM, stream)
+
+
+# ---- data-parallel accGradParameters (batch shards on several GPUs, NCCL) ------------------
+DP_FREQUENCY_ALLREDUCE, DP_FREQUENCY_REDUCE_SCATTER, DP_SPATIAL_ALLREDUCE = 0, 1, 2
+UNIQUE_ID_BYTES = 128
+
+
+def dp_shard(total: int, world: int, rank: int):
+    """(lo, count) of the contiguous shard of `total` units that `rank` holds."""
+    lo, count = ctypes.c_longlong(), ctypes.c_longlong()
+    _check(lib().fbfft_b200_dp_shard(int(total), int(world), int(rank), ctypes.byref(lo), ctypes.byref(count)))
+    return lo.value, count.value
+
+
+def comm_unique_id() -> bytes:
+    """The identifier rank 0 creates and hands to the other ranks."""
+    buf = ctypes.create_string_buffer(UNIQUE_ID_BYTES)
+    _check(lib().fbfft_b200_comm_unique_id(buf))
+    return buf.raw
+
+
+class Communicator:
+    """fbfft_b200_comm: one per process and GPU, created with that GPU current.  Initialisation is
+    bounded by timeout_ms (ranks that never join end it with an error instead of a hang)."""
+
+    def __init__(self, unique_id: bytes, rank: int, world: int, timeout_ms: int = 60000):
+        if len(unique_id) != UNIQUE_ID_BYTES:
+            raise ValueError("unique id must be %d bytes" % UNIQUE_ID_BYTES)
+        self._h = _vp()
+        _check(lib().fbfft_b200_comm_init(ctypes.c_char_p(unique_id), int(rank), int(world), int(timeout_ms),
+                                          ctypes.byref(self._h)))
+        self.rank, self.world = int(rank), int(world)
+
+    def destroy(self):
+        if self._h:
+            h, self._h = self._h, _vp()
+            _check(lib().fbfft_b200_comm_destroy(h))
+
+
+def conv_acc_grad_parameters_dp(comm: Communicator, mode: int, fftSize, input, gradWeight, gradOutput, workspace,
+                                scale=1.0, inPad=(0, 0), outPad=(0, 0), flags=0, stream=None):
+    """accGradParameters over batch shards: this rank's contraction, the sum over the ranks in the
+    given mode, the inverse transform; every rank ends with the full gradWeight."""
+    return _check(lib().fbfft_b200_conv_acc_grad_parameters_dp(
+        comm._h, int(mode), fftSize, *_t(input), inPad[0], inPad[1], *_t(gradWeight), *_t(gradOutput), outPad[0],
+        outPad[1], float(scale), *_ws(workspace), flags, _stream(stream)))

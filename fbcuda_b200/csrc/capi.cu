@@ -105,6 +105,19 @@ int fbfft_b200_device_status(void) {
   return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : g)))));
 }
 
+int fbfft_b200_clear_device_status(void) {
+  const int r = clear_device_error() | clear_device_error_coop() | clear_device_error_tc() | clear_device_error_tma() |
+                clear_device_error_fft1d() | clear_device_error_256() | clear_device_error_cols();
+  if (cudaDeviceSynchronize() != cudaSuccess || r != 0) return fail(kCudaError, "clear_device_status: cannot reset the status words");
+  return kSuccess;
+}
+
+int fbfft_b200_selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns) {
+  if (max_tries < 1 || max_tries > (1 << 20)) return fail(kUnsupportedDimension, "selftest_bounded_wait: max_tries must be in 1..2^20");
+  if (selftest_bounded_wait(max_tries, elapsed_ns) != kSuccess) return fail(kCudaError, "selftest_bounded_wait: launch or read-back failed");
+  return kSuccess;
+}
+
 int fbfft_b200_set_contraction_mode(int mode) {
   if (mode < 0 || mode > 2)
     return fail(kUnsupportedDimension, "set_contraction_mode: 0 (tensor cores), 1 (FP32 cores) or 2 (tensor cores, gather kernel)");
@@ -136,6 +149,10 @@ int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const i
   if (B == 0) return kSuccess;
   if (check_ptrs(real, cplx)) return kUnsupportedDimension;
   if (!small_size(n) && !large_size(n)) return fail(kUnsupportedSize, "fft2d_c2r: N must be 8, 16, 32, 64, 128 or 256");
+  if (n == 256)
+    return fail(kUnsupportedSize,
+                "fft2d_c2r: the single-call inverse covers N = 8..128; for N = 256 use the two-call protocol "
+                "(fbifft2d_c2c into a caller-owned [B][N][N][2] buffer, then fbifft2d)");
   if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != n || cplx_size[3] != 2)
     return fail(kUnsupportedDimension, "fft2d_c2r: complex tensor must be [B][N/2+1][N][2]");
   if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fft2d_c2r: negative padding");

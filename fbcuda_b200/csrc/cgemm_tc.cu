@@ -435,10 +435,7 @@ int cgemm_tc(const float* a, long long a_rs, long long a_ks, bool conjA, const f
   return launch_tc<64>(t, s);
 }
 
-int read_device_error_tc() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_tc() { return device_error_word_read(); }
+int clear_device_error_tc() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -581,10 +581,7 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   return launch_tma<64>(md, t, s);
 }
 
-int read_device_error_tma() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_tma() { return device_error_word_read(); }
+int clear_device_error_tma() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -14,6 +14,7 @@
 // the tensor's (padU, padL) offset inside the N x N canvas; weights sit at (0, 0).
 #include "../../include/fbfft_b200.h"
 #include "common.cuh"
+#include "dp_comm.h"
 #include "kernels.h"
 
 namespace fbfft_b200 {
@@ -101,11 +102,13 @@ int inverse(int n, float* spec, const Tensor4& t, int padL, int padU, bool block
 }
 
 // The workspace spectra use the bin-blocked layout whenever the tensor-core contraction will
-// run (its operand rows are then contiguous runs instead of isolated 32-byte sectors).  All
-// three passes of a layer take the same decision (it depends on B*C*O and on the process-wide
-// contraction mode only), so spectra reused across passes agree.
-bool use_blocked(int n, long long B, long long C, long long O) {
-  return n >= 16 && contraction_mode() != 1 && B * C * O >= 16 * 16 * 8;
+// run (its operand rows are then contiguous runs instead of isolated 32-byte sectors).  The
+// decision depends on the transform size, the plane counts and the process-wide contraction mode
+// only -- never on the batch -- so spectra reused across passes agree, and so do the result regions
+// of ranks that hold batch shards of different sizes (an empty shard included) and sum them
+// between STOP_AFTER_CONTRACTION and START_FROM_SPECTRUM.
+bool use_blocked(int n, long long C, long long O) {
+  return n >= 16 && contraction_mode() != 1 && C * O >= 16 * 16;
 }
 
 // D[m][n] (+)= inv_norm * sum_k opA(A[m][k]) opB(B[n][k]) per bin, where element (m, k) of A is
@@ -157,6 +160,15 @@ Tensor4 make_tensor(const float* p, const int* size, const int* stride) {
     t.stride[d] = stride[d];
   }
   return t;
+}
+
+// the transforms reject negative offsets into the canvas; so do the passes
+int check_pads(int in_padL, int in_padU, int out_padL, int out_padU) {
+  if (in_padL < 0 || in_padU < 0 || out_padL < 0 || out_padU < 0) {
+    set_last_error("convolution: negative padding");
+    return kUnsupportedDimension;
+  }
+  return kSuccess;
 }
 
 int check_common(int n, const Tensor4& in, const Tensor4& w, const Tensor4& out, void* ws, size_t ws_bytes) {
@@ -222,10 +234,11 @@ int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_s
                                   int in_padU, const float* weight, const int* w_size, const int* w_stride, float* out,
                                   const int* out_size, const int* out_stride, int out_padL, int out_padU,
                                   void* workspace, size_t workspace_bytes, int flags, void* stream) {
-  if (!in || !weight || !out || !in_size || !w_size || !out_size) {
+  if (!in || !weight || !out || !in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride) {
     set_last_error("null argument");
     return kUnsupportedDimension;
   }
+  if (int prc = check_pads(in_padL, in_padU, out_padL, out_padU)) return prc;
   const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(weight, w_size, w_stride),
                 to = make_tensor(out, out_size, out_stride);
   int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
@@ -235,14 +248,18 @@ int fbfft_b200_conv_update_output(int fft_size, const float* in, const int* in_s
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
-  if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
-    return rc;
-  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
-  // res[b][o] = sum_c conj(w[o][c]) in[b][c] / N^2      (m = o, n = b, k = c)
-  rc = contract(n, blk, ws + r.w_off, C, 1, (long long)O * C, true, ws + r.in_off, C, 1, (long long)B * C, false,
-                ws + r.res_off, 1, O, (long long)B * O, O, B, C, 1.0f / ((float)n * (float)n), s);
-  if (rc) return rc;
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
+  if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
+    if (!(flags & FBFFT_CONV_REUSE_INPUT_SPECTRUM) && (rc = forward(n, ti, in_padL, in_padU, ws + r.in_off, blk, s)))
+      return rc;
+    if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
+    if (flags & FBFFT_CONV_STOP_AFTER_TRANSFORMS) return kSuccess;
+    // res[b][o] = sum_c conj(w[o][c]) in[b][c] / N^2      (m = o, n = b, k = c)
+    rc = contract(n, blk, ws + r.w_off, C, 1, (long long)O * C, true, ws + r.in_off, C, 1, (long long)B * C, false,
+                  ws + r.res_off, 1, O, (long long)B * O, O, B, C, 1.0f / ((float)n * (float)n), s);
+    if (rc) return rc;
+  }
+  if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
   return inverse(n, ws + r.res_off, to, out_padL, out_padU, blk, s);
 }
 
@@ -251,10 +268,11 @@ int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* i
                                       const int* w_stride, const float* grad_out, const int* out_size,
                                       const int* out_stride, int out_padL, int out_padU, void* workspace,
                                       size_t workspace_bytes, int flags, void* stream) {
-  if (!grad_in || !weight || !grad_out || !in_size || !w_size || !out_size) {
+  if (!grad_in || !weight || !grad_out || !in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride) {
     set_last_error("null argument");
     return kUnsupportedDimension;
   }
+  if (int prc = check_pads(in_padL, in_padU, out_padL, out_padU)) return prc;
   const Tensor4 ti = make_tensor(grad_in, in_size, in_stride), tw = make_tensor(weight, w_size, w_stride),
                 to = make_tensor(grad_out, out_size, out_stride);
   int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
@@ -264,14 +282,19 @@ int fbfft_b200_conv_update_grad_input(int fft_size, float* grad_in, const int* i
   const Regions r = regions(n, B, C, O);
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
-  if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) && (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
-    return rc;
-  if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
-  // res[b][c] = sum_o w[o][c] out[b][o] / N^2           (m = c, n = b, k = o)
-  rc = contract(n, blk, ws + r.w_off, 1, C, (long long)O * C, false, ws + r.out_off, O, 1, (long long)B * O, false,
-                ws + r.res_off, 1, C, (long long)B * C, C, B, O, 1.0f / ((float)n * (float)n), s);
-  if (rc) return rc;
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
+  if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
+    if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) &&
+        (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
+      return rc;
+    if (!(flags & FBFFT_CONV_REUSE_WEIGHT_SPECTRUM) && (rc = forward(n, tw, 0, 0, ws + r.w_off, blk, s))) return rc;
+    if (flags & FBFFT_CONV_STOP_AFTER_TRANSFORMS) return kSuccess;
+    // res[b][c] = sum_o w[o][c] out[b][o] / N^2           (m = c, n = b, k = o)
+    rc = contract(n, blk, ws + r.w_off, 1, C, (long long)O * C, false, ws + r.out_off, O, 1, (long long)B * O, false,
+                  ws + r.res_off, 1, C, (long long)B * C, C, B, O, 1.0f / ((float)n * (float)n), s);
+    if (rc) return rc;
+  }
+  if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
   return inverse(n, ws + r.res_off, ti, in_padL, in_padU, blk, s);
 }
 
@@ -280,10 +303,11 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
                                         const int* w_stride, const float* grad_out, const int* out_size,
                                         const int* out_stride, int out_padL, int out_padU, float scale,
                                         void* workspace, size_t workspace_bytes, int flags, void* stream) {
-  if (!in || !grad_weight || !grad_out || !in_size || !w_size || !out_size) {
+  if (!in || !grad_weight || !grad_out || !in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride) {
     set_last_error("null argument");
     return kUnsupportedDimension;
   }
+  if (int prc = check_pads(in_padL, in_padU, out_padL, out_padU)) return prc;
   const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(grad_weight, w_size, w_stride),
                 to = make_tensor(grad_out, out_size, out_stride);
   int rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes);
@@ -293,7 +317,7 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long X = bins_of(n);
-  const bool blk = use_blocked(n, B, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(ws) & 31u) == 0;
   if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
     if (B == 0) {
       if (!(flags & FBFFT_CONV_ACCUMULATE_RESULT) && cudaMemsetAsync(ws + r.res_off, 0, (size_t)O * C * X * 2 * sizeof(float), s) != cudaSuccess) return kCudaError;
@@ -303,6 +327,7 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
       if (!(flags & FBFFT_CONV_REUSE_OUTPUT_SPECTRUM) &&
           (rc = forward(n, to, out_padL, out_padU, ws + r.out_off, blk, s)))
         return rc;
+      if (flags & FBFFT_CONV_STOP_AFTER_TRANSFORMS) return kSuccess;
       // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]      (m = o, n = c, k = b)
       rc = contract(n, blk, ws + r.out_off, 1, O, (long long)B * O, true, ws + r.in_off, 1, C, (long long)B * C, false,
                     ws + r.res_off, C, 1, (long long)O * C, O, C, B, scale / ((float)n * (float)n), s,
@@ -312,6 +337,96 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
   }
   if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
   return inverse(n, ws + r.res_off, tw, 0, 0, blk, s);
+}
+
+// accGradParameters over batch shards on several GPUs: every rank contracts its own shard, the
+// weight gradient is summed over the communicator, every rank ends with the full gradient.
+int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int fft_size, const float* in,
+                                           const int* in_size, const int* in_stride, int in_padL, int in_padU,
+                                           float* grad_weight, const int* w_size, const int* w_stride,
+                                           const float* grad_out, const int* out_size, const int* out_stride,
+                                           int out_padL, int out_padU, float scale, void* workspace,
+                                           size_t workspace_bytes, int flags, void* stream) {
+  if (!comm) {
+    set_last_error("conv_acc_grad_parameters_dp: null communicator");
+    return kUnsupportedDimension;
+  }
+  if (mode < FBFFT_DP_FREQUENCY_ALLREDUCE || mode > FBFFT_DP_SPATIAL_ALLREDUCE) {
+    set_last_error("conv_acc_grad_parameters_dp: unknown reduction mode");
+    return kUnsupportedDimension;
+  }
+  if (flags & FBFFT_CONV_ACCUMULATE_RESULT) {
+    set_last_error("conv_acc_grad_parameters_dp: ACCUMULATE_RESULT cannot be combined with the cross-GPU sum");
+    return kUnsupportedDimension;
+  }
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  const int world = comm_world(c), rank = comm_rank(c);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // this rank's contraction (argument checks included); an empty shard zeroes the result region
+  int rc = kSuccess;
+  if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
+    const int stop = mode == FBFFT_DP_SPATIAL_ALLREDUCE ? 0 : FBFFT_CONV_STOP_AFTER_CONTRACTION;
+    rc = fbfft_b200_conv_acc_grad_parameters(fft_size, in, in_size, in_stride, in_padL, in_padU, grad_weight, w_size,
+                                             w_stride, grad_out, out_size, out_stride, out_padL, out_padU, scale,
+                                             workspace, workspace_bytes, (flags & ~FBFFT_CONV_STOP_AFTER_CONTRACTION) | stop,
+                                             stream);
+    if (rc) return rc;
+    if (flags & (FBFFT_CONV_STOP_AFTER_CONTRACTION | FBFFT_CONV_STOP_AFTER_TRANSFORMS)) return kSuccess;
+  } else {
+    if (!in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride || !grad_weight) {
+      set_last_error("null argument");
+      return kUnsupportedDimension;
+    }
+    const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(grad_weight, w_size, w_stride),
+                  to = make_tensor(grad_out, out_size, out_stride);
+    if ((rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes))) return rc;
+    if (mode == FBFFT_DP_SPATIAL_ALLREDUCE) {
+      rc = fbfft_b200_conv_acc_grad_parameters(fft_size, in, in_size, in_stride, in_padL, in_padU, grad_weight, w_size,
+                                               w_stride, grad_out, out_size, out_stride, out_padL, out_padU, scale,
+                                               workspace, workspace_bytes, FBFFT_CONV_START_FROM_SPECTRUM, stream);
+      if (rc) return rc;
+    }
+  }
+  const int n = fft_size, B = in_size[0], C = in_size[1], O = out_size[1];
+  const long long planes = (long long)O * C, X = bins_of(n);
+  const Tensor4 tw = make_tensor(grad_weight, w_size, w_stride);
+  const bool gw_dense = tw.stride[3] == 1 && tw.stride[2] == tw.size[3] && tw.stride[1] == tw.size[2] * tw.size[3] &&
+                        tw.stride[0] == tw.size[1] * tw.stride[1];
+  const size_t gw_count = (size_t)planes * tw.size[2] * tw.size[3];
+  if (mode == FBFFT_DP_SPATIAL_ALLREDUCE) {
+    if (!gw_dense) {
+      set_last_error("conv_acc_grad_parameters_dp: the spatial all-reduce needs a contiguous grad_weight");
+      return kUnsupportedDimension;
+    }
+    return world > 1 ? comm_all_reduce(c, grad_weight, gw_count, s) : kSuccess;
+  }
+  const Regions r = regions(n, B, C, O);
+  float* res = static_cast<float*>(workspace) + r.res_off;
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0;
+  if (world == 1) return inverse(n, res, tw, 0, 0, blk, s);
+  if (mode == FBFFT_DP_FREQUENCY_REDUCE_SCATTER && planes % world == 0 && gw_dense) {
+    // Every rank receives the sum of 1/world of the planes, inverse-transforms and crops only those,
+    // and the spatial gradients are gathered.  In the row-blocked layout a plane's bins are spread
+    // over N/2+1 row blocks of [planes][N] complex values: one reduce-scatter per row block, as a group.
+    const long long mine = planes / world, lo = mine * rank;
+    if (blk) {
+      rc = comm_reduce_scatter_rows(c, res, n / 2 + 1, (size_t)planes * n * 2, (size_t)mine * n * 2, s);
+    } else {
+      rc = comm_reduce_scatter_rows(c, res, 1, 0, (size_t)mine * X * 2, s);
+    }
+    if (rc) return rc;
+    RealView v;
+    int count;
+    if (!as_images(tw, &v, &count)) return kUnsupportedDimension;
+    v.p += lo * v.sb;
+    CplxView sv = spectrum_view(res + lo * (blk ? (long long)n * 2 : X * 2), n, blk ? planes : 0, n);
+    rc = n <= 32 ? fft2d_small_inverse(n, sv, v, (int)mine, 0, 0, s) : fft2d_large_inverse(n, sv, v, (int)mine, 0, 0, s);
+    if (rc) return rc;
+    return comm_all_gather(c, grad_weight, (size_t)mine * tw.size[2] * tw.size[3], s);
+  }
+  // the sum of the whole frequency-domain gradient on every rank, then the full inverse everywhere
+  if ((rc = comm_all_reduce(c, res, (size_t)planes * X * 2, s))) return rc;
+  return inverse(n, res, tw, 0, 0, blk, s);
 }
 
 }  // extern "C"

@@ -56,7 +56,7 @@ extern "C" int fbfft_b200_conv_update_output_noalloc(int fft_size, const float* 
                                                      const float* weight, const int* w_size, const int* w_stride,
                                                      float* out, const int* out_size, const int* out_stride,
                                                      int out_padL, int out_padU, void* stream) {
-  if (!in_size || !w_size || !out_size) {
+  if (!in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride) {
     fbfft_b200::set_last_error("null argument");
     return FBFFT_UNSUPPORTED_DIMENSION;
   }

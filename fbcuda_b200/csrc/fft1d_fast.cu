@@ -361,10 +361,7 @@ int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long task
   }
 }
 
-int read_device_error_fft1d() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_fft1d() { return device_error_word_read(); }
+int clear_device_error_fft1d() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -219,10 +219,7 @@ int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, 
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
-int read_device_error_256() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_256() { return device_error_word_read(); }
+int clear_device_error_256() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -364,10 +364,7 @@ int fft2d_rows_inv_fast(int n, const CplxView& src, const CplxView& buffer, int 
   return launch_rows_inv<128>(src.p, buffer.p, B, s);
 }
 
-int read_device_error_cols() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_cols() { return device_error_word_read(); }
+int clear_device_error_cols() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -585,10 +585,7 @@ int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, in
   return launch_inv<128>(in, out, B, padL, padU, s);
 }
 
-int read_device_error_coop() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
-}
+int read_device_error_coop() { return device_error_word_read(); }
+int clear_device_error_coop() { return device_error_word_clear(); }
 
 }  // namespace fbfft_b200

@@ -436,10 +436,38 @@ int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, i
   }
 }
 
-int read_device_error() {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
-  return v;
+int read_device_error() { return device_error_word_read(); }
+int clear_device_error() { return device_error_word_clear(); }
+
+// ---------------------------------------------------------------- self-test of the bounded wait
+// One thread waits, through the same mbar_wait the transforms use, on a barrier whose phase
+// nothing ever completes.  The wait must run out, record its code and let the kernel return.
+namespace {
+constexpr int kErrSelftestWait = 901;
+__device__ unsigned long long g_selftest_ns = 0;
+
+__global__ void selftest_wait_kernel(int max_tries) {
+  __shared__ __align__(8) unsigned long long bar_mem;
+  if (threadIdx.x == 0) {
+    const unsigned bar = smem_u32(&bar_mem);
+    mbar_init(bar, 1);
+    fence_async_smem();
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const bool done = mbar_wait(bar, 0, kErrSelftestWait, max_tries);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    g_selftest_ns = done ? 0ULL : (t1 - t0);
+  }
+}
+}  // namespace
+
+int selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns) {
+  selftest_wait_kernel<<<1, 32>>>(max_tries);
+  if (cudaPeekAtLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) return kCudaError;
+  unsigned long long ns = 0;
+  if (cudaMemcpyFromSymbol(&ns, g_selftest_ns, sizeof(ns)) != cudaSuccess) return kCudaError;
+  if (elapsed_ns) *elapsed_ns = ns;
+  return kSuccess;
 }
 
 }  // namespace fbfft_b200

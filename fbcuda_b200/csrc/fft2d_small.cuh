@@ -228,7 +228,18 @@ __device__ __forceinline__ void store_columns_full(float* dst, int l, const floa
 // 16-byte aligned and sizes multiples of 16 bytes.  Waits are bounded: a wait that
 // runs out records an error code in g_device_error and the caller abandons its work.
 // one copy per translation unit (no relocatable device code); the unit that waits exports a reader
+// and a clearer built from the two helpers below
 static __device__ int g_device_error = 0;
+
+static inline int device_error_word_read() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+static inline int device_error_word_clear() {
+  const int zero = 0;
+  return cudaMemcpyToSymbol(g_device_error, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -261,9 +272,14 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-// true when the phase completed; false (after recording `code`) when the limit ran out
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int code) {
-  for (int i = 0; i < (1 << 20); ++i) {
+// true when the phase completed; false (after recording `code`) when `max_tries` suspended
+// attempts went by without it (each try_wait parks the thread for a hardware-defined slice of
+// time, so the bound is a time bound; fbfft_b200_selftest_bounded_wait measures the slice).
+// Every wait of the library goes through here or through the contraction's wait_bar, which is
+// bounded by the nanosecond timer and an abort word shared by the block's roles.
+constexpr int kWaitMaxTries = 1 << 20;
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int code, int max_tries = kWaitMaxTries) {
+  for (int i = 0; i < max_tries; ++i) {
     if (mbar_try(bar, parity)) return true;
   }
   atomicExch(&g_device_error, code);

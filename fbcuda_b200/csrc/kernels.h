@@ -21,6 +21,7 @@ bool fft2d_coop_supported(int n, const CplxView& c);
 int fft2d_coop_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_coop_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 int read_device_error_coop();
+int clear_device_error_coop();
 // N = 256 forward on a contiguous spectrum: two register passes, no intermediate buffer (fft2d_256.cu)
 bool fft2d_256_supported(const RealView& in, const CplxView& out, int B);
 int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
@@ -38,6 +39,7 @@ int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int 
 bool fft2d_rows_inv_fast_supported(int n, const CplxView& src, const CplxView& buffer, int B);
 int fft2d_rows_inv_fast(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s);
 int read_device_error_cols();
+int clear_device_error_cols();
 int fft2d_large_cols_forward(int n, const CplxView& buffer, const CplxView& dst, int B, cudaStream_t s);
 int fft2d_large_rows_inverse(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s);
 int fft2d_large_cols_inverse(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU,
@@ -53,7 +55,9 @@ bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, cons
 int fft1d_fast_group(int n);
 int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s);
 int read_device_error_fft1d();
+int clear_device_error_fft1d();
 int read_device_error_256();
+int clear_device_error_256();
 int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int cs0, int cs1, int cs2, int B, int padL,
                   cudaStream_t s);
 int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* real, int rs0, int rs1, int B, int padL,
@@ -85,10 +89,12 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
               bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb);
 int read_device_error_tma();
+int clear_device_error_tma();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only
 void set_contraction_mode(int mode);
 int contraction_mode();
 int read_device_error_tc();
+int clear_device_error_tc();
 
 // tiled convolution passes (conv_iterated.cu)
 int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbfft_tiled_tensor4* outs, float* weight,
@@ -97,5 +103,9 @@ int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbf
 
 // value of the device-side error word (0 = none; set when a bounded wait inside a kernel ran out)
 int read_device_error();
+int clear_device_error();
+// one block waits `max_tries` attempts on a barrier that nothing completes, gives up, records
+// code 901 and returns; *elapsed_ns (host pointer) receives the time the wait took (fft2d_small.cu)
+int selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns);
 
 }  // namespace fbfft_b200

@@ -49,8 +49,21 @@ const char* fbfft_b200_last_error(void);
 /* Synchronising health check (no counterpart in the reference): returns 0 when no
  * kernel of this library has recorded a device-side error on the current device,
  * else the code it recorded (a bounded wait on an asynchronous copy that ran out:
- * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128, 201 / 202 tensor-core contraction), or -1 if the status cannot be read. */
+ * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128, 201 / 202 and 211-216 tensor-core contraction,
+ * 901 the self-test below), or -1 if the status cannot be read. */
 int fbfft_b200_device_status(void);
+
+/* Resets the device-side error code of the current device to 0 (synchronises).  The code is
+ * sticky until cleared; no counterpart in the reference. */
+int fbfft_b200_clear_device_status(void);
+
+/* Test hook (no counterpart in the reference): launches one block whose single waiting thread
+ * waits, with the transforms' own bounded wait, on a barrier that nothing ever completes, with a
+ * limit of `max_tries` (1 .. 2^20, the limit the kernels use) suspended attempts.  The wait runs
+ * out, the kernel returns by itself, fbfft_b200_device_status() then reports 901 until cleared,
+ * and *elapsed_ns (a host pointer, may be NULL) receives the time the wait took on the device, so
+ * that a caller can convert the kernels' limit into seconds.  Synchronises. */
+int fbfft_b200_selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns);
 
 /* How fbfft_b200_transpose_mm and the convolution passes contract (process-wide; no
  * counterpart in the reference, whose transposeMM is FP32 CUDA-core code only):
@@ -180,9 +193,14 @@ int fbfft_b200_plan_tiles(int fft_size, int kernel_h, int kernel_w, int pad_h, i
  *
  * The workspace holds four spectrum regions (input, output, weight, result); a
  * pass can skip a forward transform whose spectrum an earlier pass left in the
- * workspace (REUSE flags), and accGradParameters can stop after the contraction
- * and resume from the result region so that a caller can all-reduce the
- * frequency-domain weight gradient across GPUs in between. */
+ * workspace (REUSE flags), and every pass can stop after the contraction
+ * (STOP_AFTER_CONTRACTION) and resume from the result region (START_FROM_SPECTRUM),
+ * so that a caller can sum the frequency-domain weight gradient across GPUs in
+ * between (fbfft_b200_conv_acc_grad_parameters_dp does exactly that).  The layout of
+ * the spectra inside the workspace depends on the transform size, the two plane
+ * counts and the contraction mode, never on the batch: ranks holding batch shards of
+ * different sizes (an empty one included) may add their result regions element by
+ * element. */
 enum {
   FBFFT_CONV_REUSE_INPUT_SPECTRUM = 1,
   FBFFT_CONV_REUSE_OUTPUT_SPECTRUM = 2,
@@ -191,7 +209,10 @@ enum {
   FBFFT_CONV_START_FROM_SPECTRUM = 16,
   /* accGradParameters: add this call's contraction to the result region instead of overwriting it
    * (the weight gradient summed over the tiles of an image larger than the transform) */
-  FBFFT_CONV_ACCUMULATE_RESULT = 32
+  FBFFT_CONV_ACCUMULATE_RESULT = 32,
+  /* run the forward transforms that are not marked REUSE, then return: a caller that holds the
+   * weights fixed over several calls transforms them once this way */
+  FBFFT_CONV_STOP_AFTER_TRANSFORMS = 64
 };
 enum {
   FBFFT_CONV_REGION_INPUT = 0,
@@ -230,6 +251,58 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
                                         const int* w_stride, const float* grad_out, const int* out_size,
                                         const int* out_stride, int out_padL, int out_padU, float scale,
                                         void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* ---- Data-parallel accGradParameters (no counterpart in the reference, which has no
+ * multi-GPU code; what is summed is its accGradParameters,
+ * fbfft/FFTIteratedConvolution.cuh:409-524, over batch shards) -------------------------
+ * One process per GPU; the batch is sharded, weights are replicated; updateOutput and
+ * updateGradInput need no communication.  The communicator wraps NCCL, which is loaded
+ * on first use (libnccl.so.2; inside a process that already loaded one, that copy).
+ *
+ * fbfft_b200_comm_unique_id: rank 0 fills FBFFT_B200_UNIQUE_ID_BYTES bytes (host memory) and
+ *   hands them to the other ranks by any means.
+ * fbfft_b200_comm_init: every rank, with its device current.  Bounded: when the ranks have not
+ *   all joined within timeout_ms the half-built communicator is aborted and FBFFT_CUDA_ERROR
+ *   returned.  The same limit bounds every later wait of the host on this communicator.
+ * fbfft_b200_comm_destroy: after the last call's work has finished on the stream.
+ * fbfft_b200_dp_shard: the contiguous shard [lo, lo + count) of `total` units for `rank`
+ *   (the first total % world ranks hold one more); host arithmetic only. */
+#define FBFFT_B200_UNIQUE_ID_BYTES 128
+typedef struct fbfft_b200_comm fbfft_b200_comm;
+int fbfft_b200_comm_unique_id(void* id_out);
+int fbfft_b200_comm_init(const void* unique_id, int rank, int world, int timeout_ms, fbfft_b200_comm** out);
+int fbfft_b200_comm_info(const fbfft_b200_comm* comm, int* rank, int* world);
+int fbfft_b200_comm_destroy(fbfft_b200_comm* comm);
+int fbfft_b200_dp_shard(long long total, int world, int rank, long long* lo, long long* count);
+
+/* How the weight gradient is summed over the ranks:
+ *  FREQUENCY_ALLREDUCE       one all-reduce of the frequency-domain gradient
+ *                            ([O][C][N/2+1][N] complex) between the contraction and its inverse
+ *                            transform, which every rank then runs in full;
+ *  FREQUENCY_REDUCE_SCATTER  the same sum taken as a reduce-scatter over the O*C planes: every rank
+ *                            receives 1/world of the planes, inverse-transforms and crops only those,
+ *                            and an all-gather distributes the (small) spatial gradient -- half the
+ *                            bytes on the links and 1/world of the inverse work.  Needs O*C divisible
+ *                            by world and a contiguous grad_weight, else it runs as the all-reduce;
+ *  SPATIAL_ALLREDUCE         inverse transform first, all-reduce of the spatial gradient (equal up to
+ *                            rounding, by linearity).
+ * All ranks must pass the same mode, transform size, plane counts and flags; batch sizes may
+ * differ (0 included).  Arguments as fbfft_b200_conv_acc_grad_parameters; in, grad_out and the
+ * batch are this rank's shard.  STOP_AFTER_CONTRACTION returns before the collective and
+ * START_FROM_SPECTRUM runs only the collective and what follows it, so that the sum can run on
+ * a second stream under the other passes.  Work is enqueued on `stream`; the host may wait, within
+ * the communicator's time limit, for NCCL to accept the calls. */
+enum {
+  FBFFT_DP_FREQUENCY_ALLREDUCE = 0,
+  FBFFT_DP_FREQUENCY_REDUCE_SCATTER = 1,
+  FBFFT_DP_SPATIAL_ALLREDUCE = 2
+};
+int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int fft_size, const float* in,
+                                           const int* in_size, const int* in_stride, int in_padL, int in_padU,
+                                           float* grad_weight, const int* w_size, const int* w_stride,
+                                           const float* grad_out, const int* out_size, const int* out_stride,
+                                           int out_padL, int out_padU, float scale, void* workspace,
+                                           size_t workspace_bytes, int flags, void* stream);
 
 /* updateOutput without any device allocation, for callers that must not allocate:
  * a plugin invoked while its host holds the allocator, a loop with a

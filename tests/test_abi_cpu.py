@@ -49,3 +49,67 @@ def test_validation_without_device():
     assert rc == int(fb.ErrorCode.UnsupportedSize)
     assert "N must be" in fb.last_error()
     assert L.fbfft_b200_set_contraction_mode(7) == int(fb.ErrorCode.UnsupportedDimension)
+
+
+def test_conv_entry_points_refuse_null_strides_and_negative_pads():
+    L = fb.lib()
+    i4 = (ctypes.c_int * 4)(1, 1, 8, 8)
+    p = ctypes.c_void_p(256)
+    for f in (L.fbfft_b200_conv_update_output, L.fbfft_b200_conv_update_grad_input):
+        rc = f(8, p, i4, None, 0, 0, p, i4, i4, p, i4, i4, 0, 0, p, 1 << 20, 0, None)
+        assert rc == int(fb.ErrorCode.UnsupportedDimension) and "null" in fb.last_error()
+        rc = f(8, p, i4, i4, -1, 0, p, i4, i4, p, i4, i4, 0, 0, p, 1 << 20, 0, None)
+        assert rc == int(fb.ErrorCode.UnsupportedDimension) and "negative" in fb.last_error()
+    rc = L.fbfft_b200_conv_acc_grad_parameters(8, p, i4, i4, 0, 0, p, i4, None, p, i4, i4, 0, 0, 1.0, p, 1 << 20, 0, None)
+    assert rc == int(fb.ErrorCode.UnsupportedDimension)
+    rc = L.fbfft_b200_conv_acc_grad_parameters(8, p, i4, i4, 0, 0, p, i4, i4, p, i4, i4, 0, -2, 1.0, p, 1 << 20, 0, None)
+    assert rc == int(fb.ErrorCode.UnsupportedDimension) and "negative" in fb.last_error()
+    f = L.fbfft_b200_conv_update_output_noalloc
+    f.restype = ctypes.c_int
+    assert f(8, p, i4, None, 0, 0, p, i4, i4, p, i4, i4, 0, 0, None) == int(fb.ErrorCode.UnsupportedDimension)
+
+
+def test_single_call_inverse_refuses_n256_with_the_way_out():
+    L = fb.lib()
+    c4 = (ctypes.c_int * 4)(1, 129, 256, 2)
+    r3 = (ctypes.c_int * 3)(1, 256, 256)
+    p = ctypes.c_void_p(256)
+    rc = L.fbfft_b200_fft2d_c2r(256, p, c4, c4, p, r3, r3, 0, 0, None)
+    assert rc == int(fb.ErrorCode.UnsupportedSize)
+    assert "two-call" in fb.last_error()
+
+
+def test_dp_shards_cover_the_units_like_the_python_helper():
+    from fbcuda_b200.dist import shard_bounds
+    for total in (0, 1, 7, 64, 9216):
+        for world in (1, 2, 3, 8):
+            spans = [fb.dp_shard(total, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][0] + spans[-1][1] == total
+            for r, (lo, cnt) in enumerate(spans):
+                assert (lo, lo + cnt) == shard_bounds(total, world, r)
+    L = fb.lib()
+    lo, cnt = ctypes.c_longlong(), ctypes.c_longlong()
+    assert L.fbfft_b200_dp_shard(4, 2, 2, ctypes.byref(lo), ctypes.byref(cnt)) == int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_dp_shard(4, 0, 0, ctypes.byref(lo), ctypes.byref(cnt)) == int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_dp_shard(4, 2, 0, None, None) == int(fb.ErrorCode.UnsupportedDimension)
+
+
+def test_communicator_entry_points_refuse_bad_arguments_on_the_host():
+    L = fb.lib()
+    h = ctypes.c_void_p()
+    ident = ctypes.create_string_buffer(128)
+    bad = int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_comm_unique_id(None) == bad
+    assert L.fbfft_b200_comm_init(None, 0, 2, 1000, ctypes.byref(h)) == bad
+    assert L.fbfft_b200_comm_init(ident, 2, 2, 1000, ctypes.byref(h)) == bad and "rank" in fb.last_error()
+    assert L.fbfft_b200_comm_init(ident, 0, 0, 1000, ctypes.byref(h)) == bad
+    assert L.fbfft_b200_comm_init(ident, 0, 2, 0, ctypes.byref(h)) == bad and "time limit" in fb.last_error()
+    assert L.fbfft_b200_comm_init(ident, 0, 2, 1000, None) == bad
+    assert not h.value
+    assert L.fbfft_b200_comm_destroy(None) == bad
+    assert L.fbfft_b200_comm_info(None, None, None) == bad
+    # the data-parallel pass without a communicator is an error, not a silent single-GPU run
+    i4 = (ctypes.c_int * 4)(1, 1, 8, 8)
+    p = ctypes.c_void_p(256)
+    rc = L.fbfft_b200_conv_acc_grad_parameters_dp(None, 0, 8, p, i4, i4, 0, 0, p, i4, i4, p, i4, i4, 0, 0, 1.0, p, 1 << 20, 0, None)
+    assert rc == bad and "communicator" in fb.last_error()
