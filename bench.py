@@ -12,10 +12,14 @@ batch of synthetic input:
   batched-2D configuration, its 128 x 64 planes scaled up until the input exceeds
   L2 by far); --fft-size N selects a point of the size sweep (N x N images).
   Metric: algorithmic GB/s, (4*h*w + 8*N*(N/2+1)) bytes per image.  The batch
-  shards over GPUs with no communication (weak scaling).
-* workload "conv": updateOutput + updateGradInput + accGradParameters of the
-  FFT-64 layer (B=64, C=O=128, 56x56, 3x3, pad 1), batch sharded over GPUs,
-  frequency-domain weight gradient all-reduced with NCCL.  Metric: images/s.
+  shards over GPUs with no communication (weak scaling).  After the headline the
+  same run times the convolution layers (see "conv" below) at the same number of
+  GPUs and appends them as the last keys of the line ("conv4", "conv5", "conv3");
+  --conv-blocks 0 leaves them out.
+* workload "conv": updateOutput + updateGradInput + accGradParameters of one layer
+  (--conv-config), the global batch sharded over the GPUs (strong scaling), weights
+  replicated, the weight gradient summed over the library's NCCL communicator.
+  Metric: images/s.
 
 --impl reference times the reference path's CPU restatement (the reference has no
 CPU implementation and is GPU-only code that does not build for sm_100 unmodified)
@@ -38,11 +42,12 @@ if ROOT not in sys.path:
 
 GIB = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per image of the forward kernel, keyed by (FFT size,
-# image size), from the ncu captures summarised in profiles/ (profile case: a quarter of the bench
-# batch; traffic grows in proportion to the images, so it is scaled by images per launch)
-# the same for one launch of the contraction kernel (config 4), profiles/cgemm_tma_conv4.md
-NCU_CONTRACTION_TRAFFIC = {"conv4": 524.8e6}
+# image size), from ncu captures of the 256 MiB profile case (a quarter of the bench batch; traffic
+# grows in proportion to the images, so it is scaled by images per launch; at the end of the smaller
+# case a larger share of the output is still in L2, which is why the figure sits below the algorithmic bytes)
 NCU_TRAFFIC_BYTES_PER_IMAGE = {(32, 27): 6655.6, (32, 32): 7609.0, (64, 64): 30072.0, (128, 128): 119034.0}
+# the same for one launch of the contraction kernel (FFT-64 layer, one GPU)
+NCU_CONTRACTION_TRAFFIC = {"conv4": 524.8e6}
 
 
 def measured_peak_gbs():
@@ -217,9 +222,8 @@ def dist_setup(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # keep stdout to the one JSON line unless the caller asked NCCL for more
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
@@ -351,7 +355,7 @@ def run_fft2d(args, world, rank, local):
                 "peak_source": f"of {how}", "frac_of_8TBs": achieved / 8000.0,
                 "traffic": traffic * b if traffic else None, "algorithmic_bytes_per_launch": b * per_image,
                 "kernel": "fft2d_small_fwd_kernel" if n <= 32 else ("fft2d_coop_fwd_kernel" if n <= 128 else "fft256_rows_kernel + fft256_cols_kernel"),
-                "traffic_source": "ncu capture on the profile case (profiles/), scaled by images per launch" if traffic else None}
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 256 MiB profile case, scaled by images per launch" if traffic else None}
     extra = {}
     if args.extras and rank == 0 and world == 1:
         extra = run_extras(args, x, spec, n, hw)
@@ -439,128 +443,301 @@ def run_extras(args, x, spec, n0, hw0):
             "two_call_protocol_512MiB": two_call}
 
 
-def run_conv(args, world, rank, local):
-    """FFT-64 layer (B=64, C=O=128, 56x56, k3, pad 1): fwd + gradInput + gradWeight
-    with the batch sharded over the GPUs and the frequency-domain weight gradient
-    all-reduced (sum) over NCCL between the contraction and its inverse transform."""
+CONV_CONFIGS = {
+    # global batch, C, O, image, kernel, pad, FFT size, seeds (input, weight, gradOutput), weight std, passes
+    "conv3": dict(B=128, C=64, O=128, hw=27, k=5, pad=0, n=32, seeds=(2, 3, 10), wstd=(1.0 / (64 * 25)) ** 0.5, passes=1),
+    "conv4": dict(B=64, C=128, O=128, hw=56, k=3, pad=1, n=64, seeds=(4, 5, 6), wstd=(2.0 / (128 * 9)) ** 0.5, passes=3),
+    "conv5": dict(B=32, C=96, O=96, hw=128, k=13, pad=0, n=128, seeds=(7, 8, 9), wstd=(1.0 / (96 * 169)) ** 0.5, passes=3),
+}
+NVLINK_GBS = 770.0      # measured peer-copy bandwidth per direction per GPU on this pool
+_TF32_PEAK = {}
+
+
+def tf32_peak_tflops():
+    """Tensor-pipe rate of the contraction's MMA shapes, measured once per process with the library's
+    MMA-only kernel (no loads, no split, no epilogue)."""
+    import fbcuda_b200 as fb
+    if not _TF32_PEAK:
+        _TF32_PEAK["n128"] = fb.measure_tf32_peak(128)
+        _TF32_PEAK["n256"] = fb.measure_tf32_peak(256)
+    return _TF32_PEAK
+
+
+def make_communicator(world, rank):
+    """The library's own NCCL communicator (C ABI); torch.distributed only carries the identifier."""
+    if world == 1:
+        return None
+    import torch.distributed as dist
+    import fbcuda_b200 as fb
+    ident = [fb.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ident, src=0)
+    return fb.Communicator(ident[0], rank, world, timeout_ms=120000)
+
+
+def time_event_us(fn, reps=10, warm=2):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def conv_block(name, args, world, rank, comm, with_cpu=True):
+    """One convolution layer at `world` GPUs: updateOutput (+ updateGradInput + accGradParameters),
+    global batch sharded contiguously over the ranks, weights replicated.  Returns the block of
+    the JSON line: images/s and ms per step (max over ranks), the phases timed one by one, the
+    roofline with both bounds, the end-to-end figure, the CPU restatement on a batch sample and the
+    parity of one step against the float64 oracle."""
+    import numpy as np
     import torch
     import fbcuda_b200 as fb
     from fbcuda_b200 import api
-    cfg = {"conv4": (64, 128, 128, 56, 3, 1, 64), "conv5": (32, 96, 96, 128, 13, 0, 128),
-           "conv3": (128, 64, 128, 27, 5, 0, 32)}[args.conv_config]
-    bg, c, o, hw, k, pad, n = cfg
-    from fbcuda_b200.dist import all_reduce_sum, shard_bounds
-    lo, hi = shard_bounds(bg, world, rank)
-    b = hi - lo
+    cfg = CONV_CONFIGS[name]
+    bg, c, o, hw, k, pad, n, passes = cfg["B"], cfg["C"], cfg["O"], cfg["hw"], cfg["k"], cfg["pad"], cfg["n"], cfg["passes"]
     oh = hw + 2 * pad - k + 1
-    gen = torch.Generator(device="cuda").manual_seed(4 + rank)
-    x = torch.randn((b, c, hw, hw), device="cuda", generator=gen)
-    w = torch.randn((o, c, k, k), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)) * \
-        (2.0 / (c * k * k)) ** 0.5
-    go = torch.randn((b, o, oh, oh), device="cuda", generator=gen)
-    out = torch.empty_like(go)
-    gi = torch.empty_like(x)
-    gw = torch.empty_like(w)
-    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
-    off, _ = fb.conv_workspace_region(n, b, c, o, api.REGION_RESULT)
-    wspec = ws[off // 4: off // 4 + o * c * (n // 2 + 1) * n * 2]
+    lo, b = fb.dp_shard(bg, world, rank)
     ip = (pad, pad)
+    # the full global tensors, identical on every rank (seeded device generators); a rank keeps its shard
+    def full(seed, shape, scale=1.0):
+        return torch.randn(shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed)) * scale
+    x_full = full(cfg["seeds"][0], (bg, c, hw, hw))
+    go_full = full(cfg["seeds"][2], (bg, o, oh, oh))
+    w = full(cfg["seeds"][1], (o, c, k, k), cfg["wstd"])
+    x, go = x_full[lo:lo + b].clone(), go_full[lo:lo + b].clone()
+    # planes for the weight-gradient spot check over the FULL global batch (rank 0 checks)
+    prng = np.random.default_rng(123)
+    pairs = [(int(prng.integers(o)), int(prng.integers(c))) for _ in range(6)] + [(0, 0), (o - 1, c - 1)]
+    if rank == 0:
+        x_planes = {cc: x_full[:, cc].cpu().numpy() for cc in {p[1] for p in pairs}}
+        go_planes = {oo: go_full[:, oo].cpu().numpy() for oo in {p[0] for p in pairs}}
+    del x_full, go_full
+    out, gi, gw = torch.empty_like(go), torch.empty_like(x), torch.empty_like(w)
+    ws = torch.empty(fb.conv_workspace_bytes(n, max(b, 1), c, o) // 4, device="cuda")
+    every = api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM | api.REUSE_WEIGHT_SPECTRUM
+    side = torch.cuda.Stream()
+    ws2 = torch.empty_like(ws) if (world > 1 and passes == 3) else None
 
-    overlap = world > 1 and args.dw_mode == "frequency" and not args.no_overlap
-    if overlap:
-        # the weight-gradient pass gets a workspace of its own, so that its frequency-domain
-        # all-reduce can run on a side stream while the other two passes use the first workspace
-        ws2 = torch.empty_like(ws)
-        wspec2 = ws2[off // 4: off // 4 + o * c * (n // 2 + 1) * n * 2]
-        comm = torch.cuda.Stream()
-
-    def step():
-        if overlap:
-            cur = torch.cuda.current_stream()
-            fb.conv_acc_grad_parameters(n, x, gw, go, ws2, inPad=ip, flags=api.STOP_AFTER_CONTRACTION)
-            comm.wait_stream(cur)
-            with torch.cuda.stream(comm):
-                all_reduce_sum(wspec2)
-            fb.conv_update_output(n, x, w, out, ws, inPad=ip)
-            fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
-            cur.wait_stream(comm)
-            fb.conv_acc_grad_parameters(n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM)
-            return
+    def step_one_gpu():
         fb.conv_update_output(n, x, w, out, ws, inPad=ip)
-        fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
-        if world > 1 and args.dw_mode == "frequency":
-            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.REUSE_INPUT_SPECTRUM |
-                                        api.REUSE_OUTPUT_SPECTRUM | api.STOP_AFTER_CONTRACTION)
-            all_reduce_sum(wspec)
-            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip, flags=api.START_FROM_SPECTRUM)
-        else:
+        if passes == 3:
+            fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
             fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip,
                                         flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
-            if world > 1:
-                all_reduce_sum(gw)
 
-    # One GPU: the nine launches of a step are captured once into a CUDA graph and replayed (the
-    # library allocates nothing and synchronises nothing, so its calls are capturable after one
-    # eager step has set the kernels' attributes).
-    timed = step
-    graphed = world == 1 and not args.no_graph
-    if graphed:
-        step()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        timed = graph.replay
+    def make_step_dp(mode, collective=True):
+        # the weight-gradient contraction runs first, in a workspace of its own; its sum over the
+        # ranks, inverse transform (and gather) run on a second stream under the other two passes
+        def step():
+            cur = torch.cuda.current_stream()
+            fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.STOP_AFTER_CONTRACTION)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                if collective:
+                    fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM)
+                else:
+                    fb.conv_acc_grad_parameters(n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM)
+            fb.conv_update_output(n, x, w, out, ws, inPad=ip)
+            fb.conv_update_grad_input(n, gi, w, go, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
+            cur.wait_stream(side)
+        return step
 
+    modes = {"frequency_reduce_scatter": api.DP_FREQUENCY_REDUCE_SCATTER, "frequency_allreduce": api.DP_FREQUENCY_ALLREDUCE,
+             "spatial_allreduce": api.DP_SPATIAL_ALLREDUCE}
+    steps, warm = args.steps, max(3, args.warmup)
+    block = {"workload": f"conv {'fwd' if passes == 1 else 'fwd+gradInput+gradWeight'} B={bg} C={c} O={o} {hw}x{hw} k{k} pad{pad} FFT{n}",
+             "n_gpus": world, "scaling": "strong", "images_per_step": bg, "shard_images": b}
+    if world == 1 or passes == 1:
+        # one GPU: the step's launches are captured once into a CUDA graph and replayed
+        step_check = step_one_gpu
+        timed = step_one_gpu
+        if not args.no_graph:
+            step_one_gpu()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_one_gpu()
+            timed = graph.replay
+        ms = time_steps(timed, steps, warm, 1 if passes == 1 else world)
+        block.update({"ms_per_step": ms, "images_per_s": bg / (ms / 1e3),
+                      "launch": ("eager" if args.no_graph else "CUDA graph replay") + f" of {4 if passes == 1 else 9} kernels per step"})
+    else:
+        per_mode = {}
+        for mname, mode in modes.items():
+            ms_m = time_steps(make_step_dp(mode), steps, warm, world)
+            per_mode[mname] = {"ms_per_step": ms_m, "images_per_s": bg / (ms_m / 1e3)}
+        ms_none = time_steps(make_step_dp(modes["frequency_allreduce"], collective=False), steps, warm, world)
+        for mname in per_mode:
+            per_mode[mname]["collective_exposed_us"] = (per_mode[mname]["ms_per_step"] - ms_none) * 1e3
+        head = "frequency_reduce_scatter"
+        ms = per_mode[head]["ms_per_step"]
+        block.update({"ms_per_step": ms, "images_per_s": bg / (ms / 1e3), "dw_mode": head, "dw_modes": per_mode,
+                      "ms_per_step_without_collective": ms_none, "nccl_ranks": comm.world,
+                      "launch": "eager; the weight-gradient sum, inverse and gather on a second stream under updateOutput and updateGradInput"})
+        step_check = make_step_dp(modes[head])
+
+    # ---- parity of one step against the float64 oracle (outside every timed region)
+    out.fill_(7.0), gi.fill_(7.0), gw.fill_(7.0)
+    step_check()
+    torch.cuda.synchronize()
+    if rank == 0:
+        from oracle import fbfft_oracle as orc
+        nb = min(2, b)
+        wh = w.cpu().numpy()
+        par = {"out_rel_l2": orc.rel_l2(out[:nb].cpu().numpy(), orc.fftconv_update_output(x[:nb].cpu().numpy(), wh, n, pad)),
+               "images_checked": nb}
+        if passes == 3:
+            par["grad_input_rel_l2"] = orc.rel_l2(gi[:nb].cpu().numpy(),
+                                                  orc.fftconv_update_grad_input(go[:nb].cpu().numpy(), wh, n, hw, hw, pad))
+            gw_h = gw.cpu().numpy()
+            want = np.stack([orc.fftconv_acc_grad_parameters_planes(
+                np.stack([x_planes[cc]], 1), np.stack([go_planes[oo]], 1), n, k, k, [(0, 0)], pad)[0] for (oo, cc) in pairs])
+            par["grad_weight_rel_l2"] = orc.rel_l2(np.stack([gw_h[oo, cc] for (oo, cc) in pairs]), want)
+            par["grad_weight_planes_checked"] = f"{len(pairs)} (o, c) planes over the full global batch of {bg}"
+        par["tolerance"] = 1e-4
+        par["ok"] = all(v < 1e-4 for kk, v in par.items() if kk.endswith("rel_l2"))
+        par["device_status"] = fb.device_status()
+        block["parity"] = par
+        if not par["ok"] or par["device_status"] != 0:
+            raise SystemExit(f"{name}: parity against the oracle failed: {par}")
+
+    # ---- phases, one by one on this rank's shard (rank 0 reports)
+    phases = {}
+    if b > 0:
+        phases["fwd_transform_input_us"] = time_event_us(lambda: fb.conv_update_output(
+            n, x, w, out, ws, inPad=ip, flags=api.STOP_AFTER_TRANSFORMS | api.REUSE_WEIGHT_SPECTRUM))
+        phases["fwd_transform_weight_us"] = time_event_us(lambda: fb.conv_update_output(
+            n, x, w, out, ws, inPad=ip, flags=api.STOP_AFTER_TRANSFORMS | api.REUSE_INPUT_SPECTRUM))
+        phases["contraction_output_us"] = time_event_us(lambda: fb.conv_update_output(
+            n, x, w, out, ws, inPad=ip, flags=every | api.STOP_AFTER_CONTRACTION))
+        phases["inv_transform_output_us"] = time_event_us(lambda: fb.conv_update_output(
+            n, x, w, out, ws, inPad=ip, flags=api.START_FROM_SPECTRUM))
+        if passes == 3:
+            phases["fwd_transform_grad_output_us"] = time_event_us(lambda: fb.conv_update_grad_input(
+                n, gi, w, go, ws, inPad=ip, flags=api.STOP_AFTER_TRANSFORMS | api.REUSE_WEIGHT_SPECTRUM))
+            phases["contraction_grad_input_us"] = time_event_us(lambda: fb.conv_update_grad_input(
+                n, gi, w, go, ws, inPad=ip, flags=every | api.STOP_AFTER_CONTRACTION))
+            phases["inv_transform_grad_input_us"] = time_event_us(lambda: fb.conv_update_grad_input(
+                n, gi, w, go, ws, inPad=ip, flags=api.START_FROM_SPECTRUM))
+            phases["contraction_grad_weight_us"] = time_event_us(lambda: fb.conv_acc_grad_parameters(
+                n, x, gw, go, ws, inPad=ip, flags=every | api.STOP_AFTER_CONTRACTION))
+            phases["inv_transform_grad_weight_full_us"] = time_event_us(lambda: fb.conv_acc_grad_parameters(
+                n, x, gw, go, ws, inPad=ip, flags=api.START_FROM_SPECTRUM))
+    if world > 1 and passes == 3:
+        # the sum over the ranks with what follows it (inverse, gather), alone on the stream
+        for mname, mode in modes.items():
+            fn = lambda mode=mode: fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws, inPad=ip,
+                                                                  flags=api.START_FROM_SPECTRUM)
+            barrier_sync(world)
+            phases[f"sum_and_inverse_{mname}_us"] = time_event_us(fn, reps=5, warm=2)
+    block["phases_rank0"] = phases
+
+    # ---- roofline: the slower of compulsory bytes at the measured HBM rate and the 3xTF32 products
+    # at the measured tensor rate (both over all GPUs); the dominant kernel's own fraction beside it
+    bins = (n // 2 + 1) * n
+    comp_bytes = passes * 4.0 * (bg * c * hw * hw + o * c * k * k + bg * o * oh * oh)
+    flops = passes * 8.0 * bg * c * o * bins
+    peak, how = measured_peak_gbs()
+    tf32 = tf32_peak_tflops()
+    bytes_us = comp_bytes / (world * peak * 1e9) * 1e6
+    tensor_us = 3.0 * flops / (world * tf32["n128"] * 1e12) * 1e6
+    bound_us = max(bytes_us, tensor_us)
+    freq_bytes = 8.0 * o * c * bins
+    rl = {"bound": "hbm" if bytes_us >= tensor_us else "tensor", "compulsory_bytes": comp_bytes,
+          "bytes_bound_us": bytes_us, "contraction_flops_fp32": flops, "mma_flops_3xtf32": 3.0 * flops,
+          "tensor_bound_us": tensor_us, "tf32_peak_tflops_measured": tf32, "hbm_peak_gbs": peak, "peak_source": f"of {how}",
+          "bound_us": bound_us, "step_us": ms * 1e3, "frac": bound_us / (ms * 1e3),
+          "achieved_gbs_on_compulsory_bytes": comp_bytes / (ms / 1e3) / 1e9,
+          "achieved_tflops_fp32_equivalent": flops / (ms / 1e3) / 1e12}
+    if world > 1 and passes == 3:
+        rl["nvlink_us"] = {"frequency_reduce_scatter": (world - 1) / world * freq_bytes / (NVLINK_GBS * 1e9) * 1e6,
+                           "frequency_allreduce": 2 * (world - 1) / world * freq_bytes / (NVLINK_GBS * 1e9) * 1e6,
+                           "spatial_allreduce": 2 * (world - 1) / world * gw.numel() * 4 / (NVLINK_GBS * 1e9) * 1e6,
+                           "link_gbs": NVLINK_GBS}
+    if b > 0:
+        key = "contraction_grad_weight_us" if passes == 3 else "contraction_output_us"
+        con_bytes = 8.0 * bins * (b * c + b * o + o * c)
+        con_us = phases[key]
+        rl["dominant_kernel"] = {"kernel": "cgemm_tma_kernel", "phase": key, "us": con_us,
+                                 "algorithmic_bytes": con_bytes, "achieved_gbs": con_bytes / con_us / 1e3,
+                                 "frac_of_hbm": con_bytes / con_us / 1e3 / peak,
+                                 "tflops_fp32_equivalent": 8.0 * b * c * o * bins / con_us / 1e6,
+                                 "traffic": NCU_CONTRACTION_TRAFFIC.get(name) if world == 1 else None}
+    block["roofline"] = rl
+
+    # ---- end to end: shard inputs from pinned host memory every step, the weight gradient (or the
+    # output, for the forward-only layer) read back
+    if b > 0:
+        xh, goh = x.cpu().pin_memory(), go.cpu().pin_memory()
+        res_dev = gw if passes == 3 else out
+        resh = torch.empty(res_dev.shape).pin_memory()
+
+        def step_e2e():
+            x.copy_(xh, non_blocking=True)
+            if passes == 3:
+                go.copy_(goh, non_blocking=True)
+            step_check()
+            resh.copy_(res_dev, non_blocking=True)
+
+        ms_e2e = time_steps(step_e2e, max(2, steps // 2), 3, 1 if passes == 1 else world)
+        block["e2e"] = {"value": bg / (ms_e2e / 1e3), "unit": "images/s", "ms_per_step": ms_e2e,
+                        "h2d_bytes_per_step": (x.numel() + (go.numel() if passes == 3 else 0)) * 4,
+                        "d2h_bytes_per_step": res_dev.numel() * 4}
+        del xh, goh, resh
+
+    # ---- the CPU restatement of the reference algorithm on a batch sample (rank 0, one GPU run only)
+    if with_cpu and world == 1 and rank == 0:
+        from oracle import cpuref
+        cores = max(1, cpuref.hardware_threads())
+        bs = max(1, bg // 8)
+        xs, gs, wh = x[:bs].cpu().numpy(), go[:bs].cpu().numpy(), w.cpu().numpy()
+        t0 = time.perf_counter()
+        for pnum in range(passes):
+            cpuref.conv_pass(pnum, xs, gs, wh, n, in_pad=ip, threads=cores)
+        dt = time.perf_counter() - t0
+        block["cpu_baseline"] = {"value": bs / dt, "unit": "images/s", "cores": cores, "kind": "port",
+                                 "sample": f"batch {bs} of {bg}, one step ({dt:.2f} s), weight-side work not amortised over the full batch"}
+    del x, go, w, out, gi, gw, ws, ws2
+    torch.cuda.empty_cache()
+    return block
+
+
+def run_conv(args, world, rank, local):
+    """--workload conv: one layer as the whole line."""
+    comm = make_communicator(world, rank)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     t0 = time.time()
-    ms = time_steps(timed, args.steps, max(3, args.warmup), world)
+    block = conv_block(args.conv_config, args, world, rank, comm)
     t1 = time.time()
     clocks = sampler.stop(t0, t1) if rank == 0 else None
-    ips = bg / (ms / 1e3)
-
-    xh, goh = x.cpu().pin_memory(), go.cpu().pin_memory()
-    gwh = torch.empty(gw.shape).pin_memory()
-
-    def step_e2e():
-        x.copy_(xh, non_blocking=True)
-        go.copy_(goh, non_blocking=True)
-        step()
-        gwh.copy_(gw, non_blocking=True)
-
-    ms_e2e = time_steps(step_e2e, max(2, args.steps // 2), 3, world)
-    bins = (n // 2 + 1) * n
-    flops = 3 * 8.0 * bg * c * o * bins
-    # the dominant kernel alone: the weight-gradient contraction on the spectra already in the
-    # workspace (operands read once + result written once = its algorithmic bytes)
-    ms_con = time_steps(lambda: fb.conv_acc_grad_parameters(
-        n, x, gw, go, ws, inPad=ip, flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM |
-        api.STOP_AFTER_CONTRACTION), args.steps, 3, world)
-    con_bytes = 8.0 * bins * (b * c + b * o + o * c)
-    peak = measured_peak_gbs()
-    traffic = NCU_CONTRACTION_TRAFFIC.get(args.conv_config) if world == 1 else None
-    line = {"metric": "FFT-conv layer fwd+bwd images/s", "value": ips, "unit": "images/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+    if comm is not None:
+        comm.destroy()
+    line = {"metric": "FFT-conv layer fwd+bwd images/s", "value": block["images_per_s"], "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": block["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"conv fwd+gradInput+gradWeight B={bg} C={c} O={o} {hw}x{hw} k{k} pad{pad} FFT{n}",
-                       "parallelism": f"batch sharded over {world} GPU(s), weights replicated, dW all-reduce in the {args.dw_mode} domain" +
-                                      (" on a side stream, overlapped with updateOutput and updateGradInput" if overlap else ""),
-                       "l2": "spectra (hundreds of MB) exceed the 126 MB L2",
-                       "launch": "CUDA graph replay of the step's 9 kernels" if graphed else "eager launches"},
-            "e2e": {"value": bg / (ms_e2e / 1e3), "unit": "images/s",
-                    "h2d_bytes_per_step": (x.numel() + go.numel()) * 4, "d2h_bytes_per_step": gw.numel() * 4,
-                    "ms_per_step": ms_e2e},
-            "gpu_launches": args.steps * (11 if overlap else 9), "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": con_bytes / (ms_con / 1e3) / 1e9, "peak": peak[0], "unit": "GB/s",
-                         "frac": con_bytes / (ms_con / 1e3) / 1e9 / peak[0], "peak_source": f"of {peak[1]}",
-                         "traffic": traffic, "algorithmic_bytes_per_launch": con_bytes,
-                         "kernel": "cgemm_tma_kernel (one of the step's three contractions, timed alone: "
-                                   f"{ms_con * 1e3:.1f} us)",
-                         "contraction_tflops_fp32_equivalent": flops / 3 / world / (ms_con / 1e3) / 1e12,
-                         "note": "the step covers 6 transform batches and 3 contractions; shares in profiles/"}}
+            "config": {"workload": block["workload"], "l2": "spectra (hundreds of MB) exceed the 126 MB L2",
+                       "parallelism": f"batch sharded over {world} GPU(s), weights replicated"},
+            "e2e": block.get("e2e"), "gpu_launches": args.steps * 9, "clocks": clocks, "roofline": block.get("roofline"),
+            "cpu_baseline": block.get("cpu_baseline"), args.conv_config: block}
     return line
+
+
+def rounded(v, digits=6):
+    """Floats of the line to `digits` significant digits (keeps the line short)."""
+    if isinstance(v, float):
+        return float(f"{v:.{digits}g}")
+    if isinstance(v, dict):
+        return {k: rounded(x, digits) for k, x in v.items()}
+    if isinstance(v, (list, tuple)):
+        return [rounded(x, digits) for x in v]
+    return v
 
 
 def main():
@@ -571,10 +748,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fft2d", choices=["fft2d", "conv"])
     ap.add_argument("--conv-config", default="conv4", choices=["conv3", "conv4", "conv5"])
-    ap.add_argument("--dw-mode", default="frequency", choices=["frequency", "spatial"])
     ap.add_argument("--no-graph", action="store_true", help="conv workload on one GPU: launch eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--no-overlap", action="store_true",
-                    help="frequency-domain dW all-reduce in line instead of overlapped with the other two passes")
+    ap.add_argument("--conv-blocks", type=int, default=1,
+                    help="fft2d workload: also time the convolution layers and append them to the line")
     ap.add_argument("--fft-size", type=int, default=32)
     ap.add_argument("--image-hw", type=int, default=0, help="image height = width (default: 27 for FFT size 32, else the FFT size)")
     ap.add_argument("--extras", type=int, default=1)
@@ -592,9 +768,24 @@ def main():
     world, rank, local = dist_setup(args)
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
-    line = run_fft2d(args, world, rank, local) if args.workload == "fft2d" else run_conv(args, world, rank, local)
+    if args.workload == "fft2d":
+        line = run_fft2d(args, world, rank, local)
+        if args.conv_blocks and not args.profile_case:
+            # the other half of the metric: the convolution layers at this number of GPUs, as the
+            # LAST keys of the line
+            import torch
+            torch.cuda.empty_cache()
+            comm = make_communicator(world, rank)
+            for name in ("conv4", "conv5") + (("conv3",) if world == 1 else ()):
+                block = conv_block(name, args, world, rank, comm)
+                if rank == 0:
+                    line[name] = block
+            if comm is not None:
+                comm.destroy()
+    else:
+        line = run_conv(args, world, rank, local)
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(rounded(line)))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

@@ -17,10 +17,13 @@ from .api import (  # noqa: F401
     fbifft2D_c2c,
     fft2d_c2r,
     fft2d_r2c,
+    fft2d_r2c_storage,
+    fft2d_c2r_storage,
     last_error,
     device_status,
     clear_device_status,
     selftest_bounded_wait,
+    measure_tf32_peak,
     dp_shard,
     comm_unique_id,
     Communicator,
@@ -34,6 +37,7 @@ from .api import (  # noqa: F401
     conv_update_grad_input,
     conv_acc_grad_parameters,
     plan_tiles,
+    conv_plan,
     plan_tiles_layout,
     tiled_conv_update_output,
     tiled_conv_update_grad_input,

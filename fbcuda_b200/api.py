@@ -40,6 +40,13 @@ class _Tiled(ctypes.Structure):
                 ("stride", ctypes.c_int * 4), ("size", ctypes.c_int * 4)]
 
 
+class _ConvPlan(ctypes.Structure):
+    """fbfft_b200_conv_plan_t."""
+    _fields_ = [("fft_size", ctypes.c_int), ("tiles", ctypes.c_int), ("tile_out_h", ctypes.c_int),
+                ("tile_out_w", ctypes.c_int), ("contraction", ctypes.c_int), ("dw_mode", ctypes.c_int),
+                ("workspace_bytes", ctypes.c_size_t), ("est_us", ctypes.c_float * 5)]
+
+
 _ip = ctypes.POINTER(ctypes.c_int)
 _vp = ctypes.c_void_p
 
@@ -79,12 +86,27 @@ def lib() -> ctypes.CDLL:
                                                           [ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
         L.fbfft_b200_conv_acc_grad_parameters_dp.argtypes = ([_vp, ctypes.c_int, ctypes.c_int] + tp + t4 + tp +
                                                              [ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
+        L.fbfft_b200_conv_plan.argtypes = [ctypes.c_int] * 10 + [ctypes.POINTER(_ConvPlan)]
+        L.fbfft_b200_conv_plan.restype = ctypes.c_int
+        tail = [ctypes.c_int, ctypes.c_int, _vp, sz, ctypes.c_int, _vp]
+        L.fbfft_b200_conv_tiled_update_output.argtypes = [ctypes.c_int] + t4 * 3 + tail
+        L.fbfft_b200_conv_tiled_update_grad_input.argtypes = [ctypes.c_int] + t4 * 3 + tail
+        L.fbfft_b200_conv_tiled_acc_grad_parameters.argtypes = ([ctypes.c_int] + t4 * 3 + [ctypes.c_int, ctypes.c_int,
+                                                                ctypes.c_float, _vp, sz, ctypes.c_int, _vp])
+        for name in ("conv_tiled_update_output", "conv_tiled_update_grad_input", "conv_tiled_acc_grad_parameters"):
+            getattr(L, "fbfft_b200_" + name).restype = ctypes.c_int
         L.fbfft_b200_comm_unique_id.argtypes = [_vp]
         L.fbfft_b200_comm_init.argtypes = [_vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_vp)]
         L.fbfft_b200_comm_info.argtypes = [_vp, _ip, _ip]
         L.fbfft_b200_comm_destroy.argtypes = [_vp]
         ll = ctypes.c_longlong
         L.fbfft_b200_dp_shard.argtypes = [ll, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ll), ctypes.POINTER(ll)]
+        st = [ctypes.c_int] * 3 + t4 + t4 + [ctypes.c_int, ctypes.c_int, _vp]
+        L.fbfft_b200_fft2d_r2c_storage.argtypes = st
+        L.fbfft_b200_fft2d_c2r_storage.argtypes = st
+        L.fbfft_b200_fft2d_r2c_storage.restype = L.fbfft_b200_fft2d_c2r_storage.restype = ctypes.c_int
+        L.fbfft_b200_measure_tf32_peak.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        L.fbfft_b200_measure_tf32_peak.restype = ctypes.c_int
         L.fbfft_b200_selftest_bounded_wait.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_ulonglong)]
         for name in ("conv_update_output", "conv_update_grad_input", "conv_acc_grad_parameters",
                      "conv_acc_grad_parameters_dp", "comm_unique_id", "comm_init", "comm_info", "comm_destroy",
@@ -114,6 +136,13 @@ def selftest_bounded_wait(max_tries: int = 1024) -> int:
     ns = ctypes.c_ulonglong(0)
     _check(lib().fbfft_b200_selftest_bounded_wait(int(max_tries), ctypes.byref(ns)))
     return int(ns.value)
+
+
+def measure_tf32_peak(n_cols: int = 256) -> float:
+    """TFLOP/s of tcgen05.mma kind::tf32 (128 x n_cols x 8, shared-memory operands) on the current GPU."""
+    v = ctypes.c_double(0.0)
+    _check(lib().fbfft_b200_measure_tf32_peak(int(n_cols), ctypes.byref(v)))
+    return float(v.value)
 
 
 def set_contraction_mode(mode: int) -> None:
@@ -203,6 +232,30 @@ def fft2d_r2c(n: int, real, complex, padL: int = 0, padU: int = 0, stream=None) 
 def fft2d_c2r(n: int, complex, real, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
     """Single-call inverse transform for any N in {8..256}."""
     return _check(lib().fbfft_b200_fft2d_c2r(n, *_t(complex), *_t(real), padL, padU, _stream(stream)))
+
+
+STORAGE_F32, STORAGE_F16, STORAGE_BF16 = 0, 1, 2
+
+
+def _storage(t) -> int:
+    import torch
+    try:
+        return {torch.float32: STORAGE_F32, torch.float16: STORAGE_F16, torch.bfloat16: STORAGE_BF16}[t.dtype]
+    except KeyError:
+        raise TypeError("storage types are float32, float16 and bfloat16") from None
+
+
+def fft2d_r2c_storage(n: int, real, complex, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """fbfft2D for N in {8, 16, 32} on fp32 / fp16 / bf16 tensors (any combination of the two);
+    the storage types are taken from the tensors' dtypes."""
+    return _check(lib().fbfft_b200_fft2d_r2c_storage(n, _storage(real), _storage(complex), *_t(real), *_t(complex), padL,
+                                                     padU, _stream(stream)))
+
+
+def fft2d_c2r_storage(n: int, complex, real, padL: int = 0, padU: int = 0, stream=None) -> ErrorCode:
+    """fbifft2D for N in {8, 16, 32} on fp32 / fp16 / bf16 tensors."""
+    return _check(lib().fbfft_b200_fft2d_c2r_storage(n, _storage(complex), _storage(real), *_t(complex), *_t(real), padL,
+                                                     padU, _stream(stream)))
 
 
 def transposeMM(A, B, C, invNorm: float, conjugateTransposeA: bool, conjugateTransposeB: bool,
@@ -352,60 +405,39 @@ def conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, 
                                                             float(scale), *_ws(workspace), flags, _stream(stream)))
 
 
-# ---- images larger than the transform: the workspace passes, tile by tile -----------------
-def _tile_windows(fftSize, in_shape, out_shape, kernel, pad, style):
-    """[(input window, input pads), (output window, output pads)] per tile; a window is
-    (y, x, h, w) into the last two axes, pads are (padL, padU)."""
-    ins, outs = plan_tiles_layout(fftSize, in_shape, out_shape, kernel, pad, style)
-    def window(entry, width):
-        off, (h, w), padL, padU = entry
-        return (off // width, off % width, h, w), (padL, padU)
-    return [(window(i, in_shape[3]), window(o, out_shape[3])) for i, o in zip(ins, outs)]
+# ---- whole layers: plan and the tile loop inside the library ------------------------------
+def conv_plan(batch, inPlanes, outPlanes, inH, inW, kH, kW, padH=0, padW=0, world=1) -> dict:
+    """fbfft_b200_conv_plan as a dict: fft_size, tiles, tile_out (h, w), contraction, dw_mode,
+    workspace_bytes and the cost estimates per candidate size {8: us, ..., 128: us}."""
+    p = _ConvPlan()
+    _check(lib().fbfft_b200_conv_plan(batch, inPlanes, outPlanes, inH, inW, kH, kW, padH, padW, world, ctypes.byref(p)))
+    return {"fft_size": p.fft_size, "tiles": p.tiles, "tile_out": (p.tile_out_h, p.tile_out_w),
+            "contraction": p.contraction, "dw_mode": p.dw_mode, "workspace_bytes": int(p.workspace_bytes),
+            "est_us": {8 << i: float(p.est_us[i]) for i in range(5)}}
 
 
-def _crop(t, win):
-    y, x, h, w = win
-    return t[:, :, y:y + h, x:x + w]
+def tiled_conv_update_output(fftSize, input, weight, output, workspace, pad=(0, 0), flags=0, stream=None):
+    """updateOutput of a stride-1 convolution on images of any size: the library loops over the
+    overlap-save tiles (fbfft_b200_conv_tiled_update_output).  pad = (padH, padW) of implicit zeros
+    around the input; the workspace is sized for one tile."""
+    return _check(lib().fbfft_b200_conv_tiled_update_output(fftSize, *_t(input), *_t(weight), *_t(output), pad[0], pad[1],
+                                                            *_ws(workspace), flags, _stream(stream)))
 
 
-def tiled_conv_update_output(fftSize, input, weight, output, workspace, pad=(0, 0), stream=None):
-    """updateOutput of a stride-1 convolution whose image is larger than the transform: the tiles of
-    plan_tiles (style 0) through conv_update_output, the weight spectrum computed once.
-    pad = (padH, padW) of implicit zeros around the input; the workspace is sized for one tile."""
-    kernel = (weight.shape[2], weight.shape[3])
-    flags = 0
-    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, input.shape, output.shape, kernel, pad, 0):
-        conv_update_output(fftSize, _crop(input, iw), weight, _crop(output, ow), workspace, ipad, opad, flags, stream)
-        flags = REUSE_WEIGHT_SPECTRUM
-    return ErrorCode(0)
+def tiled_conv_update_grad_input(fftSize, gradInput, weight, gradOutput, workspace, pad=(0, 0), flags=0, stream=None):
+    """updateGradInput over the tiles: every gradInput tile is the crop at (k - 1, k - 1) of the full
+    convolution of its gradOutput window with the weight."""
+    return _check(lib().fbfft_b200_conv_tiled_update_grad_input(fftSize, *_t(gradInput), *_t(weight), *_t(gradOutput),
+                                                                pad[0], pad[1], *_ws(workspace), flags, _stream(stream)))
 
 
-def tiled_conv_update_grad_input(fftSize, gradInput, weight, gradOutput, workspace, pad=(0, 0), stream=None):
-    """updateGradInput over the tiles of plan_tiles (style 1): every gradInput tile is the crop at
-    (k - 1, k - 1) of the full convolution of its gradOutput window with the weight."""
-    kernel = (weight.shape[2], weight.shape[3])
-    flags = 0
-    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, gradInput.shape, gradOutput.shape, kernel, pad, 1):
-        conv_update_grad_input(fftSize, _crop(gradInput, iw), weight, _crop(gradOutput, ow), workspace, ipad, opad,
-                               flags, stream)
-        flags = REUSE_WEIGHT_SPECTRUM
-    return ErrorCode(0)
-
-
-def tiled_conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, scale=1.0, pad=(0, 0),
+def tiled_conv_acc_grad_parameters(fftSize, input, gradWeight, gradOutput, workspace, scale=1.0, pad=(0, 0), flags=0,
                                    stream=None):
-    """accGradParameters over the tiles of plan_tiles (style 0): the per-tile contractions add up in
-    the workspace's result region (ACCUMULATE_RESULT), one inverse transform at the end."""
-    kernel = (gradWeight.shape[2], gradWeight.shape[3])
-    flags = STOP_AFTER_CONTRACTION
-    for (iw, ipad), (ow, opad) in _tile_windows(fftSize, input.shape, gradOutput.shape, kernel, pad, 0):
-        conv_acc_grad_parameters(fftSize, _crop(input, iw), gradWeight, _crop(gradOutput, ow), workspace, scale, ipad,
-                                 opad, flags, stream)
-        flags = STOP_AFTER_CONTRACTION | ACCUMULATE_RESULT
-    win = (0, 0, min(input.shape[2], fftSize), min(input.shape[3], fftSize))
-    owin = (0, 0, 1, 1)
-    return conv_acc_grad_parameters(fftSize, _crop(input, win), gradWeight, _crop(gradOutput, owin), workspace, scale,
-                                    (0, 0), (0, 0), START_FROM_SPECTRUM, stream)
+    """accGradParameters over the tiles: the per-tile contractions add up in the workspace's result
+    region, one inverse transform at the end."""
+    return _check(lib().fbfft_b200_conv_tiled_acc_grad_parameters(fftSize, *_t(input), *_t(gradWeight), *_t(gradOutput),
+                                                                  pad[0], pad[1], float(scale), *_ws(workspace), flags,
+                                                                  _stream(stream)))
 
 
 # ---- data-parallel accGradParameters (batch shards on several GPUs, NCCL) ------------------

@@ -101,13 +101,15 @@ const char* fbfft_b200_last_error(void) { return g_last_error; }
 
 int fbfft_b200_device_status(void) {
   const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc(), d = read_device_error_tma(),
-            e = read_device_error_fft1d(), f = read_device_error_256(), g = read_device_error_cols();
-  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : g)))));
+            e = read_device_error_fft1d(), f = read_device_error_256(), g = read_device_error_cols(),
+            h = read_device_error_peak();
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : (g != 0 ? g : h))))));
 }
 
 int fbfft_b200_clear_device_status(void) {
   const int r = clear_device_error() | clear_device_error_coop() | clear_device_error_tc() | clear_device_error_tma() |
-                clear_device_error_fft1d() | clear_device_error_256() | clear_device_error_cols();
+                clear_device_error_fft1d() | clear_device_error_256() | clear_device_error_cols() |
+                clear_device_error_peak();
   if (cudaDeviceSynchronize() != cudaSuccess || r != 0) return fail(kCudaError, "clear_device_status: cannot reset the status words");
   return kSuccess;
 }
@@ -115,6 +117,13 @@ int fbfft_b200_clear_device_status(void) {
 int fbfft_b200_selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns) {
   if (max_tries < 1 || max_tries > (1 << 20)) return fail(kUnsupportedDimension, "selftest_bounded_wait: max_tries must be in 1..2^20");
   if (selftest_bounded_wait(max_tries, elapsed_ns) != kSuccess) return fail(kCudaError, "selftest_bounded_wait: launch or read-back failed");
+  return kSuccess;
+}
+
+int fbfft_b200_measure_tf32_peak(int n_cols, double* tflops) {
+  if (!tflops || !(n_cols == 64 || n_cols == 128 || n_cols == 256))
+    return fail(kUnsupportedDimension, "measure_tf32_peak: n_cols must be 64, 128 or 256 and the output non-null");
+  if (measure_tf32_peak(n_cols, tflops) != kSuccess) return fail(kCudaError, "measure_tf32_peak: launch or timing failed");
   return kSuccess;
 }
 
@@ -161,6 +170,56 @@ int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const i
   RealView out = real_view(real, real_size, real_stride);
   if (small_size(n)) return fft2d_small_inverse(n, in, out, B, padL, padU, s);
   return fft2d_large_inverse(n, in, out, B, padL, padU, s);
+}
+
+namespace {
+int check_storage(const char* who, int n, int real_type, int cplx_type, const void* real, const int* real_size,
+                  const int* real_stride, const void* cplx, const int* cplx_size, const int* cplx_stride, int padL,
+                  int padU) {
+  static thread_local char msg[160];
+  auto bad = [&](int code, const char* what) {
+    std::snprintf(msg, sizeof(msg), "%s: %s", who, what);
+    return fail(code, msg);
+  };
+  if (!real_size || !real_stride || !cplx_size || !cplx_stride) return bad(kUnsupportedDimension, "null size/stride");
+  if (!small_size(n)) return bad(kUnsupportedSize, "16-bit storage covers N = 8, 16 and 32");
+  if (real_type < FBFFT_STORAGE_F32 || real_type > FBFFT_STORAGE_BF16 || cplx_type < FBFFT_STORAGE_F32 ||
+      cplx_type > FBFFT_STORAGE_BF16)
+    return bad(kUnsupportedDimension, "storage types are FBFFT_STORAGE_F32, _F16 or _BF16");
+  const int B = real_size[0], h = real_size[1], w = real_size[2];
+  if (B == 0) return kSuccess;
+  if (!real || !cplx) return bad(kUnsupportedDimension, "null tensor pointer");
+  if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != n || cplx_size[3] != 2)
+    return bad(kUnsupportedDimension, "complex tensor must be [B][N/2+1][N][2]");
+  if (h < 1 || w < 1 || h > n || w > n || padL < 0 || padU < 0)
+    return bad(kUnsupportedDimension, "the image must fit the transform and the padding be non-negative");
+  if (real_stride[2] != 1 || real_stride[1] != w || (B > 1 && real_stride[0] != h * w) || cplx_stride[3] != 1 ||
+      cplx_stride[2] != 2 || cplx_stride[1] != 2 * n || (B > 1 && cplx_stride[0] != (n / 2 + 1) * n * 2))
+    return bad(kUnsupportedDimension, "tensors must be contiguous");
+  if ((reinterpret_cast<uintptr_t>(real) & 3u) || (reinterpret_cast<uintptr_t>(cplx) & 15u))
+    return bad(kUnsupportedDimension, "the real tensor must be 4-byte aligned, the complex tensor 16-byte aligned");
+  return kSuccess;
+}
+}  // namespace
+
+int fbfft_b200_fft2d_r2c_storage(int n, int real_type, int cplx_type, const void* real, const int* real_size,
+                                 const int* real_stride, void* cplx, const int* cplx_size, const int* cplx_stride, int padL,
+                                 int padU, void* stream) {
+  const int rc = check_storage("fft2d_r2c_storage", n, real_type, cplx_type, real, real_size, real_stride, cplx, cplx_size,
+                               cplx_stride, padL, padU);
+  if (rc != kSuccess || real_size[0] == 0) return rc;
+  return fft2d_small_storage(n, false, real_type, cplx_type, real, cplx, real_size[0], real_size[1], real_size[2], padL, padU,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int fbfft_b200_fft2d_c2r_storage(int n, int cplx_type, int real_type, const void* cplx, const int* cplx_size,
+                                 const int* cplx_stride, void* real, const int* real_size, const int* real_stride, int padL,
+                                 int padU, void* stream) {
+  const int rc = check_storage("fft2d_c2r_storage", n, real_type, cplx_type, real, real_size, real_stride, cplx, cplx_size,
+                               cplx_stride, padL, padU);
+  if (rc != kSuccess || real_size[0] == 0) return rc;
+  return fft2d_small_storage(n, true, cplx_type, real_type, cplx, real, real_size[0], real_size[1], real_size[2], padL, padU,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int fbfft_b200_fbfft2d(const float* real, const int* real_size, const int* real_stride, float* cplx,

@@ -303,7 +303,9 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
                                         const int* w_stride, const float* grad_out, const int* out_size,
                                         const int* out_stride, int out_padL, int out_padU, float scale,
                                         void* workspace, size_t workspace_bytes, int flags, void* stream) {
-  if (!in || !grad_weight || !grad_out || !in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride) {
+  // an empty batch shard may come with null data pointers
+  if (!grad_weight || !in_size || !w_size || !out_size || !in_stride || !w_stride || !out_stride ||
+      (in_size[0] > 0 && (!in || !grad_out))) {
     set_last_error("null argument");
     return kUnsupportedDimension;
   }
@@ -365,11 +367,9 @@ int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int 
   // this rank's contraction (argument checks included); an empty shard zeroes the result region
   int rc = kSuccess;
   if (!(flags & FBFFT_CONV_START_FROM_SPECTRUM)) {
-    const int stop = mode == FBFFT_DP_SPATIAL_ALLREDUCE ? 0 : FBFFT_CONV_STOP_AFTER_CONTRACTION;
     rc = fbfft_b200_conv_acc_grad_parameters(fft_size, in, in_size, in_stride, in_padL, in_padU, grad_weight, w_size,
                                              w_stride, grad_out, out_size, out_stride, out_padL, out_padU, scale,
-                                             workspace, workspace_bytes, (flags & ~FBFFT_CONV_STOP_AFTER_CONTRACTION) | stop,
-                                             stream);
+                                             workspace, workspace_bytes, flags | FBFFT_CONV_STOP_AFTER_CONTRACTION, stream);
     if (rc) return rc;
     if (flags & (FBFFT_CONV_STOP_AFTER_CONTRACTION | FBFFT_CONV_STOP_AFTER_TRANSFORMS)) return kSuccess;
   } else {
@@ -380,12 +380,6 @@ int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int 
     const Tensor4 ti = make_tensor(in, in_size, in_stride), tw = make_tensor(grad_weight, w_size, w_stride),
                   to = make_tensor(grad_out, out_size, out_stride);
     if ((rc = check_common(fft_size, ti, tw, to, workspace, workspace_bytes))) return rc;
-    if (mode == FBFFT_DP_SPATIAL_ALLREDUCE) {
-      rc = fbfft_b200_conv_acc_grad_parameters(fft_size, in, in_size, in_stride, in_padL, in_padU, grad_weight, w_size,
-                                               w_stride, grad_out, out_size, out_stride, out_padL, out_padU, scale,
-                                               workspace, workspace_bytes, FBFFT_CONV_START_FROM_SPECTRUM, stream);
-      if (rc) return rc;
-    }
   }
   const int n = fft_size, B = in_size[0], C = in_size[1], O = out_size[1];
   const long long planes = (long long)O * C, X = bins_of(n);
@@ -393,16 +387,17 @@ int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int 
   const bool gw_dense = tw.stride[3] == 1 && tw.stride[2] == tw.size[3] && tw.stride[1] == tw.size[2] * tw.size[3] &&
                         tw.stride[0] == tw.size[1] * tw.stride[1];
   const size_t gw_count = (size_t)planes * tw.size[2] * tw.size[3];
+  const Regions r = regions(n, B, C, O);
+  float* res = static_cast<float*>(workspace) + r.res_off;
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0;
   if (mode == FBFFT_DP_SPATIAL_ALLREDUCE) {
     if (!gw_dense) {
       set_last_error("conv_acc_grad_parameters_dp: the spatial all-reduce needs a contiguous grad_weight");
       return kUnsupportedDimension;
     }
+    if ((rc = inverse(n, res, tw, 0, 0, blk, s))) return rc;
     return world > 1 ? comm_all_reduce(c, grad_weight, gw_count, s) : kSuccess;
   }
-  const Regions r = regions(n, B, C, O);
-  float* res = static_cast<float*>(workspace) + r.res_off;
-  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0;
   if (world == 1) return inverse(n, res, tw, 0, 0, blk, s);
   if (mode == FBFFT_DP_FREQUENCY_REDUCE_SCATTER && planes % world == 0 && gw_dense) {
     // Every rank receives the sum of 1/world of the planes, inverse-transforms and crops only those,

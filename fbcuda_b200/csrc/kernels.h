@@ -13,6 +13,10 @@ namespace fbfft_b200 {
 int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 
+// the same transforms with fp16 / bf16 storage of either tensor (FBFFT_STORAGE_*), contiguous tensors (fft2d_small16.cu)
+int fft2d_small_storage(int n, bool inverse, int src_type, int dst_type, const void* src, void* dst, int B, int h, int w,
+                        int padL, int padU, cudaStream_t s);
+
 // N in {64, 128, 256}: transposed [B][N/2+1 (kx)][N (ky)] layout (fft2d_large.cu)
 int fft2d_large_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
 int fft2d_large_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s);
@@ -104,6 +108,10 @@ int iterated_convolution(int fft_size, const fbfft_tiled_tensor4* ins, const fbf
 // value of the device-side error word (0 = none; set when a bounded wait inside a kernel ran out)
 int read_device_error();
 int clear_device_error();
+// tensor-pipe rate of tcgen05.mma.kind::tf32 (M = 128, N = n_cols, K = 8) from shared-memory operands (tf32_peak.cu)
+int measure_tf32_peak(int n_cols, double* tflops);
+int read_device_error_peak();
+int clear_device_error_peak();
 // one block waits `max_tries` attempts on a barrier that nothing completes, gives up, records
 // code 901 and returns; *elapsed_ns (host pointer) receives the time the wait took (fft2d_small.cu)
 int selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns);

@@ -50,7 +50,7 @@ const char* fbfft_b200_last_error(void);
  * kernel of this library has recorded a device-side error on the current device,
  * else the code it recorded (a bounded wait on an asynchronous copy that ran out:
  * 101 / 102 forward / inverse transform for N <= 32, 103 inverse transform for N = 64, 128, 201 / 202 and 211-216 tensor-core contraction,
- * 901 the self-test below), or -1 if the status cannot be read. */
+ * 901 the self-test below, 902 the tensor-peak measurement), or -1 if the status cannot be read. */
 int fbfft_b200_device_status(void);
 
 /* Resets the device-side error code of the current device to 0 (synchronises).  The code is
@@ -64,6 +64,13 @@ int fbfft_b200_clear_device_status(void);
  * and *elapsed_ns (a host pointer, may be NULL) receives the time the wait took on the device, so
  * that a caller can convert the kernels' limit into seconds.  Synchronises. */
 int fbfft_b200_selftest_bounded_wait(int max_tries, unsigned long long* elapsed_ns);
+
+/* Measurement hook (no counterpart in the reference): the rate, in TFLOP/s, at which this GPU's
+ * tensor cores run the MMA the contraction issues (tcgen05.mma kind::tf32, M = 128, N = n_cols in
+ * {64, 128, 256}, K = 8, operands in shared memory) when nothing else competes -- the tensor-peak
+ * denominator of the convolution roofline.  Creates two events, launches a few short kernels on
+ * the default stream and synchronises; *tflops is a host pointer. */
+int fbfft_b200_measure_tf32_peak(int n_cols, double* tflops);
 
 /* How fbfft_b200_transpose_mm and the convolution passes contract (process-wide; no
  * counterpart in the reference, whose transposeMM is FP32 CUDA-core code only):
@@ -134,6 +141,26 @@ int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const i
                          const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream);
 int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const int* cplx_stride, float* real,
                          const int* real_size, const int* real_stride, int padL, int padU, void* stream);
+
+/* fbfft2D / fbifft2D for N in {8, 16, 32} with the images, the spectra, or both stored as fp16 or
+ * bf16; the arithmetic stays fp32.  The reference leaves this open ("TODO: f16 implementation",
+ * fbfft/FFT2D32.cuh:385 and :451); layouts, padding rule and normalisation are those of the fp32
+ * transforms (fbfft/FFT2D32.cuh:361-470).  real_type / cplx_type are FBFFT_STORAGE_*; sizes and
+ * strides count elements of the storage type; tensors must be contiguous, the real tensor 4-byte
+ * and the complex tensor 16-byte aligned, the image no larger than the transform.
+ * Accuracy: a 16-bit result carries the rounding of its storage type on top of the fp32 error --
+ * against the float64 transform of the stored (already rounded) input the relative L2 error stays
+ * below 2^-11 + 1e-5 with fp16 results and 2^-8 + 1e-5 with bf16 results (half a unit in the last
+ * place of an 11- / 8-bit significand per element; about 1/sqrt(3) of that on average), and below
+ * 1e-5, as for fbfft_b200_fft2d_r2c, with fp32 results.  fp16 holds magnitudes up to 65504: the
+ * unnormalised spectrum of an N x N image of values in [-1, 1] is bounded by N*N <= 1024. */
+enum { FBFFT_STORAGE_F32 = 0, FBFFT_STORAGE_F16 = 1, FBFFT_STORAGE_BF16 = 2 };
+int fbfft_b200_fft2d_r2c_storage(int n, int real_type, int cplx_type, const void* real, const int* real_size,
+                                 const int* real_stride, void* cplx, const int* cplx_size, const int* cplx_stride, int padL,
+                                 int padU, void* stream);
+int fbfft_b200_fft2d_c2r_storage(int n, int cplx_type, int real_type, const void* cplx, const int* cplx_size,
+                                 const int* cplx_stride, void* real, const int* real_size, const int* real_stride, int padL,
+                                 int padU, void* stream);
 
 /* transposeMM<Dim, ConjugateTransposeA, ConjugateTransposeB, Accumulate>(A, B, C,
  * invNorm, s) -- MM.cuh:11-17, MM-inl.cuh:515-814.  A, B, C are float tensors of
@@ -251,6 +278,53 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
                                         const int* w_stride, const float* grad_out, const int* out_size,
                                         const int* out_stride, int out_padL, int out_padU, float scale,
                                         void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* ---- Whole layers: choice of the transform size and the loop over tiles ---------------------
+ * In the reference both were the caller's job: it chose the instantiation
+ * FFTIteratedConvolution<8|16|32> (fbfft/FFTIteratedConvolution.cuh:624-755) or chained the
+ * building blocks for larger transforms, and it built the tile lists (:70-95, 105-114, 431-442).
+ *
+ * fbfft_b200_conv_plan: for a stride-1 convolution of [batch][in_planes][in_h][in_w] with
+ * [out_planes][in_planes][kernel_h][kernel_w] and implicit zero padding (pad_h, pad_w), with the
+ * batch sharded over `world` GPUs, picks the transform size (the cheapest of 8..128 under a
+ * bytes + flops + per-tile cost model fitted to B200 measurements; est_us[i] is the estimate for
+ * size 8 << i, 0 where the kernel does not fit), and reports the number of overlap-save tiles,
+ * the outputs per tile, the contraction mode the passes will use (0 tensor cores, 1 FP32), the
+ * reduction mode for fbfft_b200_conv_acc_grad_parameters_dp and the workspace one GPU needs.
+ * Host arithmetic only. */
+typedef struct fbfft_b200_conv_plan_t {
+  int fft_size;
+  int tiles;
+  int tile_out_h, tile_out_w;
+  int contraction;
+  int dw_mode;
+  size_t workspace_bytes;
+  float est_us[5];
+} fbfft_b200_conv_plan_t;
+int fbfft_b200_conv_plan(int batch, int in_planes, int out_planes, int in_h, int in_w, int kernel_h, int kernel_w,
+                         int pad_h, int pad_w, int world, fbfft_b200_conv_plan_t* plan);
+
+/* The three passes on whole images of any size: the library walks the overlap-save tiles of
+ * fbfft_b200_plan_tiles itself (the tile loops of fbfft/FFTIteratedConvolution.cuh:105-114 and
+ * :431-442), the weight spectrum is computed once per call (never, with
+ * FBFFT_CONV_REUSE_WEIGHT_SPECTRUM in `flags`), and the weight gradient is summed over the tiles in
+ * the frequency domain with a single inverse transform at the end.  in [B][C][H][W],
+ * out [B][O][H + 2 pad_h - kh + 1][W + 2 pad_w - kw + 1]; the workspace is the one of a single tile
+ * (fbfft_b200_conv_workspace_bytes).  Nothing synchronises and nothing is allocated on the device,
+ * so a call can be captured into a CUDA graph like the single-tile passes. */
+int fbfft_b200_conv_tiled_update_output(int fft_size, const float* in, const int* in_size, const int* in_stride,
+                                        const float* weight, const int* w_size, const int* w_stride, float* out,
+                                        const int* out_size, const int* out_stride, int pad_h, int pad_w,
+                                        void* workspace, size_t workspace_bytes, int flags, void* stream);
+int fbfft_b200_conv_tiled_update_grad_input(int fft_size, float* grad_in, const int* in_size, const int* in_stride,
+                                            const float* weight, const int* w_size, const int* w_stride,
+                                            const float* grad_out, const int* out_size, const int* out_stride, int pad_h,
+                                            int pad_w, void* workspace, size_t workspace_bytes, int flags, void* stream);
+int fbfft_b200_conv_tiled_acc_grad_parameters(int fft_size, const float* in, const int* in_size, const int* in_stride,
+                                              float* grad_weight, const int* w_size, const int* w_stride,
+                                              const float* grad_out, const int* out_size, const int* out_stride,
+                                              int pad_h, int pad_w, float scale, void* workspace, size_t workspace_bytes,
+                                              int flags, void* stream);
 
 /* ---- Data-parallel accGradParameters (no counterpart in the reference, which has no
  * multi-GPU code; what is summed is its accGradParameters,

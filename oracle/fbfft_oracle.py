@@ -305,6 +305,15 @@ def _rfft2_canvas(x: np.ndarray, n: int, off: int = 0) -> np.ndarray:
     return np.fft.rfft2(c, axes=(-2, -1))
 
 
+def _per_bin_matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """[i][k][y][x], [k][j][y][x] -> [i][j][y][x]: sum over k at every bin, as one batched matrix
+    product (same sums as the einsum it replaces, orders of magnitude faster at the full shapes)."""
+    y, x = a.shape[-2:]
+    am = np.ascontiguousarray(a.reshape(a.shape[0], a.shape[1], y * x).transpose(2, 0, 1))
+    bm = np.ascontiguousarray(b.reshape(b.shape[0], b.shape[1], y * x).transpose(2, 0, 1))
+    return np.matmul(am, bm).transpose(1, 2, 0).reshape(a.shape[0], b.shape[1], y, x)
+
+
 def fftconv_update_output(inp, weight, n: int, pad: int = 0) -> np.ndarray:
     inp = np.asarray(inp, dtype=np.float64)
     weight = np.asarray(weight, dtype=np.float64)
@@ -313,7 +322,7 @@ def fftconv_update_output(inp, weight, n: int, pad: int = 0) -> np.ndarray:
     oh, ow = h + 2 * pad - kh + 1, w + 2 * pad - kw + 1
     fi = _rfft2_canvas(inp, n, pad)
     fw = _rfft2_canvas(weight, n)
-    fo = np.einsum("bcyx,ocyx->boyx", fi, np.conj(fw), optimize=True)
+    fo = _per_bin_matmul(fi, np.conj(fw).transpose(1, 0, 2, 3))     # sum_c fi[b][c] conj(fw[o][c])
     return np.fft.irfft2(fo, s=(n, n), axes=(-2, -1))[..., :oh, :ow]
 
 
@@ -322,7 +331,7 @@ def fftconv_update_grad_input(grad_out, weight, n: int, h: int, w: int, pad: int
     weight = np.asarray(weight, dtype=np.float64)
     fo = _rfft2_canvas(go, n)
     fw = _rfft2_canvas(weight, n)
-    fi = np.einsum("boyx,ocyx->bcyx", fo, fw, optimize=True)
+    fi = _per_bin_matmul(fo, fw)                                      # sum_o fo[b][o] fw[o][c]
     return np.fft.irfft2(fi, s=(n, n), axes=(-2, -1))[..., pad:pad + h, pad:pad + w]
 
 
@@ -331,8 +340,22 @@ def fftconv_acc_grad_parameters(inp, grad_out, n: int, kh: int, kw: int, pad: in
     go = np.asarray(grad_out, dtype=np.float64)
     fi = _rfft2_canvas(inp, n, pad)
     fo = _rfft2_canvas(go, n)
-    fw = np.einsum("bcyx,boyx->ocyx", fi, np.conj(fo), optimize=True)
+    fw = _per_bin_matmul(np.conj(fo).transpose(1, 0, 2, 3), fi)       # sum_b conj(fo[b][o]) fi[b][c]
     return scale * np.fft.irfft2(fw, s=(n, n), axes=(-2, -1))[..., :kh, :kw]
+
+
+def fftconv_acc_grad_parameters_planes(inp, grad_out, n: int, kh: int, kw: int, pairs, pad: int = 0,
+                                       scale: float = 1.0) -> np.ndarray:
+    """The same weight gradient for a list of (o, c) plane pairs only -> [len(pairs)][kh][kw]
+    (a spot check over the full batch where the whole gradient is not needed)."""
+    inp = np.asarray(inp)
+    go = np.asarray(grad_out)
+    res = np.zeros((len(pairs), kh, kw))
+    for i, (o, c) in enumerate(pairs):
+        fi = _rfft2_canvas(np.asarray(inp[:, c], dtype=np.float64), n, pad)
+        fo = _rfft2_canvas(np.asarray(go[:, o], dtype=np.float64), n)
+        res[i] = scale * np.fft.irfft2((fi * np.conj(fo)).sum(0), s=(n, n))[:kh, :kw]
+    return res
 
 
 # --------------------------------------------------------------------------

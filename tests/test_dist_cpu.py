@@ -99,8 +99,7 @@ def _worker_reduce_scatter(rank, world, port, out_dir, batch):
     plo, pcnt = fb.dp_shard(planes, world, rank)                               # a reduce-scatter would deliver
     mine = (t[..., 0].numpy() + 1j * t[..., 1].numpy())[:, plo:plo + pcnt, :].transpose(1, 0, 2)
     # Hermitian completion along ky and inverse, cropped to the kernel support
-    gw_mine = np.fft.irfft2(np.swapaxes(mine, -1, -2), s=(n, n), axes=(-1, -2))[..., :k, :k] if False else \
-        np.fft.ifft2(_hermitian_rows(mine, n), axes=(-2, -1)).real[..., :k, :k]
+    gw_mine = np.fft.ifft2(_hermitian_rows(mine, n), axes=(-2, -1)).real[..., :k, :k]
     pieces = [torch.zeros((pcnt, k, k), dtype=torch.float64) for _ in range(world)]
     dist.all_gather(pieces, torch.from_numpy(gw_mine.copy()))
     gw = torch.cat(pieces).numpy().reshape(o, c, k, k)

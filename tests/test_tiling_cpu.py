@@ -66,3 +66,18 @@ def test_plan_rejects_bad_arguments():
         fb.plan_tiles_layout(16, (1, 1, 20, 20), (1, 1, 17, 18), (3, 3))      # output size does not match
     with pytest.raises(fb.FbfftError):
         fb.plan_tiles_layout(16, (1, 1, 20, 20), (1, 1, 18, 18), (3, 3), style=2)
+
+
+def test_conv_plan_picks_sizes_that_hold_the_kernel_and_rank_like_the_measurements():
+    # shapes whose fastest transform size was measured on a B200 (ms for N = 32 / 64 / 128)
+    assert fb.conv_plan(32, 64, 64, 112, 112, 3, 3, 1, 1)["fft_size"] == 128      # 0.67 / 0.53 / 0.45
+    assert fb.conv_plan(32, 128, 128, 56, 56, 3, 3, 1, 1)["fft_size"] == 64       # 0.31 / 0.29 / 1.05
+    assert fb.conv_plan(16, 64, 64, 224, 224, 3, 3, 1, 1)["fft_size"] == 128      # 2.38 / 1.51 / 1.33
+    p = fb.conv_plan(32, 96, 96, 128, 128, 13, 13, 0, 0)
+    assert p["fft_size"] == 128 and p["tiles"] == 1 and p["tile_out"] == (116, 116) and p["est_us"][8] == 0.0
+    p = fb.conv_plan(64, 128, 128, 56, 56, 3, 3, 1, 1, world=8)
+    assert p["dw_mode"] == 1 and p["workspace_bytes"] == fb.conv_workspace_bytes(64, 8, 128, 128)
+    assert fb.conv_plan(8, 3, 5, 30, 30, 3, 3, 0, 0, world=2)["dw_mode"] == 0     # 15 planes do not split over 2 ranks
+    assert fb.conv_plan(8, 3, 5, 30, 30, 3, 3)["contraction"] == 1                # too few planes for 128-row tiles
+    with pytest.raises(fb.FbfftError):
+        fb.conv_plan(8, 3, 5, 4, 4, 7, 7)                                         # kernel larger than the image

@@ -3,7 +3,8 @@ ctypes, must give what the workspace-taking entry point gives.  It exists for
 callers that cannot allocate device memory at call time (allocator lock held by
 the host framework, no-allocation rule after start-up, memory pool exhausted);
 its spectra live in a fixed scratch area inside the library.  Two calls in a row
-check that nothing left in that shared scratch by one call disturbs the next.
+check that nothing left in that shared scratch by one call disturbs the next; the
+result is also compared with the float64 direct convolution.
 Collected last on purpose (file name), and self-contained so that it also passes
 alone in a fresh process."""
 import ctypes
@@ -13,7 +14,8 @@ import pytest
 import torch
 
 import fbcuda_b200 as fb
-from fbcuda_b200 import api
+from fbcuda_b200 import api  # noqa: F401
+from oracle import fbfft_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -53,7 +55,12 @@ def test_noalloc_matches_workspace_entry_point_twice(n, b, c, o, hw, k, pad):
         got = torch.full((b, o, oh, oh), 7.0, device="cuda")
         assert _call_noalloc(n, x, w, got, pad) == 0, fb.last_error()
         torch.cuda.synchronize()
-        assert _rel_l2(got, want) < CONV_TOL, (n, call)
+        # the same kernels on the same data: the two entry points must agree bit for bit
+        assert torch.equal(got, want), (n, call, _rel_l2(got, want))
+        # and both must be right: float64 direct convolution
+        ref = orc.conv_update_output(x.cpu().numpy(), w.cpu().numpy(), pad)
+        assert orc.rel_l2(got.cpu().numpy(), ref) < CONV_TOL, (n, call)
+        assert fb.device_status() == 0
 
 
 def test_noalloc_rejects_layers_beyond_the_scratch():
