@@ -222,8 +222,7 @@ def dist_setup(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # keep stdout to the one JSON line unless the caller asked NCCL for more
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
+        # NCCL_DEBUG is left as the caller set it (unset: NCCL prints nothing and stdout is the one JSON line)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 

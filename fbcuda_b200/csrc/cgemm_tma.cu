@@ -26,8 +26,9 @@
 //                 [-s Bi | Br] (the Ai products negated when A is conjugated); tcgen05.commit frees
 //                 the half stage and, after the last k-step, hands the accumulators to the epilogue;
 //   warps 13-16   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
-//                 interleave the 4 bins' re/im into 32 bytes per (m, n) in a 4 KB staging buffer and
-//                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
+//                 interleave the 4 bins' re/im into the 32 bytes of an (m, n) element and store them
+//                 straight from registers (one sector per element); when accumulating, the 32-byte
+//                 pieces go through a 4 KB staging buffer and one reduce-add tensor store per 4 columns.
 // What bounds it: shared-memory bandwidth.  Per half stage the MMAs read 96 KB of operand tiles,
 // the split writes 56 KB and reads 24 KB, the copies write 24 KB -- about 200 KB at 128 B/clock;
 // measured alone, the MMAs run at the tf32 peak and the split at 70 % of the shared-memory rate,
@@ -161,6 +162,8 @@ struct TmaArgs {
   const float2* B;
   long long b_rs, b_ks, b_bs;  // B[n][k][x]
   int a_qb, b_qb;
+  float* D;                    // result: bin x of (m, n) at D + 2 * ((x/d_qb)*d_bs + x%d_qb + m*d_ms + n*d_ns) floats
+  long long d_ms, d_ns, d_bs;  // (d_qb == 0: bins innermost, D + 2 * (x + m*d_ms + n*d_ns))
   int M, N, K, X;
   int d_qb;  // bins per block of D; 0 = bins innermost (store coordinates (2x, m, n, 0) instead of (2*(x % d_qb), m, n, x / d_qb))
   float inv_norm;
@@ -168,7 +171,7 @@ struct TmaArgs {
   int n_tiles, m_tiles, total_tiles;
 };
 
-template <int BN>
+template <int BN, bool ACCUM>
 __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_d, TmaArgs g) {
   using C = Cfg<BN>;
   constexpr int NR = C::NR, NH = C::NH, NACC = C::NACC;
@@ -373,16 +376,44 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (g.accumulate) {
-            tma_reduce_add4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
-          } else {
-            tma_store4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
-          }
+          tma_reduce_add4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
           bulk_commit();
+        }
+      };
+      // Overwriting results leave straight from registers: the four bins of an (m, n) element are 32
+      // contiguous bytes (one sector), written by the lane that holds row m; nothing waits for a
+      // staging buffer.  Accumulating results keep the staged reduce-add tensor stores.
+      float* drow = g.D + 2 * ((long long)db * g.d_bs + (g.d_qb ? x0 % g.d_qb : x0) + (long long)(mrow + lane) * g.d_ms);
+      const bool row_ok = mrow + lane < g.M;
+      auto emit_direct = [&](const float (&v)[XB][2][4], int c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int n = n0 + c * 4 + j;
+          if (row_ok && n < g.N) {
+            float4* dst = reinterpret_cast<float4*>(drow + 2 * (long long)n * g.d_ns);
+            dst[0] = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
+                                 v[1][1][j] * g.inv_norm);
+            dst[1] = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
+                                 v[3][1][j] * g.inv_norm);
+          }
         }
       };
       if (nch == 0) {
         release();
+      } else if constexpr (!ACCUM) {
+        float va[XB][2][4], vb[XB][2][4];
+        load_chunk(0, va);
+#pragma unroll 1
+        for (int c = 0; c < nch; c += 2) {
+          tmem_ld_wait();
+          if (c + 1 < nch) load_chunk(c + 1, vb); else release();
+          emit_direct(va, c);
+          if (c + 1 < nch) {
+            tmem_ld_wait();
+            if (c + 2 < nch) load_chunk(c + 2, va); else release();
+            emit_direct(vb, c + 1);
+          }
+        }
       } else {
         // two register sets: the accumulator reads of the next chunk fly while this one is stored
         float va[XB][2][4], vb[XB][2][4];
@@ -530,7 +561,8 @@ int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(cgemm_tma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+    cudaFuncSetAttribute(cgemm_tma_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+    cudaFuncSetAttribute(cgemm_tma_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
     configured[dev] = true;
   }
   a.n_tiles = (a.N + BN - 1) / BN;
@@ -538,7 +570,11 @@ int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
   const long long total = (long long)a.n_tiles * a.m_tiles * (a.X / XB);
   a.total_tiles = (int)total;
   const int grid = total < sm_count() ? (int)total : sm_count();
-  cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
+  if (a.accumulate) {
+    cgemm_tma_kernel<BN, true><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
+  } else {
+    cgemm_tma_kernel<BN, false><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
+  }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
@@ -573,6 +609,7 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.a_qb = a_qb, t.b_qb = b_qb;
   t.d_qb = (d_bs != d_qb) ? d_qb : 0;
+  t.D = d, t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
   if (BN == 16) return launch_tma<16>(md, t, s);
