@@ -396,11 +396,10 @@ def run_extras(args, x, spec, n0, hw0):
         ms_f = time_steps(lambda: fb.fft2d_r2c(n, x, spec), 10, 3, 1)
         entry = {"fwd_us": ms_f * 1e3, "fwd_gbs": b * fft_bytes_per_image(n, n, n) / ms_f / 1e6}
         entry["fwd_frac_of_measured"] = entry["fwd_gbs"] / peak
-        if n <= 128:
-            ms_i = time_steps(lambda: fb.fft2d_c2r(n, spec, back), 10, 3, 1)
-            entry["inv_us"] = ms_i * 1e3
-            entry["inv_gbs"] = b * fft_bytes_per_image(n, n, n) / ms_i / 1e6
-            entry["inv_frac_of_measured"] = entry["inv_gbs"] / peak
+        ms_i = time_steps(lambda: fb.fft2d_c2r(n, spec, back), 10, 3, 1)
+        entry["inv_us"] = ms_i * 1e3
+        entry["inv_gbs"] = b * fft_bytes_per_image(n, n, n) / ms_i / 1e6
+        entry["inv_frac_of_measured"] = entry["inv_gbs"] / peak
         sweep[str(n)] = entry
         del x, spec, back
         torch.cuda.empty_cache()
@@ -438,8 +437,31 @@ def run_extras(args, x, spec, n0, hw0):
         two_call[str(n)] = entry
         del x, buf, spec, mid, back
         torch.cuda.empty_cache()
+    # the 1-D configuration as stated: 4096 signals of length 32, forward and inverse (launch-latency bound)
+    x = torch.rand((4096, 32), device="cuda") * 2 - 1
+    spec = torch.empty((4096, 17, 2), device="cuda")
+    back = torch.empty_like(x)
+    config1 = {"workload": "fbfft1D / fbifft1D, 4096 signals of length 32",
+               "fwd_us": time_steps(lambda: fb.fbfft1D(x, spec), 50, 5, 1) * 1e3,
+               "inv_us": time_steps(lambda: fb.fbifft1D(back, spec), 50, 5, 1) * 1e3}
+    del x, spec, back
+    # 16-bit storage of images and spectra (fp32 arithmetic): the default workload's shape, GB/s on the halved bytes
+    storage = {}
+    b16 = GIB // (4 * hw0 * hw0)
+    for name, dt in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+        x = (torch.rand((b16, hw0, hw0), device="cuda") * 2 - 1).to(dt)
+        spec = torch.empty((b16, n0 // 2 + 1, n0, 2), device="cuda", dtype=dt)
+        back = torch.empty_like(x)
+        byts = b16 * fft_bytes_per_image(n0, hw0, hw0) / 2
+        ms_f = time_steps(lambda: fb.fft2d_r2c_storage(n0, x, spec), 10, 3, 1)
+        ms_b = time_steps(lambda: fb.fft2d_c2r_storage(n0, spec, back), 10, 3, 1)
+        storage[name] = {"images": b16, "fwd_us": ms_f * 1e3, "fwd_gbs": byts / ms_f / 1e6, "fwd_frac_of_measured": byts / ms_f / 1e6 / peak,
+                         "inv_us": ms_b * 1e3, "inv_gbs": byts / ms_b / 1e6, "inv_frac_of_measured": byts / ms_b / 1e6 / peak}
+        del x, spec, back
+        torch.cuda.empty_cache()
     return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d,
-            "two_call_protocol_512MiB": two_call}
+            "two_call_protocol_512MiB": two_call, "config1_1d_4096x32": config1,
+            f"storage_16bit_N{n0}_{hw0}x{hw0}": storage}
 
 
 CONV_CONFIGS = {

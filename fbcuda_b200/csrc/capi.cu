@@ -158,10 +158,6 @@ int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const i
   if (B == 0) return kSuccess;
   if (check_ptrs(real, cplx)) return kUnsupportedDimension;
   if (!small_size(n) && !large_size(n)) return fail(kUnsupportedSize, "fft2d_c2r: N must be 8, 16, 32, 64, 128 or 256");
-  if (n == 256)
-    return fail(kUnsupportedSize,
-                "fft2d_c2r: the single-call inverse covers N = 8..128; for N = 256 use the two-call protocol "
-                "(fbifft2d_c2c into a caller-owned [B][N][N][2] buffer, then fbifft2d)");
   if (cplx_size[0] != B || cplx_size[1] != n / 2 + 1 || cplx_size[2] != n || cplx_size[3] != 2)
     return fail(kUnsupportedDimension, "fft2d_c2r: complex tensor must be [B][N/2+1][N][2]");
   if (padL < 0 || padU < 0) return fail(kUnsupportedDimension, "fft2d_c2r: negative padding");

@@ -26,9 +26,8 @@
 //                 [-s Bi | Br] (the Ai products negated when A is conjugated); tcgen05.commit frees
 //                 the half stage and, after the last k-step, hands the accumulators to the epilogue;
 //   warps 13-16   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
-//                 interleave the 4 bins' re/im into the 32 bytes of an (m, n) element and store them
-//                 straight from registers (one sector per element); when accumulating, the 32-byte
-//                 pieces go through a 4 KB staging buffer and one reduce-add tensor store per 4 columns.
+//                 interleave the 4 bins' re/im into 32 bytes per (m, n) in a 4 KB staging buffer and
+//                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
 // What bounds it: shared-memory bandwidth.  Per half stage the MMAs read 96 KB of operand tiles,
 // the split writes 56 KB and reads 24 KB, the copies write 24 KB -- about 200 KB at 128 B/clock;
 // measured alone, the MMAs run at the tf32 peak and the split at 70 % of the shared-memory rate,
@@ -36,6 +35,8 @@
 // Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
 // block still releases its tensor memory before returning.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
+
+#include <cstring>
 
 #include "fft2d_small.cuh"  // mbarrier helpers, fence_async_smem
 #include "kernels.h"
@@ -62,6 +63,8 @@ struct Cfg {
   // copies issued k-fastest do not all land in the same banks
   static constexpr int A_KSTRIDE = BM * 32 + 32, B_KSTRIDE = BN * 32 + 32;
   static constexpr int A_RAW = KQ * A_KSTRIDE, B_RAW = KQ * B_KSTRIDE, RAW = A_RAW + B_RAW;
+  // tensor copies write dense boxes: k slices BM*32 / BN*32 bytes apart, B behind the 16 KB of A
+  static constexpr int A_RAW_T = KQ * BM * 32;
   static constexpr int A_TILE = BM * KS * 4;         // one (bin, part, split) tile of A
   static constexpr int B_TILE = 3 * BN * KS * 4;     // one (bin, split) stack of B
   static constexpr int HALF_A = 2 * 2 * 2 * A_TILE, HALF_B = 2 * 2 * B_TILE, HSTAGE = HALF_A + HALF_B;
@@ -108,6 +111,12 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 }
 __device__ __forceinline__ void cp_async16(unsigned dst, const void* src, unsigned src_bytes) {
   asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load4(unsigned dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ void tma_store4(const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned src) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm), "r"(c0),
@@ -162,20 +171,20 @@ struct TmaArgs {
   const float2* B;
   long long b_rs, b_ks, b_bs;  // B[n][k][x]
   int a_qb, b_qb;
-  float* D;                    // result: bin x of (m, n) at D + 2 * ((x/d_qb)*d_bs + x%d_qb + m*d_ms + n*d_ns) floats
-  long long d_ms, d_ns, d_bs;  // (d_qb == 0: bins innermost, D + 2 * (x + m*d_ms + n*d_ns))
   int M, N, K, X;
   int d_qb;  // bins per block of D; 0 = bins innermost (store coordinates (2x, m, n, 0) instead of (2*(x % d_qb), m, n, x / d_qb))
   float inv_norm;
   int conjA, conjB, accumulate;
   int n_tiles, m_tiles, total_tiles;
+  int use_tma;  // operands arrive by tensor copies (the convolution workspace) instead of 16-byte cp.async copies
 };
 
-template <int BN, bool ACCUM>
-__global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_d, TmaArgs g) {
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_constant__ CUtensorMap map_d, const __grid_constant__ CUtensorMap map_a,
+                                                                const __grid_constant__ CUtensorMap map_b, TmaArgs g) {
   using C = Cfg<BN>;
   constexpr int NR = C::NR, NH = C::NH, NACC = C::NACC;
-  extern __shared__ __align__(128) unsigned char smem_raw[];
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* raw_mem = smem_raw;
   unsigned char* conv_mem = smem_raw + C::OFF_CONV;
   unsigned char* epi_mem = smem_raw + C::OFF_EPI;
@@ -191,7 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
   if (tid == 0) {
     *abort_word = 0;
     for (int i = 0; i < NR; ++i) {
-      mbar_init(bar(RAW_FULL + i), kProdThreads);
+      mbar_init(bar(RAW_FULL + i), g.use_tma ? 1 : kProdThreads);
       mbar_init(bar(RAW_FREE + i), kConvThreads / 32);
     }
     for (int i = 0; i < NH; ++i) {
@@ -234,6 +243,32 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
     // the stage's barrier count their completion.  Consecutive segments of a warp follow the
     // direction in which the operand is contiguous (rows or k), so that a warp's copies coalesce
     // into whole 128-byte lines when the layout allows it.
+    if (g.use_tma) {
+      // One thread, two tensor copies per raw stage: box {32 bytes, rows, 4 values of k} of each operand,
+      // zero-filled outside the tensor, written as [k][row][32 B] with the 32-byte swizzle (the two
+      // 16-byte halves of a row swap places every 4 rows: the split's reads stay free of bank conflicts).
+      // Tensor copies have no per-SM cap on requests in flight; the 16-byte cp.async path below levels
+      // off near 32 KB in flight per SM, which is about half of what the HBM latency needs.
+      if (tid == kWarpProd * 32) {
+        unsigned rs = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < g.total_tiles && ok; t += gridDim.x) {
+          int n0, m0, x0;
+          tile_coords(t, &n0, &m0, &x0);
+          for (int q = 0; q < 2 * nsteps; ++q, ++rs) {
+            const unsigned st = rs % NR;
+            if (rs >= NR && !wait_bar(bar(RAW_FREE + st), ((rs / NR) - 1) & 1, kErrRawFree, abort_word)) {
+              ok = false;
+              break;
+            }
+            const unsigned dst = smem_u32(raw_mem + st * C::RAW);
+            mbar_expect_tx(bar(RAW_FULL + st), (unsigned)((BM + BN) * KQ * 32));
+            tma_load4(dst, &map_a, 2 * (x0 % g.a_qb), m0, q * KQ, x0 / g.a_qb, bar(RAW_FULL + st));
+            tma_load4(dst + C::A_RAW_T, &map_b, 2 * (x0 % g.b_qb), n0, q * KQ, x0 / g.b_qb, bar(RAW_FULL + st));
+          }
+        }
+      }
+    } else {
     const int p = tid - kWarpProd * 32, half = p & 1, sp = p >> 1;  // sp in 0..63
     // unit u = i*64 + sp of an operand with R rows: k-fastest (row = u / 4, j = u % 4) or row-fastest
     const bool a_kfast = g.a_ks < g.a_rs, b_kfast = g.b_ks < g.b_rs;
@@ -274,6 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
         // the barrier receives this thread's arrival once all its copies above have landed
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(RAW_FULL + st)) : "memory");
       }
+    }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
@@ -376,44 +412,16 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_reduce_add4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
-          bulk_commit();
-        }
-      };
-      // Overwriting results leave straight from registers: the four bins of an (m, n) element are 32
-      // contiguous bytes (one sector), written by the lane that holds row m; nothing waits for a
-      // staging buffer.  Accumulating results keep the staged reduce-add tensor stores.
-      float* drow = g.D + 2 * ((long long)db * g.d_bs + (g.d_qb ? x0 % g.d_qb : x0) + (long long)(mrow + lane) * g.d_ms);
-      const bool row_ok = mrow + lane < g.M;
-      auto emit_direct = [&](const float (&v)[XB][2][4], int c) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int n = n0 + c * 4 + j;
-          if (row_ok && n < g.N) {
-            float4* dst = reinterpret_cast<float4*>(drow + 2 * (long long)n * g.d_ns);
-            dst[0] = make_float4(v[0][0][j] * g.inv_norm, v[0][1][j] * g.inv_norm, v[1][0][j] * g.inv_norm,
-                                 v[1][1][j] * g.inv_norm);
-            dst[1] = make_float4(v[2][0][j] * g.inv_norm, v[2][1][j] * g.inv_norm, v[3][0][j] * g.inv_norm,
-                                 v[3][1][j] * g.inv_norm);
+          if (g.accumulate) {
+            tma_reduce_add4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
+          } else {
+            tma_store4(&map_d, dx, mrow, n0 + c * 4, db, stag_u32);
           }
+          bulk_commit();
         }
       };
       if (nch == 0) {
         release();
-      } else if constexpr (!ACCUM) {
-        float va[XB][2][4], vb[XB][2][4];
-        load_chunk(0, va);
-#pragma unroll 1
-        for (int c = 0; c < nch; c += 2) {
-          tmem_ld_wait();
-          if (c + 1 < nch) load_chunk(c + 1, vb); else release();
-          emit_direct(va, c);
-          if (c + 1 < nch) {
-            tmem_ld_wait();
-            if (c + 2 < nch) load_chunk(c + 2, va); else release();
-            emit_direct(vb, c + 1);
-          }
-        }
       } else {
         // two register sets: the accumulator reads of the next chunk fly while this one is stored
         float va[XB][2][4], vb[XB][2][4];
@@ -454,7 +462,27 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           break;
         }
         const unsigned char* ra = raw_mem + (a_kq ? st1 : st0) * C::RAW;
-        const unsigned char* rb = raw_mem + (b_kq ? st1 : st0) * C::RAW + C::A_RAW;
+        const unsigned char* rb = raw_mem + (b_kq ? st1 : st0) * C::RAW + (g.use_tma ? C::A_RAW_T : C::A_RAW);
+        const int a_kst = g.use_tma ? BM * 32 : C::A_KSTRIDE, b_kst = g.use_tma ? BN * 32 : C::B_KSTRIDE;
+        // Everything this thread needs of the two raw stages goes to registers first and the stages are
+        // handed back at once: the copies of the k-step after next start while this one is still being
+        // split, instead of after it (FFT-128 layer: 335 -> 308 us per contraction).
+        float4 va[2][4];  // [pair][j]: k = 4*a_kq + j, (bin0.re, bin0.im, bin1.re, bin1.im) of the pair
+        float2 vb[2][4];  // [pair][j]: (re, im) of bin 2*pair + b_sel
+#pragma unroll
+        for (int pair = 0; pair < 2; ++pair) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            va[pair][j] = *reinterpret_cast<const float4*>(ra + j * a_kst + a_row * 32 + ((pair ^ ((a_row >> 2) & 1)) << 4));
+            vb[pair][j] = has_b ? *reinterpret_cast<const float2*>(rb + j * b_kst + b_row * 32 + ((pair ^ ((b_row >> 2) & 1)) << 4) + b_sel * 8)
+                                : make_float2(0.f, 0.f);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(RAW_FREE + st0));
+          mbar_arrive(bar(RAW_FREE + st1));
+        }
 #pragma unroll
         for (int pair = 0; pair < 2; ++pair, ++h) {
           const unsigned buf = h % NH;
@@ -465,9 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           }
           unsigned char* cst = conv_mem + buf * C::HSTAGE;
           {
-            float4 v[4];  // k = 4*a_kq + j: (bin0.re, bin0.im, bin1.re, bin1.im) of this pair
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4*>(ra + j * C::A_KSTRIDE + a_row * 32 + ((pair ^ ((a_row >> 2) & 1)) << 4));
+            const float4(&v)[4] = va[pair];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {  // c = binl*2 + part
               const float w[4] = {c == 0 ? v[0].x : c == 1 ? v[0].y : c == 2 ? v[0].z : v[0].w,
@@ -482,10 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
             }
           }
           if (has_b) {
-            float2 v[4];  // (re, im) of bin 2*pair + b_sel
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              v[j] = *reinterpret_cast<const float2*>(rb + j * C::B_KSTRIDE + b_row * 32 + ((pair ^ ((b_row >> 2) & 1)) << 4) + b_sel * 8);
+            const float2(&v)[4] = vb[pair];
             const float wr[4] = {v[0].x, v[1].x, v[2].x, v[3].x}, wi[4] = {v[0].y, v[1].y, v[2].y, v[3].y};
             float4 brh, brl, bih, bil;
             split4(wr, &brh, &brl);
@@ -503,12 +526,6 @@ __global__ void __launch_bounds__(kThreads, 1) cgemm_tma_kernel(const __grid_con
           fence_async_smem();  // generic-proxy writes -> visible to the tensor core
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(CV_FULL + buf));
-        }
-        // both raw stages of this k-step are consumed by this warp
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar(RAW_FREE + st0));
-          mbar_arrive(bar(RAW_FREE + st1));
         }
       }
     }
@@ -541,7 +558,7 @@ EncodeTiledFn encoder() {
 // complex elements: (floats of a block's bins, rows, k, blocks).  bs == qb is the natural
 // bins-innermost layout, seen as one "block" holding all X bins.
 bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long long bs, int qb, int rows, int kcount,
-              int X, int box_rows, int box_k) {
+              int X, int box_rows, int box_k, bool swizzle32 = false) {
   EncodeTiledFn enc = encoder();
   if (!enc) return false;
   const bool blocked = bs != qb;
@@ -551,18 +568,17 @@ bool make_map(CUtensorMap* m, const float* p, long long rs, long long ks, long l
   const cuuint32_t box[4] = {8, (cuuint32_t)box_rows, (cuuint32_t)box_k, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(p), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN>
-int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
+int launch_tma(const CUtensorMap& md, const CUtensorMap& ma, const CUtensorMap& mb, TmaArgs a, cudaStream_t s) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(cgemm_tma_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
-    cudaFuncSetAttribute(cgemm_tma_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+    cudaFuncSetAttribute(cgemm_tma_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
     configured[dev] = true;
   }
   a.n_tiles = (a.N + BN - 1) / BN;
@@ -570,15 +586,26 @@ int launch_tma(const CUtensorMap& md, TmaArgs a, cudaStream_t s) {
   const long long total = (long long)a.n_tiles * a.m_tiles * (a.X / XB);
   a.total_tiles = (int)total;
   const int grid = total < sm_count() ? (int)total : sm_count();
-  if (a.accumulate) {
-    cgemm_tma_kernel<BN, true><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
-  } else {
-    cgemm_tma_kernel<BN, false><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, a);
-  }
+  cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, ma, mb, a);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
 }  // namespace
+
+// fp32 tensor map without swizzle or interleave, zero fill outside the tensor (shared with the
+// transforms that stage zero-padded images by tensor copies); false when the driver lacks the encoder
+bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigned long long* dims,
+                           const unsigned long long* strides_bytes, const unsigned* box) {
+  EncodeTiledFn enc = encoder();
+  if (!enc || rank < 1 || rank > 5) return false;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) d[i] = dims[i], bx[i] = box[i], es[i] = 1;
+  for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
+  return enc(static_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), d, st,
+             bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,
                          long long b_ks, long long b_bs, const float* d, long long d_ms, long long d_ns, long long d_bs,
@@ -609,13 +636,22 @@ int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const 
   t.M = M, t.N = N, t.K = K, t.X = X, t.inv_norm = inv_norm;
   t.a_qb = a_qb, t.b_qb = b_qb;
   t.d_qb = (d_bs != d_qb) ? d_qb : 0;
-  t.D = d, t.d_ms = d_ms, t.d_ns = d_ns, t.d_bs = d_bs;
   t.conjA = conjA, t.conjB = conjB, t.accumulate = accumulate;
   t.n_tiles = t.m_tiles = t.total_tiles = 0;
-  if (BN == 16) return launch_tma<16>(md, t, s);
-  if (BN == 32) return launch_tma<32>(md, t, s);
-  if (BN == 48) return launch_tma<48>(md, t, s);
-  return launch_tma<64>(md, t, s);
+  // operands in 4-bin blocks (the convolution workspace) arrive by tensor copies
+  alignas(64) CUtensorMap ma, mb;
+  std::memset(&ma, 0, sizeof(ma));
+  std::memset(&mb, 0, sizeof(mb));
+#ifndef FBFFT_OPERAND_TMA
+#define FBFFT_OPERAND_TMA 1
+#endif
+  t.use_tma = FBFFT_OPERAND_TMA && a_qb == XB && b_qb == XB && a_bs != a_qb && b_bs != b_qb &&
+              make_map(&ma, a, a_rs, a_ks, a_bs, a_qb, M, K, X, BM, KQ, true) &&
+              make_map(&mb, b, b_rs, b_ks, b_bs, b_qb, N, K, X, BN, KQ, true);
+  if (BN == 16) return launch_tma<16>(md, ma, mb, t, s);
+  if (BN == 32) return launch_tma<32>(md, ma, mb, t, s);
+  if (BN == 48) return launch_tma<48>(md, ma, mb, t, s);
+  return launch_tma<64>(md, ma, mb, t, s);
 }
 
 int read_device_error_tma() { return device_error_word_read(); }

@@ -20,6 +20,10 @@
 //            The finished tile leaves through cp.async.bulk row stores.
 //   inverse  the same two passes backwards; the spectrum rows arrive through
 //            cp.async.bulk copies completing on an mbarrier (bounded wait).
+#include <cuda.h>  // CUtensorMap
+
+#include <cstring>
+
 #include "coop_fft.cuh"
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "kernels.h"
@@ -61,14 +65,21 @@ __device__ __forceinline__ void block_sync() {
 // columns (convolution weights).  The column pass is evaluated directly -- thread ky sums the image's
 // rows against its 16 twiddles, 16 columns at a time -- instead of transforming 64 column pairs of
 // zeros, and the row pass reads only those 16 columns.
-template <int N, bool IN_BULK, bool FULL = false, bool SMALLW = false>
+// CANVAS (with IN_BULK): zero-padded images whose rows are whole 16-byte units.  One tensor copy
+// (cp.async.bulk.tensor, zero fill outside the image) brings the whole N x N canvas of an image
+// into shared memory at a compile-time pitch of N + 4 floats: the copy starts at column
+// -4 ceil(padL / 4) of the image (a tensor copy's innermost coordinate must sit on a 16-byte
+// boundary) and row -padU, so the padding never costs a predicate and pass A reads with
+// compile-time strides like FULL.
+template <int N, bool IN_BULK, bool FULL = false, bool SMALLW = false, bool CANVAS = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_fwd_kernel(RealView in, float* __restrict__ out,
                                                                                 long long out_sb, int B, int padL,
-                                                                                int padU, long long blk_planes) {
+                                                                                int padU, long long blk_planes,
+                                                                                const __grid_constant__ CUtensorMap cmap) {
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
-  extern __shared__ __align__(16) float2 smem[];
+  extern __shared__ __align__(128) float2 smem[];
   float2* mid = smem;   // [N][PM]        pass A -> pass B
   float2* tile = smem;  // [H+1][PO]      pass B -> bulk stores (aliases mid)
   // the packed row's two halves live in the tile's padding columns N (direct) and N + 1 (mirrored),
@@ -93,7 +104,22 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     return hi <= total_bytes || (total_bytes & 15) == 0;
   };
   bool staged = false;
+  constexpr int CP = N + 4;  // canvas pitch (floats)
   auto fetch = [&](int b) {
+    if constexpr (CANVAS) {
+      staged = true;
+      if (threadIdx.x == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bar, CP * N * 4);
+        const int cx = -4 * ((padL + 3) / 4), cy = -padU;
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                smem_u32(smem)),
+            "l"(&cmap), "r"(cx), "r"(cy), "r"(b), "r"(bar)
+            : "memory");
+      }
+      return;
+    }
     long long lo;
     unsigned bytes;
     staged = window(b, &lo, &bytes);
@@ -181,7 +207,18 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           block_sync<T>();
         }
       }
-      if constexpr (FULL) {
+      if constexpr (CANVAS) {
+        // canvas column X sits at float X + 4 ceil(padL / 4) - padL of a canvas row
+        const float* p0 = reinterpret_cast<const float*>(smem) + item + (4 * ((padL + 3) / 4) - padL) + P * q * CP;
+#pragma unroll
+        for (int m = 0; m < Q; ++m) {
+#pragma unroll
+          for (int jl = 0; jl < P; ++jl) {
+            a[m * P + jl].x = p0[(jl + R * m) * CP];
+            a[m * P + jl].y = p0[(jl + R * m) * CP + H];
+          }
+        }
+      } else if constexpr (FULL) {
         const float* p0 = reinterpret_cast<const float*>(smem) + item + P * q * N;
 #pragma unroll
         for (int m = 0; m < Q; ++m) {
@@ -513,6 +550,8 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
     cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
     configured[dev] = true;
   }
+  alignas(64) CUtensorMap cmap;
+  std::memset(&cmap, 0, sizeof(cmap));
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
@@ -525,16 +564,32 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
         cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         small_configured[dev] = true;
       }
-      fft2d_coop_fwd_kernel<N, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, smem, s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+      fft2d_coop_fwd_kernel<N, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, smem, s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, cmap);
+      return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+    }
+  }
+  if (in_bulk && !(in.h == N && in.w == N && padL == 0 && padU == 0) && in.w % 4 == 0 && in.w + padL <= N &&
+      in.h + padU <= N) {
+    // zero-padded images with rows of whole 16-byte units: the canvas arrives by one tensor copy per image
+    const unsigned long long dims[3] = {(unsigned long long)in.w, (unsigned long long)in.h, (unsigned long long)B};
+    const unsigned long long strides[2] = {(unsigned long long)in.w * 4, (unsigned long long)in.h * in.w * 4};
+    const unsigned box[3] = {(unsigned)(N + 4), (unsigned)N, 1u};
+    static bool canvas_configured[64];
+    if (encode_tensor_map_f32(&cmap, in.p, 3, dims, strides, box)) {
+      if (dev >= 0 && dev < 64 && !canvas_configured[dev]) {
+        cudaFuncSetAttribute(fft2d_coop_fwd_kernel<N, true, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem<N>());
+        canvas_configured[dev] = true;
+      }
+      fft2d_coop_fwd_kernel<N, true, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, cmap);
       return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
     }
   }
   if (in_bulk && in.h == N && in.w == N && padL == 0 && padU == 0) {
-    fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+    fft2d_coop_fwd_kernel<N, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, cmap);
   } else if (in_bulk) {
-    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+    fft2d_coop_fwd_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, cmap);
   } else {
-    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes);
+    fft2d_coop_fwd_kernel<N, false><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, fwd_smem<N>(), s>>>(in, out.p, out.sb, B, padL, padU, out.blk_planes, cmap);
   }
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }

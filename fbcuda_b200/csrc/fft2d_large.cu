@@ -205,7 +205,10 @@ int fft2d_large_inverse(int n, const CplxView& in, const RealView& out, int B, i
   if (fft2d_coop_supported(n, in)) return fft2d_coop_inverse(n, in, out, B, padL, padU, s);
   if (n == 64) return launch_inv<64>(in, out, B, padL, padU, s);
   if (n == 128) return launch_inv<128>(in, out, B, padL, padU, s);
-  set_last_error("single-call inverse is available for N <= 128; use the two-call protocol for N = 256");
+  if (n == 256 && fft2d_256_inverse_supported(in, out, B, padL, padU)) return fft2d_256_inverse(in, out, B, s);
+  set_last_error(
+      "single-call inverse for N = 256 needs contiguous, 16-byte aligned tensors and full 256 x 256 output images "
+      "without crop (the output doubles as the intermediate buffer); otherwise use the two-call protocol");
   return kUnsupportedSize;
 }
 

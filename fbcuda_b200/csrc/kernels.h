@@ -29,6 +29,9 @@ int clear_device_error_coop();
 // N = 256 forward on a contiguous spectrum: two register passes, no intermediate buffer (fft2d_256.cu)
 bool fft2d_256_supported(const RealView& in, const CplxView& out, int B);
 int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
+// N = 256 inverse into contiguous, uncropped 256 x 256 images, which double as the intermediate buffer (fft2d_256.cu)
+bool fft2d_256_inverse_supported(const CplxView& in, const RealView& out, int B, int padL, int padU);
+int fft2d_256_inverse(const CplxView& in, const RealView& out, int B, cudaStream_t s);
 // forward transform by direct evaluation for images with a support of at most 8 x 8, N in {16, 32, 64, 128} (fft2d_pruned.cu)
 bool fft2d_pruned_supported(int n, const RealView& real, const CplxView& cplx, int padL, int padU);
 int fft2d_pruned_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s);
@@ -92,6 +95,9 @@ bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long lo
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
               bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb);
+// fp32 tensor map (no swizzle, zero fill outside the tensor) into a 128-byte, 64-byte aligned buffer (cgemm_tma.cu)
+bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigned long long* dims,
+                           const unsigned long long* strides_bytes, const unsigned* box);
 int read_device_error_tma();
 int clear_device_error_tma();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only

@@ -136,7 +136,12 @@ int fbfft_b200_fbifft2d(const float* src, const int* src_size, const int* src_st
  * reference for N >= 64, where it needs two calls and a caller-owned buffer
  * (fbfft/FBFFT2D-inl.cuh:597-617 then :627-669).  cplx is [B][N/2+1][N][2] in the
  * reference's final layout for the size class: [ky][kx] for N <= 32, transposed
- * [kx][ky] for N >= 64.  n is the transform size. */
+ * [kx][ky] for N >= 64.  n is the transform size.
+ * N = 256: an image and its spectrum do not fit one SM, so both directions run two passes
+ * without a buffer of their own -- the forward transform works inside the spectrum tensor, the
+ * inverse inside the real tensor, which must therefore be the full, contiguous, 16-byte aligned
+ * [B][256][256] image with padL = padU = 0 (FBFFT_UNSUPPORTED_SIZE otherwise: crops and strides
+ * go through the two-call protocol with its caller-owned [B][N][N][2] buffer). */
 int fbfft_b200_fft2d_r2c(int n, const float* real, const int* real_size, const int* real_stride, float* cplx,
                          const int* cplx_size, const int* cplx_stride, int padL, int padU, void* stream);
 int fbfft_b200_fft2d_c2r(int n, const float* cplx, const int* cplx_size, const int* cplx_stride, float* real,

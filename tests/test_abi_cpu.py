@@ -69,12 +69,15 @@ def test_conv_entry_points_refuse_null_strides_and_negative_pads():
     assert f(8, p, i4, None, 0, 0, p, i4, i4, p, i4, i4, 0, 0, None) == int(fb.ErrorCode.UnsupportedDimension)
 
 
-def test_single_call_inverse_refuses_n256_with_the_way_out():
+def test_single_call_inverse_n256_refuses_cropped_outputs_with_the_way_out():
+    # the N = 256 inverse works inside the real tensor, which must be the full 256 x 256 image
     L = fb.lib()
     c4 = (ctypes.c_int * 4)(1, 129, 256, 2)
-    r3 = (ctypes.c_int * 3)(1, 256, 256)
+    cs = (ctypes.c_int * 4)(129 * 512, 512, 2, 1)
+    r3 = (ctypes.c_int * 3)(1, 200, 200)
+    rs = (ctypes.c_int * 3)(40000, 200, 1)
     p = ctypes.c_void_p(256)
-    rc = L.fbfft_b200_fft2d_c2r(256, p, c4, c4, p, r3, r3, 0, 0, None)
+    rc = L.fbfft_b200_fft2d_c2r(256, p, c4, cs, p, r3, rs, 0, 0, None)
     assert rc == int(fb.ErrorCode.UnsupportedSize)
     assert "two-call" in fb.last_error()
 

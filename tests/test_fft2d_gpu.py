@@ -166,7 +166,23 @@ def test_n256_many_images():
     want = np.fft.rfft2(x.astype(np.float64)).transpose(0, 2, 1)            # [b][ky][kx] -> [b][kx][ky]
     per = np.linalg.norm((got - want).reshape(b, -1), axis=1) / np.linalg.norm(want.reshape(b, -1), axis=1)
     assert per.max() < FFT_TOL, int(per.argmax())
+    # the single-call inverse (two passes inside the output images), canary around the output
+    back = gpu_ifft2d(spec.astype(np.float32), n, n, n, 0, 0, fill=7.0).astype(np.float64)
+    want_b = np.fft.irfft2(want.transpose(0, 2, 1), s=(n, n)) * (n * n)
+    perb = np.linalg.norm((back - want_b).reshape(b, -1), axis=1) / np.linalg.norm(want_b.reshape(b, -1), axis=1)
+    assert perb.max() < FFT_TOL, int(perb.argmax())
     assert fb.device_status() == 0
+
+
+def test_n256_inverse_ignores_what_the_hermitian_half_implies():
+    """The single-call N = 256 inverse on an arbitrary (not Hermitian-consistent) stored half: lines
+    kx = 0 and kx = 128 contribute only their real parts, as the float64 definition says."""
+    n, b = 256, 3
+    rng = np.random.default_rng(2560)
+    spec = rng.normal(size=(b, n // 2 + 1, n, 2)).astype(np.float32)
+    back = gpu_ifft2d(spec, n, n, n, 0, 0)
+    want = orc.fbifft2d(spec, n, n, n, 0, 0)
+    assert orc.rel_l2(back, want) < FFT_TOL
 
 
 @pytest.mark.parametrize("case", [(28, 28, 0, 0), (28, 28, 2, 3), (24, 20, 1, 2), (32, 32, 0, 0), (2, 2, 5, 7), (32, 4, 0, 3)])
@@ -179,4 +195,20 @@ def test_n32_images_of_whole_16_byte_units(case, b):
     x = rng.uniform(-1, 1, (b, h, w)).astype(np.float32)
     spec = gpu_fft2d(x, 32, pl, pu)
     assert orc.rel_l2(spec, orc.fbfft2d(x, 32, pl, pu)) < FFT_TOL
+    assert fb.device_status() == 0
+
+
+@pytest.mark.parametrize("case", [(64, 56, 56, 1, 1), (64, 60, 52, 3, 5), (64, 4, 8, 0, 0), (64, 64, 60, 0, 4), (64, 40, 64, 9, 0),
+                                  (128, 116, 116, 0, 0), (128, 100, 64, 7, 2), (128, 128, 124, 0, 3), (128, 12, 20, 30, 40)])
+@pytest.mark.parametrize("b", [1, 3, 500])
+def test_zero_padded_images_with_rows_of_whole_16_byte_units(case, b):
+    """N = 64 / 128, contiguous images whose width is a multiple of 4 floats: the canvas is staged by
+    one tensor copy per image (zero fill outside the image, any padL / padU)."""
+    n, h, w, pl, pu = case
+    if n == 128 and b == 500:
+        b = 150
+    rng = np.random.default_rng(b + 7 * h + w + pl)
+    x = rng.uniform(-1, 1, (b, h, w)).astype(np.float32)
+    spec = gpu_fft2d(x, n, pl, pu)
+    assert orc.rel_l2(spec, orc.fbfft2d(x, n, pl, pu)) < FFT_TOL
     assert fb.device_status() == 0

@@ -48,9 +48,9 @@ def gpu_ifft2d(spec, n, h, w, pad_l=0, pad_u=0, fill=0.0):
     n_el = b * h * w
     raw, out = canary_alloc((b, h, w))
     out.fill_(fill)
-    if n == 256:
-        # the single-call inverse stops at N = 128 (an image no longer fits in shared
-        # memory); N = 256 goes through the two-call protocol with a caller-owned buffer
+    if n == 256 and not (h == 256 and w == 256 and pad_l == 0 and pad_u == 0):
+        # the single-call N = 256 inverse works inside the full 256 x 256 output image; crops go
+        # through the two-call protocol with a caller-owned buffer
         mid = torch.empty((b, n, n, 2), device="cuda")
         fb.fbifft2D_c2c(dev(spec), mid)
         fb.fbifft2D(mid, out, pad_l, pad_u)
