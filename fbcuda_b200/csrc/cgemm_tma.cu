@@ -9,17 +9,18 @@
 // A tile is 128 rows of m, BN columns of n and 4 consecutive bins (32 contiguous bytes of every
 // operand element: one DRAM sector).  Each block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // Roles (17 warps):
-//   warps 8-11    issue, per 4 values of k, the 16-byte cp.async copies of one raw stage ([k][row]
-//                 [32 B] per operand, zero-filled outside the tensor) into a ring of NR stages; the
-//                 stage's mbarrier counts the copies' completion.  Lanes follow the direction in
-//                 which the operand is contiguous, so the convolution workspace (4-bin blocks,
-//                 planes adjacent) is read in whole 128-byte lines.  (TMA tensor copies were measured
-//                 first: with a 32-byte inner box they reach 1.3 TB/s, these copies 2 TB/s on
-//                 bins-innermost tensors and the full rate on the blocked workspace.)
-//   warps 0-7     read the raw stages, split every fp32 into hi = tf32(x) and lo = x - hi, and write
-//                 K-major operand tiles in the tensor core's no-swizzle layout (8 x 16-byte core
-//                 matrices) per bin: Ar, Ai (hi and lo) and the stack [-s Bi | Br | s Bi] (hi and lo;
-//                 s = -1 when B is conjugated), into a ring of two half stages of two bins each;
+//   warps 8-11    bring the raw fp32 operands of 4 values of k into a ring of NR stages ([k][row][32 B]
+//                 per operand).  Operands in 4-bin blocks (the convolution workspace) arrive by two
+//                 tensor copies per stage, issued by one thread (cp.async.bulk.tensor with the 32-byte
+//                 swizzle, zero fill outside the tensor, completion bytes on the stage's mbarrier).
+//                 Other layouts take 16-byte cp.async copies issued by all four warps, lanes following
+//                 the direction in which the operand is contiguous; that path levels off near 32 KB in
+//                 flight per SM (FFT-64 layer: 170 us per contraction against 136 us with tensor copies).
+//   warps 0-7     read the raw stages into registers, hand them back at once, split every fp32 into
+//                 hi = tf32(x) and lo = x - hi, and write K-major operand tiles in the tensor core's
+//                 no-swizzle layout (8 x 16-byte core matrices) per bin: Ar, Ai (hi and lo) and the
+//                 stack [-s Bi | Br | s Bi] (hi and lo; s = -1 when B is conjugated), into a ring of two
+//                 half stages of two bins each;
 //   warp 12       one lane issues, per bin and k-step of 8, six MMAs of 128 x 2BN x 8 into the bin's
 //                 [Re | Im] accumulator:  Ar_h x S_h, Ai_h x S'_h, Ar_h x S_l, Ai_h x S'_l, Ar_l x S_h,
 //                 Ai_l x S'_h with S = rows BN..3BN of the stack = [Br | s Bi] and S' = rows 0..2BN =
@@ -28,10 +29,17 @@
 //   warps 13-16   read the accumulators (tcgen05.ld, each warp its own 32 lanes = rows), scale,
 //                 interleave the 4 bins' re/im into 32 bytes per (m, n) in a 4 KB staging buffer and
 //                 issue one tensor store (or reduce-add when accumulating) per 4 columns of n.
-// What bounds it: shared-memory bandwidth.  Per half stage the MMAs read 96 KB of operand tiles,
-// the split writes 56 KB and reads 24 KB, the copies write 24 KB -- about 200 KB at 128 B/clock;
-// measured alone, the MMAs run at the tf32 peak and the split at 70 % of the shared-memory rate,
-// and together their times add.
+// What bounds it, measured with roles switched off one at a time (FFT-64 layer, B = 64, before the
+// tensor copies: 171 us): everything but the copies 119 us, the copies alone 115 us, the barrier
+// skeleton with the accumulator reads 44 us, MMAs and stores under 10 us each.  The split and the
+// MMAs' operand reads share the shared-memory bandwidth (per half stage the MMAs read 96 KB of
+// operand tiles, the split writes 56 KB and reads 24 KB, the copies write 24 KB), and the two half
+// stages serialise split and MMAs of a bin pair through two barrier hand-overs.  Tried and measured
+// slower: stores of the result straight from registers (32-byte st.global.v8: 184 us; two 16-byte
+// halves: 209 us), the 128-row operand loaded straight into registers one k-step ahead (same time
+// for row-contiguous operands, 205 us for k-contiguous ones), L2 prefetches ahead of the copies
+// (290 us), busy polling instead of suspending waits (182 us), MMAs issued by the last converter
+// warp to arrive (201 us), a third half stage or six raw stages for column tiles <= 32 (no change).
 // Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
 // block still releases its tensor memory before returning.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
