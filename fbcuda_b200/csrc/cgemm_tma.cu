@@ -39,7 +39,10 @@
 // halves: 209 us), the 128-row operand loaded straight into registers one k-step ahead (same time
 // for row-contiguous operands, 205 us for k-contiguous ones), L2 prefetches ahead of the copies
 // (290 us), busy polling instead of suspending waits (182 us), MMAs issued by the last converter
-// warp to arrive (201 us), a third half stage or six raw stages for column tiles <= 32 (no change).
+// warp to arrive (201 us), a third half stage or six raw stages for column tiles <= 32 (no change),
+// the epilogue's staging buffer as two halves stored separately (145 us against 138 us).  Second
+// ablation, on this kernel (138 us): without the epilogue 109, without the split 125, without the
+// copies 122, without the MMAs 126; barrier skeleton alone 27, with the accumulator reads 44.
 // Every mbarrier wait is bounded; a wait that runs out records an error, the roles drain, and the
 // block still releases its tensor memory before returning.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up through the runtime
