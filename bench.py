@@ -459,7 +459,22 @@ def run_extras(args, x, spec, n0, hw0):
                          "inv_us": ms_b * 1e3, "inv_gbs": byts / ms_b / 1e6, "inv_frac_of_measured": byts / ms_b / 1e6 / peak}
         del x, spec, back
         torch.cuda.empty_cache()
+    # the reference-shaped tile-list entry point (FFTIteratedConvolution<32>, one tile) on the forward layer,
+    # reduced batch: it keeps the reference's structure (both operand spectra recomputed per output plane)
+    itb, itc, ito = 16, 64, 128
+    xi = torch.randn((itb, itc, 27, 27), device="cuda")
+    wi = torch.randn((ito, itc, 5, 5), device="cuda") / 40.0
+    oi = torch.empty((itb, ito, 23, 23), device="cuda")
+    tin, tout = fb.TiledDeviceTensor([(xi, 0, 0)]), fb.TiledDeviceTensor([(oi, 0, 0)])
+    it_ms = time_steps(lambda: fb.FFTIteratedConvolution(32, tin, tout, wi, 0, 1.0, itb), 5, 2, 1)
+    wsi = torch.empty(fb.conv_workspace_bytes(32, itb, itc, ito) // 4, device="cuda")
+    ws_ms = time_steps(lambda: fb.conv_update_output(32, xi, wi, oi, wsi), 5, 2, 1)
+    iterated = {"workload": f"updateOutput B={itb} C={itc} O={ito} 27x27 k5 FFT32, one tile",
+                "FFTIteratedConvolution_us": it_ms * 1e3, "workspace_pass_us": ws_ms * 1e3}
+    del xi, wi, oi, wsi
+    torch.cuda.empty_cache()
     return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d,
+            "iterated_convolution_tile_list": iterated,
             "two_call_protocol_512MiB": two_call, "config1_1d_4096x32": config1,
             f"storage_16bit_N{n0}_{hw0}x{hw0}": storage}
 
@@ -470,6 +485,7 @@ CONV_CONFIGS = {
     "conv4": dict(B=64, C=128, O=128, hw=56, k=3, pad=1, n=64, seeds=(4, 5, 6), wstd=(2.0 / (128 * 9)) ** 0.5, passes=3),
     "conv5": dict(B=32, C=96, O=96, hw=128, k=13, pad=0, n=128, seeds=(7, 8, 9), wstd=(1.0 / (96 * 169)) ** 0.5, passes=3),
 }
+NCCL_MAX_CTAS = 0        # set from --nccl-max-ctas
 NVLINK_GBS = 770.0      # measured peer-copy bandwidth per direction per GPU on this pool
 _TF32_PEAK = {}
 
@@ -492,6 +508,8 @@ def make_communicator(world, rank):
     import fbcuda_b200 as fb
     ident = [fb.comm_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ident, src=0)
+    if NCCL_MAX_CTAS:
+        os.environ["FBFFT_B200_NCCL_MAX_CTAS"] = str(NCCL_MAX_CTAS)
     return fb.Communicator(ident[0], rank, world, timeout_ms=120000)
 
 
@@ -571,6 +589,7 @@ def conv_block(name, args, world, rank, comm, with_cpu=True):
     modes = {"frequency_reduce_scatter": api.DP_FREQUENCY_REDUCE_SCATTER, "frequency_allreduce": api.DP_FREQUENCY_ALLREDUCE,
              "spatial_allreduce": api.DP_SPATIAL_ALLREDUCE}
     steps, warm = args.steps, max(3, args.warmup)
+    fb.set_contraction_reserved_sms(args.reserve_sms if (world > 1 and passes == 3) else 0)
     block = {"workload": f"conv {'fwd' if passes == 1 else 'fwd+gradInput+gradWeight'} B={bg} C={c} O={o} {hw}x{hw} k{k} pad{pad} FFT{n}",
              "n_gpus": world, "scaling": "strong", "images_per_step": bg, "shard_images": b}
     if world == 1 or passes == 1:
@@ -599,6 +618,7 @@ def conv_block(name, args, world, rank, comm, with_cpu=True):
         ms = per_mode[head]["ms_per_step"]
         block.update({"ms_per_step": ms, "images_per_s": bg / (ms / 1e3), "dw_mode": head, "dw_modes": per_mode,
                       "ms_per_step_without_collective": ms_none, "nccl_ranks": comm.world,
+                      "contraction_reserved_sms": args.reserve_sms, "nccl_max_ctas": NCCL_MAX_CTAS,
                       "launch": "eager; the weight-gradient sum, inverse and gather on a second stream under updateOutput and updateGradInput"})
         step_check = make_step_dp(modes[head])
 
@@ -725,6 +745,7 @@ def conv_block(name, args, world, rank, comm, with_cpu=True):
                                  "sample": f"batch {bs} of {bg}, one step ({dt:.2f} s), weight-side work not amortised over the full batch"}
     del x, go, w, out, gi, gw, ws, ws2
     torch.cuda.empty_cache()
+    fb.set_contraction_reserved_sms(0)
     return block
 
 
@@ -770,6 +791,10 @@ def main():
     ap.add_argument("--workload", default="fft2d", choices=["fft2d", "conv"])
     ap.add_argument("--conv-config", default="conv4", choices=["conv3", "conv4", "conv5"])
     ap.add_argument("--no-graph", action="store_true", help="conv workload on one GPU: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--reserve-sms", type=int, default=16,
+                    help="several GPUs: SMs the contraction leaves free so that the NCCL kernels of the weight-gradient sum run beside it")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0,
+                    help="several GPUs: cap on the blocks of NCCL's kernels for the library's communicator (0: NCCL's default)")
     ap.add_argument("--conv-blocks", type=int, default=1,
                     help="fft2d workload: also time the convolution layers and append them to the line")
     ap.add_argument("--fft-size", type=int, default=32)
@@ -786,6 +811,8 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    global NCCL_MAX_CTAS
+    NCCL_MAX_CTAS = args.nccl_max_ctas
     world, rank, local = dist_setup(args)
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)

@@ -29,6 +29,7 @@ from .api import (  # noqa: F401
     Communicator,
     conv_acc_grad_parameters_dp,
     set_contraction_mode,
+    set_contraction_reserved_sms,
     lib,
     transposeMM,
     conv_workspace_bytes,

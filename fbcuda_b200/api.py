@@ -145,6 +145,11 @@ def measure_tf32_peak(n_cols: int = 256) -> float:
     return float(v.value)
 
 
+def set_contraction_reserved_sms(sms: int) -> None:
+    """SMs the persistent contraction leaves free for kernels of other streams (collectives)."""
+    _check(lib().fbfft_b200_set_contraction_reserved_sms(int(sms)))
+
+
 def set_contraction_mode(mode: int) -> None:
     """0: tensor cores (3xTF32, TMA-fed persistent kernel) when the operands qualify; 1: FP32 CUDA cores only;
     2: tensor cores through the gather kernel only (comparison point)."""

@@ -127,6 +127,12 @@ int fbfft_b200_measure_tf32_peak(int n_cols, double* tflops) {
   return kSuccess;
 }
 
+int fbfft_b200_set_contraction_reserved_sms(int sms) {
+  if (sms < 0 || sms > 128) return fail(kUnsupportedDimension, "set_contraction_reserved_sms: 0..128");
+  set_contraction_reserved_sms(sms);
+  return kSuccess;
+}
+
 int fbfft_b200_set_contraction_mode(int mode) {
   if (mode < 0 || mode > 2)
     return fail(kUnsupportedDimension, "set_contraction_mode: 0 (tensor cores), 1 (FP32 cores) or 2 (tensor cores, gather kernel)");

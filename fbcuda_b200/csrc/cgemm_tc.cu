@@ -396,6 +396,9 @@ int g_mode = 0;  // 0 auto (tensor cores when the operands qualify), 1 FP32 CUDA
 
 void set_contraction_mode(int mode) { g_mode = mode; }
 int contraction_mode() { return g_mode; }
+static int g_reserved_sms = 0;
+void set_contraction_reserved_sms(int n) { g_reserved_sms = n < 0 ? 0 : n; }
+int contraction_reserved_sms() { return g_reserved_sms; }
 
 bool cgemm_tc_supported(const float* a, long long a_rs, long long a_ks, const float* b, long long b_rs, long long b_ks,
                         const float* d, long long d_ms, long long d_ns, int M, int N, int K, int X) {

@@ -596,7 +596,11 @@ int launch_tma(const CUtensorMap& md, const CUtensorMap& ma, const CUtensorMap& 
   a.m_tiles = (a.M + BM - 1) / BM;
   const long long total = (long long)a.n_tiles * a.m_tiles * (a.X / XB);
   a.total_tiles = (int)total;
-  const int grid = total < sm_count() ? (int)total : sm_count();
+  // one persistent block per SM; a caller that runs collectives beside the contraction can keep some
+  // SMs free for them (a block fills an SM's shared memory, so nothing else starts there before it ends)
+  const int sms = sm_count() - contraction_reserved_sms();
+  const int cap = sms > 1 ? sms : 1;
+  const int grid = total < cap ? (int)total : cap;
   cgemm_tma_kernel<BN><<<grid, kThreads, Cfg<BN>::SMEM, s>>>(md, ma, mb, a);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }

@@ -15,6 +15,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <thread>
@@ -164,6 +165,12 @@ int fbfft_b200_comm_init(const void* unique_id, int rank, int world, int timeout
   std::memcpy(&id, unique_id, sizeof(id));
   ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
   cfg.blocking = 0;
+  // FBFFT_B200_NCCL_MAX_CTAS caps the blocks NCCL's kernels use, so that they fit on the SMs a caller
+  // keeps free of the persistent contraction (fbfft_b200_set_contraction_reserved_sms)
+  if (const char* e = std::getenv("FBFFT_B200_NCCL_MAX_CTAS")) {
+    const int v = std::atoi(e);
+    if (v >= 1 && v <= 64) cfg.maxCTAs = v;
+  }
   Comm* c = new Comm;
   c->rank = rank, c->world = world, c->timeout_ms = timeout_ms;
   ncclResult_t r = api().CommInitRankConfig(&c->nccl, world, id, rank, &cfg);

@@ -220,11 +220,11 @@ __global__ void __launch_bounds__(kThreads16, 3) fft2d_small_inv16_kernel(const 
   extern __shared__ __align__(16) float2 smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float2* buf = smem + warp * (IPW * IS);
-  float* slot = reinterpret_cast<float*>(smem + kWarps16 * (IPW * IS)) + warp * slot_floats;
-  unsigned char* raw = reinterpret_cast<unsigned char*>(reinterpret_cast<float*>(smem + kWarps16 * (IPW * IS)) + kWarps16 * slot_floats) +
-                       warp * raw_bytes;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(
-      reinterpret_cast<unsigned char*>(reinterpret_cast<float*>(smem + kWarps16 * (IPW * IS)) + kWarps16 * slot_floats) + kWarps16 * raw_bytes);
+  // the cropped fp32 image is staged in the work buffer itself, once the column pass holds it in registers
+  float* slot = reinterpret_cast<float*>(buf);
+  unsigned char* raw = reinterpret_cast<unsigned char*>(smem + kWarps16 * (IPW * IS)) + warp * raw_bytes;
+  unsigned long long* bars =
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(smem + kWarps16 * (IPW * IS)) + kWarps16 * raw_bytes);
   const unsigned bar = smem_u32(bars + warp);
   if (lane == 0) mbar_init(bar, 1);
   fence_async_smem();
@@ -268,6 +268,7 @@ __global__ void __launch_bounds__(kThreads16, 3) fft2d_small_inv16_kernel(const 
     {
       float2 z[N];
       inv_columns<N>(ib, l, z);
+      __syncwarp();  // every lane holds its columns: the work buffer may take the image
       // the cropped image, still fp32, in the slot
       store_columns<N>(slot + li * hw, w, 1, h, w, padL, padU, l, z, 1.0f);
     }
@@ -296,7 +297,8 @@ int launch16(bool inverse, const void* src, void* dst, int B, int h, int w, int 
   const int slot_floats = ((IPW * h * w + 3) / 4) * 4 + 4;
   // raw staging per warp: the task's images plus alignment slack (forward), the task's spectra (inverse)
   const int raw_bytes = inverse ? IPW * ROWS * N * 2 * (int)sizeof(TI) : ((IPW * h * w * (int)sizeof(TI) + 15) / 16) * 16 + 32;
-  const int smem = kWarps16 * (IPW * SmallCfg<N>::IS * 8 + slot_floats * 4 + raw_bytes + 8);
+  // (the inverse stages its fp32 image inside the work buffer: no slot of its own)
+  const int smem = kWarps16 * (IPW * SmallCfg<N>::IS * 8 + (inverse ? 0 : slot_floats * 4) + raw_bytes + 8);
   const int want = (ntasks + kWarps16 - 1) / kWarps16, cap = sm_count() * 3;
   const int grid = want < cap ? want : cap;
   if (inverse) {

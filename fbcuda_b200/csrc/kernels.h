@@ -103,6 +103,9 @@ int clear_device_error_tma();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only
 void set_contraction_mode(int mode);
 int contraction_mode();
+// SMs the persistent contraction leaves free (for collectives that run beside it)
+void set_contraction_reserved_sms(int n);
+int contraction_reserved_sms();
 int read_device_error_tc();
 int clear_device_error_tc();
 

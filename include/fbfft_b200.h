@@ -81,6 +81,13 @@ int fbfft_b200_measure_tf32_peak(int n_cols, double* tflops);
  * needs 32-byte aligned operands and strides that are multiples of 4). */
 int fbfft_b200_set_contraction_mode(int mode);
 
+/* Number of SMs the tensor-core contraction leaves free (process-wide, default 0; no counterpart in
+ * the reference).  The contraction runs one persistent block per SM that fills the SM's shared
+ * memory, so no other kernel starts on an SM it occupies; a data-parallel caller that wants the
+ * weight-gradient collective (NCCL kernels on a second stream) to run BESIDE the contractions of the
+ * other passes, not after them, reserves a few SMs for it. */
+int fbfft_b200_set_contraction_reserved_sms(int sms);
+
 /* fbfft1D<1>(DeviceTensor<float,2>& real, DeviceTensor<float,3>& complex, padL, s)
  * -- fbfft/FBFFT.cuh:11-16, fbfft/FBFFT-inl.cuh:19-87.
  * real [B][N], N = real_size[1] in {8..256}; complex [B][N/2+1][2].
@@ -342,7 +349,9 @@ int fbfft_b200_conv_tiled_acc_grad_parameters(int fft_size, const float* in, con
  *   hands them to the other ranks by any means.
  * fbfft_b200_comm_init: every rank, with its device current.  Bounded: when the ranks have not
  *   all joined within timeout_ms the half-built communicator is aborted and FBFFT_CUDA_ERROR
- *   returned.  The same limit bounds every later wait of the host on this communicator.
+ *   returned.  The same limit bounds every later wait of the host on this communicator.  The
+ *   environment variable FBFFT_B200_NCCL_MAX_CTAS (1..64), read here, caps the blocks NCCL's kernels
+ *   use (see fbfft_b200_set_contraction_reserved_sms).
  * fbfft_b200_comm_destroy: after the last call's work has finished on the stream.
  * fbfft_b200_dp_shard: the contiguous shard [lo, lo + count) of `total` units for `rank`
  *   (the first total % world ranks hold one more); host arithmetic only. */

@@ -49,6 +49,9 @@ def test_validation_without_device():
     assert rc == int(fb.ErrorCode.UnsupportedSize)
     assert "N must be" in fb.last_error()
     assert L.fbfft_b200_set_contraction_mode(7) == int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_set_contraction_reserved_sms(-1) == int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_set_contraction_reserved_sms(129) == int(fb.ErrorCode.UnsupportedDimension)
+    assert L.fbfft_b200_set_contraction_reserved_sms(16) == 0 and L.fbfft_b200_set_contraction_reserved_sms(0) == 0
 
 
 def test_conv_entry_points_refuse_null_strides_and_negative_pads():
