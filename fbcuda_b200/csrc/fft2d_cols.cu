@@ -5,9 +5,12 @@
 // One block owns one image.  The image (N x (N/2+1) complex values, contiguous) arrives by one
 // cp.async.bulk (completion on an mbarrier, bounded wait).  Column kx < N/2 belongs to Q = N/64
 // neighbouring lanes, which read it from shared memory (lanes run over kx: no bank conflicts) and
-// transform it in registers (coop_fft.cuh); the last column kx = N/2 has no lanes of its own, so it
-// is set aside and transformed in a second round by the lanes of column 0.  The results overwrite the
-// image as a [N/2+1][N] tile whose rows leave through bulk stores.
+// transform it in registers (coop_fft.cuh); the last column kx = N/2 has no lanes of its own.  It is
+// set aside and transformed in a second round by lanes of warp 0 -- at N = 128, where that round
+// would otherwise idle the other three warps once per image, the set-aside columns of four
+// consecutive images of the block wait for ONE such round and their rows kx = N/2 leave by bulk
+// stores of their own (234 -> 193 us for 8192 images: 0.71 -> 0.86 of the copy bandwidth).  The other results overwrite the image as a [N/2+1][N] tile whose rows leave
+// through bulk stores.
 #include "coop_fft.cuh"
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "kernels.h"
@@ -22,7 +25,11 @@ template <int N>
 struct ColsCfg {
   static constexpr int R = 64, Q = N / 64, H = N / 2, HC = N / 2 + 1, T = H * Q, PO = N + 2;
   static constexpr int REGION = HC * PO;                  // complex values: tile [HC][PO] >= image [N][HC]
-  static constexpr int SMEM = (REGION + N) * 8 + 16;      // + the set-aside column + the mbarrier
+  // images whose last columns share one extra round (measured at N = 64, where a block is one warp:
+  // sharing the round among 8 images at 10 blocks per SM changed nothing, 201 -> 205 us for 32 768
+  // images; the pass is not bound by its arithmetic there)
+  static constexpr int G = N == 128 ? 4 : 1;
+  static constexpr int SMEM = (REGION + G * N) * 8 + 16;  // + the set-aside columns + the mbarrier
   static constexpr int BLOCKS = N == 64 ? 12 : 3;
 };
 
@@ -30,12 +37,12 @@ template <int N>
 __global__ void __launch_bounds__(ColsCfg<N>::T, ColsCfg<N>::BLOCKS) cols_fwd_kernel(const float* __restrict__ buf,
                                                                                     float* __restrict__ dst, int B) {
   using C = ColsCfg<N>;
-  constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, H = C::H, HC = C::HC, T = C::T, PO = C::PO;
+  constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, H = C::H, HC = C::HC, T = C::T, PO = C::PO, G = C::G;
   extern __shared__ __align__(16) float2 sm[];
   float2* img = sm;            // [N][HC]
   float2* tile = sm;           // [HC][PO]
-  float2* last = sm + C::REGION;  // column N/2: [N]
-  const unsigned bar = smem_u32(sm + C::REGION + N);
+  float2* last = sm + C::REGION;  // column N/2 of up to G images: [G][N]
+  const unsigned bar = smem_u32(sm + C::REGION + G * N);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q = lane / LP, kx = warp * LP + (lane % LP);
   float2 lf[Q];
@@ -48,10 +55,40 @@ __global__ void __launch_bounds__(ColsCfg<N>::T, ColsCfg<N>::BLOCKS) cols_fwd_ke
       bulk_g2s(smem_u32(img), buf + (long long)b * (2 * N * HC), kImageBytes, bar);
     }
   };
+  // transform of the `count` set-aside columns (images first_b, first_b + gridDim.x, ...) by warp 0,
+  // line j in the lanes of column j; the rows kx = N/2 go back into `last` and leave from there
+  auto flush_last = [&](int first_b, int count) {
+    if (warp == 0) {
+      float2 a[R];
+      const int j = lane % LP;  // line slot; slots >= count transform stale values that are never stored
+      const float2* src = last + (j < G ? j : 0) * N;
+#pragma unroll
+      for (int m = 0; m < Q; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < P; ++jl) a[m * P + jl] = src[jl + P * q + R * m];
+      }
+      coop_fft<N, R, Q, false>(a, q, lf);
+      __syncwarp();  // every lane has read its line before any lane overwrites it
+      if (j < count) {
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          last[j * N + Q * k + q] = a[brev(k, R)];
+        });
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane < count)
+        bulk_s2g(dst + (long long)(first_b + lane * (int)gridDim.x) * (2 * N * HC) + (long long)H * (2 * N), smem_u32(last + lane * N),
+                 N * 8);
+      bulk_commit();
+      bulk_wait_read();  // the lines are free again
+    }
+  };
   if (threadIdx.x == 0) mbar_init(bar, 1);
   fence_async_smem();
   __syncthreads();
   unsigned phase = 0;
+  int pending = 0, first_pending = 0;
   if (blockIdx.x < B) fetch(blockIdx.x);
   for (int b = blockIdx.x; b < B; b += gridDim.x) {
     if (!mbar_wait(bar, phase, kErrColsFwdWait)) return;
@@ -62,33 +99,23 @@ __global__ void __launch_bounds__(ColsCfg<N>::T, ColsCfg<N>::BLOCKS) cols_fwd_ke
 #pragma unroll
       for (int jl = 0; jl < P; ++jl) a[m * P + jl] = img[(jl + P * q + R * m) * HC + kx];
     }
-    for (int y = threadIdx.x; y < N; y += T) last[y] = img[y * HC + H];
+    if (pending == 0) first_pending = b;
+    for (int y = threadIdx.x; y < N; y += T) last[pending * N + y] = img[y * HC + H];
+    ++pending;
     __syncthreads();  // the image is in registers (and its last column set aside): the tile may overwrite it
     coop_fft<N, R, Q, false>(a, q, lf);
     static_for<R>([&](auto kc) {
       constexpr int k = decltype(kc)::value;
       tile[kx * PO + Q * k + q] = a[brev(k, R)];
     });
-    if (warp == 0) {
-      // second round: column N/2 by the lanes of column 0 (the warp's other lanes only take part in
-      // the exchange)
-#pragma unroll
-      for (int m = 0; m < Q; ++m) {
-#pragma unroll
-        for (int jl = 0; jl < P; ++jl) a[m * P + jl] = last[jl + P * q + R * m];
-      }
-      coop_fft<N, R, Q, false>(a, q, lf);
-      if (kx == 0) {
-        static_for<R>([&](auto kc) {
-          constexpr int k = decltype(kc)::value;
-          tile[H * PO + Q * k + q] = a[brev(k, R)];
-        });
-      }
+    if (pending == G || b + (int)gridDim.x >= B) {
+      flush_last(first_pending, pending);
+      pending = 0;
     }
     fence_async_smem();
     __syncthreads();
     float* out = dst + (long long)b * (2 * N * HC);
-    for (int r = threadIdx.x; r < HC; r += T) bulk_s2g(out + (long long)r * (2 * N), smem_u32(tile + r * PO), N * 8);
+    for (int r = threadIdx.x; r < H; r += T) bulk_s2g(out + (long long)r * (2 * N), smem_u32(tile + r * PO), N * 8);
     bulk_commit();
     bulk_wait_read();
     __syncthreads();
