@@ -127,6 +127,14 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
       const long long pc = cols <= 16 ? 16 : (cols <= 32 ? 32 : (p48 < p64 ? p48 : p64));
       return ((rows + 127) / 128 * 128) * pc;
     };
+    // a shard of at most 8 images leaves a contraction with 8 columns or 8 terms: no tile of the
+    // tensor-core kernel fits that, the FP32 kernels stream the large operand (or the result) once
+    if (contraction_mode() == 0 &&
+        cgemm_small_supported(a, b, d, d_pm * n, d_pn * n, d_planes * n, n, 4, 4, M, N, K, (int)X, accumulate)) {
+      const int rc = cgemm_small(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K,
+                                 (int)X, inv_norm, s, a_planes * 4, b_planes * 4, d_planes * n, n);
+      if (rc != -1) return rc;  // -1: a tensor map could not be encoded, the general kernel takes over
+    }
     if (padded(N, M) < padded(M, N)) {
       return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, d_pn * n, d_pm * n, N, M, K, (int)X,
                       inv_norm, accumulate, s, b_planes * 4, a_planes * 4, d_planes * n, 4, 4, n);

@@ -100,6 +100,14 @@ bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigne
                            const unsigned long long* strides_bytes, const unsigned* box);
 int read_device_error_tma();
 int clear_device_error_tma();
+// FP32 CUDA-core version for n <= 8 columns or k <= 8 terms, operands in 4-bin blocks, overwriting result (cgemm_small.cu)
+bool cgemm_small_supported(const float* a, const float* b, const float* d, long long d_ms, long long d_ns, long long d_bs,
+                           int d_qb, int a_qb, int b_qb, int M, int N, int K, int X, bool accumulate);
+int cgemm_small(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
+                bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
+                cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int d_qb);
+int read_device_error_small();
+int clear_device_error_small();
 // 0: tensor cores when the operands qualify, 1: FP32 CUDA cores only, 2: tensor cores, gather kernel only
 void set_contraction_mode(int mode);
 int contraction_mode();

@@ -81,6 +81,50 @@ def test_layer_at_benchmark_batch_through_both_call_chains(name):
     assert fb.device_status() == 0
 
 
+@pytest.mark.parametrize("case", [
+    # n, batch shard, C, O, image, kernel, pad: the shards data-parallel runs on 4 and 8 GPUs leave
+    (64, 8, 128, 128, 56, 3, 1), (128, 4, 96, 96, 128, 13, 0), (32, 5, 40, 200, 27, 5, 0), (16, 1, 16, 16, 12, 3, 1),
+    (32, 3, 130, 24, 20, 5, 2), (64, 7, 33, 65, 30, 7, 0), (16, 8, 256, 4, 14, 3, 0)])
+def test_small_batch_shards_take_the_fp32_streaming_contraction(case):
+    """At most 8 images: updateOutput / updateGradInput contract against 8 or fewer columns and
+    accGradParameters sums 8 or fewer terms; plane counts that are no multiple of the 128-row and
+    64-column tiles, k that is no multiple of the stage depth."""
+    n, b, c, o, hw, k, pad = case
+    rng = np.random.default_rng(sum(case))
+    oh = hw + 2 * pad - k + 1
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    w = (rng.normal(size=(o, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    xd, wd, god = dev(x), dev(w), dev(go)
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    out = torch.full(go.shape, 7.0, device="cuda")
+    gi = torch.full(x.shape, 7.0, device="cuda")
+    gw = torch.full(w.shape, 7.0, device="cuda")
+    ip = (pad, pad)
+    fb.conv_update_output(n, xd, wd, out, ws, inPad=ip)
+    fb.conv_update_grad_input(n, gi, wd, god, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, inPad=ip, scale=0.5,
+                                flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    assert orc.rel_l2(host(out), orc.fftconv_update_output(x, w, n, pad)) < CONV_TOL
+    assert orc.rel_l2(host(gi), orc.fftconv_update_grad_input(go, w, n, hw, hw, pad)) < CONV_TOL
+    assert orc.rel_l2(host(gw), orc.fftconv_acc_grad_parameters(x, go, n, k, k, pad, scale=0.5)) < CONV_TOL
+    # same answer as the tensor-core contraction gives for the same workspace layout
+    fb.set_contraction_mode(2)
+    try:
+        out2, gi2, gw2 = torch.empty_like(out), torch.empty_like(gi), torch.empty_like(gw)
+        fb.conv_update_output(n, xd, wd, out2, ws, inPad=ip)
+        fb.conv_update_grad_input(n, gi2, wd, god, ws, inPad=ip, flags=api.REUSE_WEIGHT_SPECTRUM)
+        fb.conv_acc_grad_parameters(n, xd, gw2, god, ws, inPad=ip, scale=0.5,
+                                    flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
+        torch.cuda.synchronize()
+    finally:
+        fb.set_contraction_mode(0)
+    for got, other in ((out, out2), (gi, gi2), (gw, gw2)):
+        assert orc.rel_l2(host(got), host(other).astype(np.float64)) < CONV_TOL
+
+
 @pytest.mark.parametrize("name", ["fft64", "fft128"])
 def test_layer_phase_flags_reassemble_the_passes(name):
     """STOP_AFTER_TRANSFORMS, STOP_AFTER_CONTRACTION and START_FROM_SPECTRUM cut every pass into
