@@ -7,13 +7,18 @@
 // on FP32 CUDA cores, for operands in the convolution workspace's 4-bin blocks.
 //   few columns (n <= 8: updateOutput / updateGradInput of a shard of at most 8 images): the big
 //       operand A (the weight spectrum) streams through shared memory exactly once, every thread
-//       owns one row of m and half of the 4 bins and keeps n accumulators; 8 complex multiply-adds
-//       per 16 bytes of weights is below what the FP32 pipes sustain per byte of HBM, so the pass
-//       runs at the rate the weights arrive.  The tensor-core kernel spends a whole 128-row split
-//       and six padded MMAs on the same bytes (104 us against the 48 us the bytes take, FFT-64
-//       layer at 8 images).
+//       owns one row of m and half of the 4 bins and keeps n accumulators.  The tensor-core kernel
+//       spends a whole 128-row split and six padded MMAs on the same bytes.  Measured, FFT-64 layer
+//       (128 x 128 planes, 277 MB of weights) at 8 images: 69 us against 104 us; FFT-128 layer (96 x 96,
+//       613 MB) at 4 images: 106-115 us against 272 us (the bytes alone take 94 us at the copy rate).
+//       How A is described to the copy engine matters as much as the math: as 32-byte runs (one 4-bin
+//       element) the stream stops at 4.0-4.4 TB/s; described as 1 KB runs of 32 adjacent rows, or as
+//       128-byte runs of 4 adjacent k with the 128-byte swizzle, whichever the operand's strides allow,
+//       the same bytes arrive at 5.0-5.9 TB/s.
 //   short sum (k <= 8: accGradParameters of such a shard): a rank-k update whose only real traffic is
-//       the result; a thread keeps its row of A in registers and walks the columns.
+//       the result; a thread keeps its row of A in registers and walks the columns; the 8 lanes of a
+//       row write 16 consecutive bins, a whole 128-byte line (FFT-128 layer at 4 images: 118 us against
+//       179 us, 613 MB of result; with 32-byte pieces of lines the same kernel took 254 us).
 // Operands arrive by tensor copies (cp.async.bulk.tensor, zero fill outside the tensors, completion
 // on mbarriers with bounded waits); a lane pair holds the two 16-byte halves of an element, so every
 // store is a whole 32-byte sector.
@@ -30,6 +35,7 @@ namespace {
 
 constexpr int SM_ROWS = 128;  // rows of m per tile
 constexpr int SK = 4;         // values of k per stage
+constexpr int KB = 8;         // longest short sum
 enum : int { kErrSmallFull = 221, kErrSmallFree = 222, kErrSmallKWait = 223 };
 
 struct SmallArgs {
@@ -41,6 +47,7 @@ struct SmallArgs {
   float inv_norm;
   float sa;     // sign of A's imaginary part after folding both conjugations into A
   int conj_out; // conjugate the sum at the end (B was conjugated)
+  int a_mode;   // few columns, how A arrives: 0 = 32-byte runs, 1 = 1 KB runs of 32 rows, 2 = 128-byte runs of 4 k (swizzled)
 };
 
 __device__ __forceinline__ void tma_load4s(unsigned dst, const CUtensorMap* tm, int c0, int c1, int c2, int c3, unsigned bar) {
@@ -50,8 +57,46 @@ __device__ __forceinline__ void tma_load4s(unsigned dst, const CUtensorMap* tm, 
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load3s(unsigned dst, const CUtensorMap* tm, int c0, int c1, int c2, unsigned bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
 __device__ __forceinline__ float* d_addr(const SmallArgs& g, int x0, int m, int n) {
   return g.D + 2 * ((long long)(x0 / g.d_qb) * g.d_bs + (x0 % g.d_qb) + (long long)m * g.d_ms + (long long)n * g.d_ns);
+}
+
+// Complex multiply-add on the packed FP32 pipe (fma.rn.f32x2): with the element of the streamed
+// operand duplicated, (ar, ar) and (ai, ai), and the shared operand as it lies in memory, (br, bi),
+//   P += (ar, ar) * (br, bi),   Q += (ai, ai) * (br, bi),   sum = (P.x - Q.y, P.y + Q.x):
+// two instructions per complex product instead of four.
+struct Dup {
+  float2 re0, im0, re1, im1;  // bins 0 and 1 of a thread's 16 bytes
+};
+__device__ __forceinline__ Dup dup_of(const float4 a, float sa) {
+  Dup d;
+  d.re0 = make_float2(a.x, a.x), d.im0 = make_float2(a.y * sa, a.y * sa);
+  d.re1 = make_float2(a.z, a.z), d.im1 = make_float2(a.w * sa, a.w * sa);
+  return d;
+}
+struct Acc {
+  float2 p0, q0, p1, q1;
+};
+__device__ __forceinline__ void acc_zero(Acc& c) { c.p0 = c.q0 = c.p1 = c.q1 = make_float2(0.f, 0.f); }
+__device__ __forceinline__ void acc_mad(Acc& c, const Dup& a, const float4 b) {
+#ifndef FBFFT_SMALL_NOMATH
+  const float2 b0 = make_float2(b.x, b.y), b1 = make_float2(b.z, b.w);
+  c.p0 = __ffma2_rn(a.re0, b0, c.p0);
+  c.q0 = __ffma2_rn(a.im0, b0, c.q0);
+  c.p1 = __ffma2_rn(a.re1, b1, c.p1);
+  c.q1 = __ffma2_rn(a.im1, b1, c.q1);
+#endif
+}
+__device__ __forceinline__ float4 acc_value(const Acc& c, float inv_norm, float sgn) {
+  return make_float4((c.p0.x - c.q0.y) * inv_norm, (c.p0.y + c.q0.x) * sgn, (c.p1.x - c.q1.y) * inv_norm,
+                     (c.p1.y + c.q1.x) * sgn);
 }
 
 // ------------------------------------------------------------------ few columns
@@ -59,14 +104,16 @@ __device__ __forceinline__ float* d_addr(const SmallArgs& g, int x0, int m, int 
 // A [SK][128 rows][32 B], B [SK][NB columns][32 B].
 template <int NB>
 struct FewCfg {
-  static constexpr int NS = 5;
-  static constexpr int A_BYTES = SK * SM_ROWS * 32, B_BYTES = SK * NB * 32, STAGE = A_BYTES + ((B_BYTES + 127) / 128) * 128;
+  // 8 columns need 152 registers: one block of 10 stages per SM; 4 columns: two blocks of 5 stages
+  static constexpr int MINB = NB == 8 ? 1 : 2;
+  static constexpr int NS = MINB == 2 ? 5 : 10;
+  static constexpr int A_BYTES = SK * SM_ROWS * 32, B_BYTES = SK * NB * 32, STAGE = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
   static constexpr int SMEM = NS * STAGE + 256;
   static constexpr int THREADS = 9 * 32;
 };
 
 template <int NB>
-__global__ void __launch_bounds__(FewCfg<NB>::THREADS, 2) cgemm_fewcols_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(FewCfg<NB>::THREADS, FewCfg<NB>::MINB) cgemm_fewcols_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                                const __grid_constant__ CUtensorMap map_b,
                                                                                SmallArgs g) {
   using C = FewCfg<NB>;
@@ -94,37 +141,39 @@ __global__ void __launch_bounds__(FewCfg<NB>::THREADS, 2) cgemm_fewcols_kernel(c
           if (it >= (unsigned)C::NS && !mbar_wait(empty(st), ((it / C::NS) - 1) & 1, kErrSmallFree)) return;
           const unsigned dst = smem_u32(sm + st * C::STAGE);
           mbar_expect_tx(full(st), (unsigned)(C::A_BYTES + C::B_BYTES));
-          tma_load4s(dst, &map_a, 0, m0, s * SK, x0 / 4, full(st));
+          if (g.a_mode == 2) {
+            tma_load3s(dst, &map_a, s * SK * 8, m0, x0 / 4, full(st));
+          } else {
+            tma_load4s(dst, &map_a, 0, g.a_mode == 1 ? m0 / 32 : m0, s * SK, x0 / 4, full(st));
+          }
           tma_load4s(dst + C::A_BYTES, &map_b, 0, 0, s * SK, x0 / 4, full(st));
         }
       }
     }
     return;
   }
-  const int row = tid >> 1, half = tid & 1;
+  // modes 0 and 1: [k][row][32 B], a lane pair shares a row; mode 2: [row][4 k x 32 B] with the 16-byte
+  // pieces of a row XORed with (row % 8) (128-byte swizzle), 8 consecutive lanes take 8 consecutive rows
+  const bool kruns = g.a_mode == 2;
+  const int row = kruns ? ((tid & 7) | ((tid >> 4) << 3)) : tid >> 1, half = kruns ? (tid >> 3) & 1 : tid & 1;
+  const int a_base = kruns ? row * 128 : row * 32 + half * 16, a_step = kruns ? 0 : SM_ROWS * 32;
   unsigned it = 0;
   for (int t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
     const int x0 = (t / g.m_tiles) * 4, m0 = (t % g.m_tiles) * SM_ROWS;
-    float4 acc[NB];  // (bin0.re, bin0.im, bin1.re, bin1.im) of this thread's two bins, per column
+    Acc acc[NB];
 #pragma unroll
-    for (int n = 0; n < NB; ++n) acc[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int n = 0; n < NB; ++n) acc_zero(acc[n]);
     for (int s = 0; s < nsteps; ++s, ++it) {
       const int st = it % C::NS;
       if (!mbar_wait(full(st), (it / C::NS) & 1, kErrSmallFull)) return;
-      const unsigned char* sa = sm + st * C::STAGE + row * 32 + half * 16;
-      const unsigned char* sb = sm + st * C::STAGE + C::A_BYTES + half * 16;
+      const unsigned char* pa = sm + st * C::STAGE + a_base;
+      const unsigned char* pb = sm + st * C::STAGE + C::A_BYTES + half * 16;
 #pragma unroll
       for (int j = 0; j < SK; ++j) {
-        float4 a = *reinterpret_cast<const float4*>(sa + j * (SM_ROWS * 32));
-        a.y *= g.sa, a.w *= g.sa;
+        const int piece = kruns ? ((2 * j + half) ^ (row & 7)) << 4 : 0;
+        const Dup a = dup_of(*reinterpret_cast<const float4*>(pa + j * a_step + piece), g.sa);
 #pragma unroll
-        for (int n = 0; n < NB; ++n) {
-          const float4 b = *reinterpret_cast<const float4*>(sb + (j * NB + n) * 32);
-          acc[n].x += a.x * b.x - a.y * b.y;
-          acc[n].y += a.x * b.y + a.y * b.x;
-          acc[n].z += a.z * b.z - a.w * b.w;
-          acc[n].w += a.z * b.w + a.w * b.z;
-        }
+        for (int n = 0; n < NB; ++n) acc_mad(acc[n], a, *reinterpret_cast<const float4*>(pb + (j * NB + n) * 32));
       }
       __syncwarp();
       if (lane == 0) {
@@ -136,23 +185,29 @@ __global__ void __launch_bounds__(FewCfg<NB>::THREADS, 2) cgemm_fewcols_kernel(c
       const float sgn = g.conj_out ? -g.inv_norm : g.inv_norm;
 #pragma unroll
       for (int n = 0; n < NB; ++n) {
-        if (n < g.N)
-          *reinterpret_cast<float4*>(d_addr(g, x0, m, n) + 4 * half) =
-              make_float4(acc[n].x * g.inv_norm, acc[n].y * sgn, acc[n].z * g.inv_norm, acc[n].w * sgn);
+        if (n < g.N) *reinterpret_cast<float4*>(d_addr(g, x0, m, n) + 4 * half) = acc_value(acc[n], g.inv_norm, sgn);
       }
     }
   }
 }
 
 // ------------------------------------------------------------------ short sum
-// One tile: 128 rows of m x NC columns of n x 4 bins, all k (<= KB) at once.
-constexpr int KB = 8, NC = 64;
-constexpr int SHORT_A = KB * SM_ROWS * 32, SHORT_B = KB * NC * 32, SHORT_SMEM = SHORT_A + SHORT_B + 64;
+// One tile: 32 rows of m x 32 columns of n x 16 bins (4 blocks of 4), all k (<= KT) at once.  The
+// tensor copies order the dimensions (8 floats, 4-bin blocks, rows, k), so that shared memory holds
+// [k][row][4 blocks][32 B]: the 8 lanes (block, half) of a row read 128 contiguous bytes and write a
+// whole 128-byte line of the result (16 consecutive bins of one plane).
+constexpr int SR = 32, SC = 32;
+template <int KT>
+struct ShortCfg {
+  static constexpr int A_BYTES = KT * SR * 128, B_BYTES = KT * SC * 128, SMEM = A_BYTES + B_BYTES + 64;
+};
 
-__global__ void __launch_bounds__(256, 4) cgemm_shortsum_kernel(const __grid_constant__ CUtensorMap map_a,
+template <int KT>
+__global__ void __launch_bounds__(256, 2) cgemm_shortsum_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                 const __grid_constant__ CUtensorMap map_b, SmallArgs g) {
+  using C = ShortCfg<KT>;
   extern __shared__ __align__(1024) unsigned char sm[];
-  const unsigned bar = smem_u32(sm + SHORT_A + SHORT_B);
+  const unsigned bar = smem_u32(sm + C::A_BYTES + C::B_BYTES);
   const int tid = threadIdx.x;
   if (tid == 0) {
     mbar_init(bar, 1);
@@ -160,40 +215,32 @@ __global__ void __launch_bounds__(256, 4) cgemm_shortsum_kernel(const __grid_con
   }
   __syncthreads();
   const int t = blockIdx.x;
-  const int nt = t % g.n_tiles, mt = (t / g.n_tiles) % g.m_tiles, x0 = (t / (g.n_tiles * g.m_tiles)) * 4;
-  const int m0 = mt * SM_ROWS, n0 = nt * NC;
+  const int nt = t % g.n_tiles, mt = (t / g.n_tiles) % g.m_tiles, x0 = (t / (g.n_tiles * g.m_tiles)) * 16;
+  const int m0 = mt * SR, n0 = nt * SC;
   if (tid == 0) {
-    mbar_expect_tx(bar, (unsigned)(SHORT_A + SHORT_B));
-    tma_load4s(smem_u32(sm), &map_a, 0, m0, 0, x0 / 4, bar);
-    tma_load4s(smem_u32(sm + SHORT_A), &map_b, 0, n0, 0, x0 / 4, bar);
+    mbar_expect_tx(bar, (unsigned)(C::A_BYTES + C::B_BYTES));
+    tma_load4s(smem_u32(sm), &map_a, 0, x0 / 4, m0, 0, bar);
+    tma_load4s(smem_u32(sm + C::A_BYTES), &map_b, 0, x0 / 4, n0, 0, bar);
   }
   if (!mbar_wait(bar, 0, kErrSmallKWait)) return;
-  const int row = tid >> 1, half = tid & 1;
-  float4 a[KB];
+  const int row = tid >> 3, sub = tid & 7;  // sub = 2 * (block of 4 bins) + half
+  Dup a[KT];
 #pragma unroll
-  for (int k = 0; k < KB; ++k) {
-    a[k] = *reinterpret_cast<const float4*>(sm + (k * SM_ROWS + row) * 32 + half * 16);
-    a[k].y *= g.sa, a[k].w *= g.sa;
-  }
+  for (int k = 0; k < KT; ++k) a[k] = dup_of(*reinterpret_cast<const float4*>(sm + (k * SR + row) * 128 + sub * 16), g.sa);
   const int m = m0 + row;
   const float sgn = g.conj_out ? -g.inv_norm : g.inv_norm;
-  const unsigned char* sb = sm + SHORT_A + half * 16;
+  const unsigned char* pb = sm + C::A_BYTES + sub * 16;
   int ncols = g.N - n0;
-  if (ncols > NC) ncols = NC;
+  if (ncols > SC) ncols = SC;
+  if (m >= g.M) return;
+  float* dst = d_addr(g, x0, m, n0) + 4 * sub;  // 2 floats per bin, 2 bins per 16 bytes
 #pragma unroll 2
   for (int n = 0; n < ncols; ++n) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    Acc acc;
+    acc_zero(acc);
 #pragma unroll
-    for (int k = 0; k < KB; ++k) {
-      const float4 b = *reinterpret_cast<const float4*>(sb + (k * NC + n) * 32);
-      acc.x += a[k].x * b.x - a[k].y * b.y;
-      acc.y += a[k].x * b.y + a[k].y * b.x;
-      acc.z += a[k].z * b.z - a[k].w * b.w;
-      acc.w += a[k].z * b.w + a[k].w * b.z;
-    }
-    if (m < g.M)
-      *reinterpret_cast<float4*>(d_addr(g, x0, m, n0 + n) + 4 * half) =
-          make_float4(acc.x * g.inv_norm, acc.y * sgn, acc.z * g.inv_norm, acc.w * sgn);
+    for (int k = 0; k < KT; ++k) acc_mad(acc, a[k], *reinterpret_cast<const float4*>(pb + (k * SC + n) * 128));
+    *reinterpret_cast<float4*>(dst + 2 * (long long)n * g.d_ns) = acc_value(acc, g.inv_norm, sgn);
   }
 }
 
@@ -206,13 +253,56 @@ bool small_map(CUtensorMap* m, const float* p, long long rs, long long ks, long 
   return encode_tensor_map_f32(m, p, 4, dims, strides, box);
 }
 
+// the same tensor when its rows are adjacent planes (row stride 4 complex values) and a multiple of
+// 32: (256 floats = 32 rows, groups of 32 rows, k, blocks), box {256, box_rows / 32, box_k, 1} -- the
+// same bytes land in the same places, but the copy engine moves 1 KB runs instead of 32-byte ones
+bool small_map_row_runs(CUtensorMap* m, const float* p, long long ks, long long bs, int rows, int kcount, int X,
+                        int box_rows, int box_k) {
+  const unsigned long long dims[4] = {256ULL, (unsigned long long)(rows / 32), (unsigned long long)kcount,
+                                      (unsigned long long)(X / 4)};
+  const unsigned long long strides[3] = {1024ULL, (unsigned long long)ks * 8, (unsigned long long)bs * 8};
+  const unsigned box[4] = {256u, (unsigned)(box_rows / 32), (unsigned)box_k, 1u};
+  return encode_tensor_map_f32(m, p, 4, dims, strides, box);
+}
+
+// the same tensor when consecutive k are adjacent planes (k stride 4 complex values): (8 K floats, rows,
+// blocks), box {32 floats = 4 k, box_rows, 1}, 128-byte swizzle
+bool small_map_k_runs(CUtensorMap* m, const float* p, long long rs, long long bs, int rows, int kcount, int X, int box_rows) {
+  const unsigned long long dims[3] = {8ULL * (unsigned long long)kcount, (unsigned long long)rows, (unsigned long long)(X / 4)};
+  const unsigned long long strides[2] = {(unsigned long long)rs * 8, (unsigned long long)bs * 8};
+  const unsigned box[3] = {8u * SK, (unsigned)box_rows, 1u};
+  return encode_tensor_map_f32(m, p, 3, dims, strides, box, 128);
+}
+
+// the same tensor with the blocks second: (8 floats, blocks, rows, k), box {8, 4, box_rows, box_k}
+bool small_map_blocks_inner(CUtensorMap* m, const float* p, long long rs, long long ks, long long bs, int rows, int kcount,
+                            int X, int box_rows, int box_k) {
+  const unsigned long long dims[4] = {8ULL, (unsigned long long)(X / 4), (unsigned long long)rows, (unsigned long long)kcount};
+  const unsigned long long strides[3] = {(unsigned long long)bs * 8, (unsigned long long)rs * 8, (unsigned long long)ks * 8};
+  const unsigned box[4] = {8u, 4u, (unsigned)box_rows, (unsigned)box_k};
+  return encode_tensor_map_f32(m, p, 4, dims, strides, box);
+}
+
+template <int KT>
+int launch_shortsum(const CUtensorMap& ma, const CUtensorMap& mb, const SmallArgs& g, int blocks, cudaStream_t s) {
+  static bool configured[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaFuncSetAttribute(cgemm_shortsum_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ShortCfg<KT>::SMEM);
+    configured[dev] = true;
+  }
+  cgemm_shortsum_kernel<KT><<<blocks, 256, ShortCfg<KT>::SMEM, s>>>(ma, mb, g);
+  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+}
+
 }  // namespace
 
 // Operands in 4-bin blocks (a_qb = b_qb = 4), overwriting result, n <= 8 or k <= 8, 32-byte aligned D elements
 bool cgemm_small_supported(const float* a, const float* b, const float* d, long long d_ms, long long d_ns, long long d_bs,
                            int d_qb, int a_qb, int b_qb, int M, int N, int K, int X, bool accumulate) {
   if (accumulate || a_qb != 4 || b_qb != 4 || X % 4 != 0 || M < 1 || N < 1 || K < 1) return false;
-  if (!(N <= 8 || K <= KB)) return false;
+  if (!(N <= 8 || (K <= KB && X % 16 == 0 && d_qb % 16 == 0))) return false;
   if (d_qb < 4 || d_qb % 4 != 0 || d_ms % 2 != 0 || d_ns % 2 != 0 || d_bs % 2 != 0) return false;
   if (!aligned16(a) || !aligned16(b) || (reinterpret_cast<uintptr_t>(d) & 31u) != 0) return false;
   return true;
@@ -227,39 +317,48 @@ int cgemm_small(const float* a, long long a_rs, long long a_ks, bool conjA, cons
   // opA(a) opB(b): with B conjugated, sum_k opA(a) conj(b) = conj(sum_k conj(opA(a)) b)
   g.conj_out = conjB ? 1 : 0;
   g.sa = (conjA != conjB) ? -1.f : 1.f;
-  g.m_tiles = (M + SM_ROWS - 1) / SM_ROWS;
+  g.a_mode = 0;
   alignas(64) CUtensorMap ma, mb;
-  static bool configured[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(cgemm_fewcols_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FewCfg<4>::SMEM);
-    cudaFuncSetAttribute(cgemm_fewcols_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, FewCfg<8>::SMEM);
-    cudaFuncSetAttribute(cgemm_shortsum_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SHORT_SMEM);
-    configured[dev] = true;
-  }
   if (N <= 8) {
+    static bool configured[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaFuncSetAttribute(cgemm_fewcols_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, FewCfg<4>::SMEM);
+      cudaFuncSetAttribute(cgemm_fewcols_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, FewCfg<8>::SMEM);
+      configured[dev] = true;
+    }
     const int NB = N <= 4 ? 4 : 8;
-    if (!small_map(&ma, a, a_rs, a_ks, a_bs, M, K, X, SM_ROWS, SK) || !small_map(&mb, b, b_rs, b_ks, b_bs, N, K, X, NB, SK)) return -1;
+    g.a_mode = (a_rs == 4 && M % 32 == 0) ? 1 : (a_ks == 4 ? 2 : 0);
+    if (!(g.a_mode == 1   ? small_map_row_runs(&ma, a, a_ks, a_bs, M, K, X, SM_ROWS, SK)
+          : g.a_mode == 2 ? small_map_k_runs(&ma, a, a_rs, a_bs, M, K, X, SM_ROWS)
+                          : small_map(&ma, a, a_rs, a_ks, a_bs, M, K, X, SM_ROWS, SK)) ||
+        !small_map(&mb, b, b_rs, b_ks, b_bs, N, K, X, NB, SK))
+      return -1;
+    g.m_tiles = (M + SM_ROWS - 1) / SM_ROWS;
     g.n_tiles = 1;
     const long long total = (long long)g.m_tiles * (X / 4);
+    if (total > 0x7fffffffLL) return -1;
     g.total_tiles = (int)total;
-    const long long cap = 2LL * sm_count();
+    const long long cap = (long long)(NB == 8 ? FewCfg<8>::MINB : FewCfg<4>::MINB) * sm_count();
     const int grid = (int)(total < cap ? total : cap);
     if (NB == 4) {
       cgemm_fewcols_kernel<4><<<grid, FewCfg<4>::THREADS, FewCfg<4>::SMEM, s>>>(ma, mb, g);
     } else {
       cgemm_fewcols_kernel<8><<<grid, FewCfg<8>::THREADS, FewCfg<8>::SMEM, s>>>(ma, mb, g);
     }
-  } else {
-    if (!small_map(&ma, a, a_rs, a_ks, a_bs, M, K, X, SM_ROWS, KB) || !small_map(&mb, b, b_rs, b_ks, b_bs, N, K, X, NC, KB)) return -1;
-    g.n_tiles = (N + NC - 1) / NC;
-    const long long total = (long long)g.m_tiles * g.n_tiles * (X / 4);
-    if (total > 0x7fffffffLL) return -1;
-    g.total_tiles = (int)total;
-    cgemm_shortsum_kernel<<<(int)total, 256, SHORT_SMEM, s>>>(ma, mb, g);
+    return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
   }
-  return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+  const int KT = K <= 4 ? 4 : KB;
+  if (!small_map_blocks_inner(&ma, a, a_rs, a_ks, a_bs, M, K, X, SR, KT) ||
+      !small_map_blocks_inner(&mb, b, b_rs, b_ks, b_bs, N, K, X, SC, KT))
+    return -1;
+  g.m_tiles = (M + SR - 1) / SR;
+  g.n_tiles = (N + SC - 1) / SC;
+  const long long total = (long long)g.m_tiles * g.n_tiles * (X / 16);
+  if (total > 0x7fffffffLL) return -1;
+  g.total_tiles = (int)total;
+  return KT == 4 ? launch_shortsum<4>(ma, mb, g, (int)total, s) : launch_shortsum<KB>(ma, mb, g, (int)total, s);
 }
 
 int read_device_error_small() { return device_error_word_read(); }

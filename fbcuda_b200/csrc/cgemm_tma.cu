@@ -610,7 +610,7 @@ int launch_tma(const CUtensorMap& md, const CUtensorMap& ma, const CUtensorMap& 
 // fp32 tensor map without swizzle or interleave, zero fill outside the tensor (shared with the
 // transforms that stage zero-padded images by tensor copies); false when the driver lacks the encoder
 bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigned long long* dims,
-                           const unsigned long long* strides_bytes, const unsigned* box) {
+                           const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes) {
   EncodeTiledFn enc = encoder();
   if (!enc || rank < 1 || rank > 5) return false;
   cuuint64_t d[5], st[4];
@@ -618,8 +618,10 @@ bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigne
   for (int i = 0; i < rank; ++i) d[i] = dims[i], bx[i] = box[i], es[i] = 1;
   for (int i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
   return enc(static_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), d, st,
-             bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+             bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : (swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE),
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long long a_bs, const float* b, long long b_rs,

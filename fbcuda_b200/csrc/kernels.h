@@ -95,9 +95,10 @@ bool cgemm_tma_supported(const float* a, long long a_rs, long long a_ks, long lo
 int cgemm_tma(const float* a, long long a_rs, long long a_ks, bool conjA, const float* b, long long b_rs, long long b_ks,
               bool conjB, float* d, long long d_ms, long long d_ns, int M, int N, int K, int X, float inv_norm,
               bool accumulate, cudaStream_t s, long long a_bs, long long b_bs, long long d_bs, int a_qb, int b_qb, int d_qb);
-// fp32 tensor map (no swizzle, zero fill outside the tensor) into a 128-byte, 64-byte aligned buffer (cgemm_tma.cu)
+// fp32 tensor map (zero fill outside the tensor; swizzle 0, 32 or 128 bytes) into a 128-byte, 64-byte aligned buffer
+// (cgemm_tma.cu)
 bool encode_tensor_map_f32(void* map, const float* base, int rank, const unsigned long long* dims,
-                           const unsigned long long* strides_bytes, const unsigned* box);
+                           const unsigned long long* strides_bytes, const unsigned* box, int swizzle_bytes = 0);
 int read_device_error_tma();
 int clear_device_error_tma();
 // FP32 CUDA-core version for n <= 8 columns or k <= 8 terms, operands in 4-bin blocks, overwriting result (cgemm_small.cu)
