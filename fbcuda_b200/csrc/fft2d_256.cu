@@ -17,6 +17,15 @@
 //   columns  a warp takes 8 lines out[kx][*] (2 KB each, contiguous) through its shared-memory slot:
 //            bulk copies in, transform in registers, bulk copies out.
 // HBM traffic is twice the algorithmic bytes (the spectrum is written, read and written again).
+// Measured and dropped, 1024 images (forward / inverse, this design: 206 / 230 us):
+//   * both passes launched per chunk of 32..256 images so that the half-transformed chunk stays in L2:
+//     593..250 / 657..288 us (launch gaps and tails of the short kernels cost more than the traffic saves);
+//   * one pass by a cluster of 4 blocks per image (each block transforms 64 rows, parks them in its
+//     shared memory, gathers its 32 columns from all four through distributed shared memory): correct,
+//     HBM traffic halved (22 % of the DRAM peak), 243 / 282 us.  With 160 registers a thread and 66 KB a
+//     block only 12 warps fit an SM and either design issues 0.35 instructions per cycle and scheduler
+//     (stalls spread over remote loads, the shared-memory queue, barriers and fences): the two 64-point
+//     register transforms per thread bound the time, not the bytes.
 #include "coop_fft.cuh"
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "kernels.h"
@@ -339,262 +348,6 @@ __global__ void __launch_bounds__(kColsWarps * 32, 3) ifft256_rows_kernel(float*
   bulk_wait_read();
 }
 
-// ------------------------------------------------------------------ one pass: a cluster of 4 blocks per image
-// The image does not fit one SM, but it fits four: the 4 blocks of a cluster each transform 64 rows
-// (forward) or 32 + 1 lines (inverse) exactly as the first kernels above do, park their part in
-// their own shared memory, and after a cluster barrier every block gathers the lines of the second
-// dimension from all four shared memories (ld.shared::cluster), transforms them in registers and
-// stores the final result: the half-transformed image never travels to HBM.  A second cluster
-// barrier (arrive after the gather, wait after the transform) tells a block that its lines have been
-// read, after which it reuses them to stage the 2 KB bulk stores of its results.  No thread leaves
-// before the barriers: a wait that runs out records its code and the block carries on.
-constexpr int PZ2 = N256 + 1;  // pitch of the parked row transforms (odd: the gather of 8 columns x 4 line groups
-                               // falls on all banks)
-enum : int { kErrFusedRowsWait = 116, kErrFusedInvWait = 117 };
-
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ unsigned cluster_rank() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// address of this block's shared-memory location `saddr` inside block `rank` of the cluster
-__device__ __forceinline__ unsigned peer_addr(unsigned saddr, unsigned rank) {
-  unsigned r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ float2 ld_peer2(unsigned addr) {
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ float4 ld_peer4(unsigned addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-
-template <bool FULL>
-__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(kRowsThreads, 3)
-    fft256_fused_kernel(RealView in, float* __restrict__ out, long long out_sb, int padL, int padU) {
-  extern __shared__ __align__(16) float2 zs[];  // staged rows [32][PZ] / row transforms [32][PZ2] / results [32][PZ]
-  const unsigned bar = smem_u32(zs + kLinesPerBlock * PZ);
-  if (FULL) {
-    if (threadIdx.x == 0) mbar_init(bar, 1);
-    fence_async_smem();
-    __syncthreads();
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = lane / LP256, l = lane % LP256, line = warp * LP256 + l;
-  const int band = (int)cluster_rank();
-  const long long b = blockIdx.x / 4;
-  float2 lf[Q256];
-  lane_factors<Q256, false>(q, lf);
-  float2 a[R256];
-  {
-    // rows: as in fft256_rows_kernel
-    const int y0 = band * 2 * kLinesPerBlock + 2 * line;
-    const float* src = in.p + b * in.sb;
-    if constexpr (FULL) {
-      if (threadIdx.x == 0) mbar_expect_tx(bar, kLinesPerBlock * 2 * N256 * 4);
-      __syncthreads();
-      if (q == 0) bulk_g2s(smem_u32(zs + line * PZ), src + (long long)y0 * N256, 2 * N256 * 4, bar);
-      mbar_wait(bar, 0, kErrFusedRowsWait);  // (a wait that runs out leaves its code; the barriers below still run)
-      const float* r0 = reinterpret_cast<const float*>(zs + line * PZ) + P256 * q;
-#pragma unroll
-      for (int m = 0; m < Q256; ++m) {
-#pragma unroll
-        for (int j4 = 0; j4 < P256 / 4; ++j4) {
-          const float4 u = *reinterpret_cast<const float4*>(r0 + m * R256 + 4 * j4);
-          const float4 v = *reinterpret_cast<const float4*>(r0 + N256 + m * R256 + 4 * j4);
-          a[m * P256 + j4 * 4 + 0] = make_float2(u.x, v.x);
-          a[m * P256 + j4 * 4 + 1] = make_float2(u.y, v.y);
-          a[m * P256 + j4 * 4 + 2] = make_float2(u.z, v.z);
-          a[m * P256 + j4 * 4 + 3] = make_float2(u.w, v.w);
-        }
-      }
-    } else {
-      const unsigned ya = (unsigned)(y0 - padU), yb = (unsigned)(y0 + 1 - padU);
-      const bool oka = ya < (unsigned)in.h, okb = yb < (unsigned)in.h;
-      const float* r0 = src + (long long)ya * in.sy;
-      const float* r1 = src + (long long)yb * in.sy;
-#pragma unroll
-      for (int m = 0; m < Q256; ++m) {
-#pragma unroll
-        for (int jl = 0; jl < P256; ++jl) {
-          const unsigned x = (unsigned)(jl + P256 * q + R256 * m - padL);
-          const bool okx = x < (unsigned)in.w;
-          a[m * P256 + jl].x = (oka && okx) ? __ldg(r0 + (long long)x * in.sx) : 0.f;
-          a[m * P256 + jl].y = (okb && okx) ? __ldg(r1 + (long long)x * in.sx) : 0.f;
-        }
-      }
-    }
-    coop_fft<N256, R256, Q256, false>(a, q, lf);
-    __syncthreads();  // every staged row is in registers: the parked lines (other pitch) may overwrite them
-    static_for<R256>([&](auto kc) {
-      constexpr int k = decltype(kc)::value;
-      zs[line * PZ2 + Q256 * k + q] = a[brev(k, R256)];
-    });
-  }
-  cluster_arrive();
-  cluster_wait();
-  // columns: the cluster's 16 warps x 8 lane groups take bins kx = 1..127 and, in slot 0, bins 0 and 128
-  // together (both are transforms of real columns: c[y] = F_y[0] + i F_y[128]).  Element 64 m + 16 q + j
-  // of a column is row 2 (8 q + j / 2) + j % 2 of band m: the two rows of a parked line Z separate as
-  // A = (Z[kx] + conj Z[N-kx]) / 2, B = (Z[kx] - conj Z[N-kx]) / 2i.
-  const int slot = (band * 4 + warp) * LP256 + l;
-  const int kx = slot, kxm = slot == 0 ? N256 / 2 : N256 - slot;
-  {
-    const unsigned mine = smem_u32(zs);
-#pragma unroll
-    for (int m = 0; m < Q256; ++m) {
-      const unsigned base = peer_addr(mine, (unsigned)m);
-#pragma unroll
-      for (int jj = 0; jj < P256 / 2; ++jj) {
-        const int ln = (P256 / 2) * q + jj;
-        const float2 z = ld_peer2(base + (unsigned)(ln * PZ2 + kx) * 8u);
-        const float2 w = ld_peer2(base + (unsigned)(ln * PZ2 + kxm) * 8u);
-        if (slot == 0) {
-          a[m * P256 + 2 * jj] = make_float2(z.x, w.x);
-          a[m * P256 + 2 * jj + 1] = make_float2(z.y, w.y);
-        } else {
-          a[m * P256 + 2 * jj] = make_float2(0.5f * (z.x + w.x), 0.5f * (z.y - w.y));
-          a[m * P256 + 2 * jj + 1] = make_float2(0.5f * (z.y + w.y), 0.5f * (w.x - z.x));
-        }
-      }
-    }
-  }
-  cluster_arrive();  // this block has read what it needs of the other blocks' lines
-  coop_fft<N256, R256, Q256, false>(a, q, lf);
-  cluster_wait();    // ... and its own lines have been read by everyone: they become the staging area of the stores
-  float2* region = zs + line * PZ;
-  static_for<R256>([&](auto kc) {
-    constexpr int k = decltype(kc)::value;
-    region[Q256 * k + q] = a[brev(k, R256)];
-  });
-  fence_async_smem();
-  __syncwarp();
-  float* ob = out + b * out_sb;
-  if (lane < LP256 && slot != 0) {
-    bulk_s2g(ob + (long long)kx * (2 * N256), smem_u32(region), N256 * 8);
-    bulk_commit();
-  }
-  if (band == 0 && warp == 0) {
-    // slot 0 holds C = X0 + i X128: X0[k] = (C[k] + conj C[N-k]) / 2, X128[k] = (C[k] - conj C[N-k]) / 2i
-    const float2* c = zs;  // line 0 of this block
-#pragma unroll
-    for (int i = 0; i < N256 / 32; ++i) {
-      const int k = lane + 32 * i;
-      const float2 u = c[k], v = c[(N256 - k) & (N256 - 1)];
-      *reinterpret_cast<float2*>(ob + 2 * k) = make_float2(0.5f * (u.x + v.x), 0.5f * (u.y - v.y));
-      *reinterpret_cast<float2*>(ob + (long long)(N256 / 2) * (2 * N256) + 2 * k) = make_float2(0.5f * (u.y + v.y), 0.5f * (v.x - u.x));
-    }
-  }
-  bulk_wait_read();
-}
-
-__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(kRowsThreads, 3)
-    ifft256_fused_kernel(const float* __restrict__ in, long long in_sb, float* __restrict__ out) {
-  extern __shared__ __align__(16) float2 zs[];  // [33 lines][PZ], then the mbarrier
-  const unsigned bar = smem_u32(zs + kInvLines * PZ);
-  if (threadIdx.x == 0) mbar_init(bar, 1);
-  fence_async_smem();
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = lane / LP256, l = lane % LP256, line = warp * LP256 + l;
-  const int g = (int)cluster_rank();
-  const long long b = blockIdx.x / 4;
-  float2 lf[Q256];
-  lane_factors<Q256, true>(q, lf);
-  // lines kx = 32 g + line (and line 128 with g = 0) along ky, parked as T[kx][y] in natural order
-  auto transform = [&](int slot) {
-    float2 t[R256];
-    const float2* src = zs + slot * PZ + P256 * q;
-#pragma unroll
-    for (int m = 0; m < Q256; ++m) {
-#pragma unroll
-      for (int j2 = 0; j2 < P256 / 2; ++j2) {
-        const float4 u = *reinterpret_cast<const float4*>(src + R256 * m + 2 * j2);
-        t[m * P256 + 2 * j2] = make_float2(u.x, u.y);
-        t[m * P256 + 2 * j2 + 1] = make_float2(u.z, u.w);
-      }
-    }
-    coop_fft<N256, R256, Q256, true>(t, q, lf);
-    __syncwarp();  // the lanes of a line have read it
-    static_for<R256>([&](auto kc) {
-      constexpr int k = decltype(kc)::value;
-      zs[slot * PZ + Q256 * k + q] = t[brev(k, R256)];
-    });
-  };
-  {
-    const float* src = in + b * in_sb;
-    if (threadIdx.x == 0) mbar_expect_tx(bar, (kLinesPerBlock + (g == 0 ? 1 : 0)) * N256 * 8);
-    __syncthreads();
-    if (q == 0) bulk_g2s(smem_u32(zs + line * PZ), src + (long long)(g * kLinesPerBlock + line) * (2 * N256), N256 * 8, bar);
-    if (g == 0 && threadIdx.x == 1) bulk_g2s(smem_u32(zs + kLinesPerBlock * PZ), src + (long long)(N256 / 2) * (2 * N256), N256 * 8, bar);
-    mbar_wait(bar, 0, kErrFusedInvWait);  // (a wait that runs out leaves its code; the barriers below still run)
-    transform(line);
-    if (g == 0 && warp == 0) transform(kLinesPerBlock);  // every lane group of the warp works on line 128
-  }
-  cluster_arrive();
-  cluster_wait();
-  // rows y = 64 g + 2 line and y + 1 as one complex line C[kx] = G_y[kx] + i G_{y+1}[kx], extended to all
-  // 256 bins by C[256 - kx] = conj(G_y[kx]) + i conj(G_{y+1}[kx]); bins 0 and 128 are real for both rows.
-  // T[kx][y] and T[kx][y + 1] are 16 adjacent bytes of line kx, which block kx / 32 holds (128: block 0).
-  const int y = g * 2 * kLinesPerBlock + 2 * line;
-  float2 a[R256];
-  {
-    const unsigned mine = smem_u32(zs);
-#pragma unroll
-    for (int m = 0; m < Q256; ++m) {
-#pragma unroll
-      for (int jl = 0; jl < P256; ++jl) {
-        const int j = jl + P256 * q + R256 * m;
-        const int kx = m < Q256 / 2 ? j : N256 - j;  // 0..127, or 128..1 for the mirrored half
-        const unsigned owner = kx == N256 / 2 ? 0u : (unsigned)(kx / kLinesPerBlock);
-        const int slot = kx == N256 / 2 ? kLinesPerBlock : kx % kLinesPerBlock;
-        const float4 t = ld_peer4(peer_addr(mine, owner) + (unsigned)(slot * PZ + y) * 8u);  // u = (t.x, t.y), v = (t.z, t.w)
-        if (kx == 0 || kx == N256 / 2) {
-          a[m * P256 + jl] = make_float2(t.x, t.z);
-        } else if (m < Q256 / 2) {
-          a[m * P256 + jl] = make_float2(t.x - t.w, t.y + t.z);
-        } else {
-          a[m * P256 + jl] = make_float2(t.x + t.w, t.z - t.y);
-        }
-      }
-    }
-  }
-  cluster_arrive();  // this block has read what it needs of the other blocks' lines
-  coop_fft<N256, R256, Q256, true>(a, q, lf);
-  cluster_wait();    // ... and its own lines have been read by everyone: they become the staging area of the stores
-  float* oy = reinterpret_cast<float*>(zs + line * PZ);
-  static_for<R256>([&](auto kc) {
-    constexpr int k = decltype(kc)::value;
-    const float2 v = a[brev(k, R256)];
-    oy[Q256 * k + q] = v.x;
-    oy[N256 + Q256 * k + q] = v.y;
-  });
-  fence_async_smem();
-  __syncwarp();
-  if (lane < LP256) {
-    bulk_s2g(out + b * ((long long)N256 * N256) + (long long)y * N256, smem_u32(oy), N256 * 8);
-    bulk_commit();
-  }
-  bulk_wait_read();
-}
-
-// EXPERIMENT: environment switch between the two-pass kernels and the cluster kernels
-bool fused_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("FBFFT_B200_256_FUSED");
-    v = e ? atoi(e) : 1;
-  }
-  return v != 0;
-}
-
 }  // namespace
 
 bool fft2d_256_inverse_supported(const CplxView& in, const RealView& out, int B, int padL, int padU) {
@@ -614,15 +367,6 @@ int fft2d_256_inverse(const CplxView& in, const RealView& out, int B, cudaStream
     cudaFuncSetAttribute(ifft256_cols_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     cudaFuncSetAttribute(ifft256_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kColsSmem);
     configured[dev] = true;
-  }
-  if (fused_enabled() && B <= (1 << 28)) {
-    static bool fused_configured[64];
-    if (dev >= 0 && dev < 64 && !fused_configured[dev]) {
-      cudaFuncSetAttribute(ifft256_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      fused_configured[dev] = true;
-    }
-    ifft256_fused_kernel<<<4 * B, kRowsThreads, smem, s>>>(in.p, in.sb, out.p);
-    return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
   }
   const long long work = (long long)B * 4;
   const int cap = sm_count() * 3;
@@ -657,20 +401,6 @@ int fft2d_256_forward(const RealView& in, const CplxView& out, int B, int padL, 
   const int grid = work < cap ? (int)work : cap;
   const bool full = in.sx == 1 && in.sy == N256 && in.h == N256 && in.w == N256 && padL == 0 && padU == 0 &&
                     (in.sb % 4) == 0 && aligned16(in.p);
-  if (fused_enabled() && B <= (1 << 28)) {
-    static bool fused_configured[64];
-    if (dev >= 0 && dev < 64 && !fused_configured[dev]) {
-      cudaFuncSetAttribute(fft256_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      cudaFuncSetAttribute(fft256_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      fused_configured[dev] = true;
-    }
-    if (full) {
-      fft256_fused_kernel<true><<<4 * B, kRowsThreads, smem, s>>>(in, out.p, out.sb, padL, padU);
-    } else {
-      fft256_fused_kernel<false><<<4 * B, kRowsThreads, smem, s>>>(in, out.p, out.sb, padL, padU);
-    }
-    return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
-  }
   if (full) {
     fft256_rows_kernel<true><<<grid, kRowsThreads, smem, s>>>(in, out.p, out.sb, B, padL, padU);
   } else {
