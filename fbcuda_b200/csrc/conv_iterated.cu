@@ -1,8 +1,10 @@
 // FFTIteratedConvolution<8|16|32>: the reference's tile-list convolution entry
 // point (fbfft/FFTIteratedConvolution.cuh:624-755).  Like the reference's kernels
 // (:97-207, :254-363, :409-524) it needs no device memory besides its operands:
-// every spectrum is recomputed where it is used.  One warp produces one output
-// plane:
+// every spectrum is recomputed where it is used.  Two kernels: a block of 8 warps
+// produces a group of 4 x 4 output planes and shares the operand spectra inside the
+// group (iterated_grouped_kernel, further down; layers with at least 3 planes on
+// both sides of the group), or one warp produces one output plane:
 //   pass 0  out[tile][b][o] = sum_c  in[tile][b][c]  (x) conj(w[o][c])
 //   pass 1  in [tile][b][c] = sum_o  out[tile][b][o] (x) w[o][c]
 //   pass 2  w[o][c]         = scale * sum_tile,b in[tile][b][c] (x) conj(out[tile][b][o])
