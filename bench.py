@@ -328,7 +328,7 @@ def run_fft2d(args, world, rank, local):
     bounds = [(i * b // n_chunks, (i + 1) * b // n_chunks) for i in range(n_chunks)]
     side = [torch.cuda.Stream() for _ in range(3)]
 
-    def step_e2e():
+    def step_e2e(transform=True):
         cur = torch.cuda.current_stream()
         fork = torch.cuda.Event()
         fork.record(cur)
@@ -337,15 +337,19 @@ def run_fft2d(args, world, rank, local):
             st.wait_event(fork)
             with torch.cuda.stream(st):
                 x[lo:hi].copy_(xh[lo:hi], non_blocking=True)
-                fb.fft2d_r2c(n, x[lo:hi], spec[lo:hi])
+                if transform:
+                    fb.fft2d_r2c(n, x[lo:hi], spec[lo:hi])
                 sh[lo:hi].copy_(spec[lo:hi], non_blocking=True)
         for st in side:
             cur.wait_stream(st)
 
     ms_e2e = time_steps(step_e2e, max(2, args.steps // 4), 3, world)
+    # the same copies without the transform: what the host link alone allows in this pipeline
+    ms_copies = time_steps(lambda: step_e2e(False), max(2, args.steps // 4), 2, world)
     e2e = {"value": world * b * per_image / (ms_e2e / 1e3) / 1e9, "unit": "GB/s",
            "h2d_bytes_per_step": b * hw * hw * 4, "d2h_bytes_per_step": b * (n // 2 + 1) * n * 8,
-           "ms_per_step": ms_e2e, "pipeline": f"{n_chunks} chunks on {len(side)} streams (H2D, transform, D2H overlapped)"}
+           "ms_per_step": ms_e2e, "pipeline": f"{n_chunks} chunks on {len(side)} streams (H2D, transform, D2H overlapped)",
+           "copies_alone_gbs": world * b * per_image / (ms_copies / 1e3) / 1e9, "copies_alone_ms_per_step": ms_copies}
     del xh, sh
 
     peak, how = measured_peak_gbs()
