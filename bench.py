@@ -443,6 +443,29 @@ def run_extras(args, x, spec, n0, hw0):
         two_call[str(n)] = entry
         del x, buf, spec, mid, back
         torch.cuda.empty_cache()
+    # the same first call on zero-padded images (the convolution layers' 56x56 in 64 and 116x116 in 128), and
+    # 1-D signals that are windows of a wider matrix: what callers pass when their tensors are not N wide
+    padded = {}
+    for n, hwp in ((64, 56), (128, 116)):
+        b = GIB // 2 // (4 * n * n)
+        x = torch.rand((b, hwp, hwp), device="cuda") * 2 - 1
+        buf = torch.empty((b, n, n // 2 + 1, 2), device="cuda")
+        byts = 4 * hwp * hwp * b + 8 * n * (n // 2 + 1) * b
+        ms = time_steps(lambda: fb.fbfft2D(x, buf), 10, 3, 1)
+        padded[f"fbfft2D_real_to_buffer_{hwp}x{hwp}_in_{n}"] = {"us": ms * 1e3, "gbs": byts / ms / 1e6,
+                                                               "frac_of_measured": byts / ms / 1e6 / peak}
+        del x, buf
+        torch.cuda.empty_cache()
+    for n in (32, 128):
+        b = GIB // 2 // (4 * n)
+        wide = torch.rand((b, n + 16), device="cuda") * 2 - 1
+        spec = torch.empty((b, n // 2 + 1, 2), device="cuda")
+        byts = b * (4 * n + 8 * (n // 2 + 1))
+        ms = time_steps(lambda: fb.fbfft1D(wide[:, 8:8 + n], spec), 10, 3, 1)
+        padded[f"fbfft1D_N{n}_signal_stride_{n + 16}"] = {"us": ms * 1e3, "gbs": byts / ms / 1e6,
+                                                        "frac_of_measured": byts / ms / 1e6 / peak}
+        del wide, spec
+        torch.cuda.empty_cache()
     # the 1-D configuration as stated: 4096 signals of length 32, forward and inverse (launch-latency bound)
     x = torch.rand((4096, 32), device="cuda") * 2 - 1
     spec = torch.empty((4096, 17, 2), device="cuda")
@@ -481,7 +504,8 @@ def run_extras(args, x, spec, n0, hw0):
     torch.cuda.empty_cache()
     return {"inverse_of_default_workload": inverse, "sweep_1GiB": sweep, "sweep_1d_1GiB": sweep1d,
             "iterated_convolution_tile_list": iterated,
-            "two_call_protocol_512MiB": two_call, "config1_1d_4096x32": config1,
+            "two_call_protocol_512MiB": two_call, "padded_and_strided_inputs_512MiB": padded,
+            "config1_1d_4096x32": config1,
             f"storage_16bit_N{n0}_{hw0}x{hw0}": storage}
 
 

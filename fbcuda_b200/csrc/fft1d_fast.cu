@@ -57,10 +57,45 @@ constexpr int fast1d_smem() {
   return Fast1dCfg<N>::WARPS * (Fast1dCfg<N>::NSLOT * slot_floats<N>() * 4 + 16);
 }
 
+// RAGGED (forward): the rows are not one dense [rows][N] array but rows of w <= N floats inside a zero
+// canvas -- zero-padded images of the two-call protocol (row g is canvas row g % rpi of image g / rpi,
+// image row (g % rpi) - padU), signals with a stride between them, or a left pad.  Every lane brings in
+// its pair's two rows with one bulk copy each (w * 4 bytes, to column padL of its region) and writes the
+// zeros around them itself; rows outside the image are all zeros and cost no copy.
+struct RaggedIn {
+  const float* p;
+  long long sb, sy;  // floats between images and between image rows
+  int h, w, padL, padU, rpi;
+};
+
+// the two rows (2 * pair, 2 * pair + 1) of a pair: source pointers or nullptr for rows outside the image
+__device__ __forceinline__ void ragged_rows(const RaggedIn& rg, long long pair, const float* (&src)[2]) {
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const long long g = 2 * pair + r;
+    const long long b = g / rg.rpi;
+    const int y = (int)(g % rg.rpi) - rg.padU;
+    src[r] = ((unsigned)y < (unsigned)rg.h) ? rg.p + b * rg.sb + (long long)y * rg.sy : nullptr;
+  }
+}
+// zeros of a pair's region (two rows of N floats) that the copies leave untouched
+template <int N>
+__device__ __forceinline__ void ragged_zero(const RaggedIn& rg, float* region, const float* const (&src)[2]) {
+  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float4* row = reinterpret_cast<float4*>(region + r * N);
+    const int lo = src[r] ? rg.padL / 4 : N / 4, hi = src[r] ? (rg.padL + rg.w) / 4 : N / 4;
+    for (int i = 0; i < lo; ++i) row[i] = z;
+    for (int i = hi; i < N / 4; ++i) row[i] = z;
+  }
+}
+
 // INV = false: src real [tasks*64][N], dst complex [tasks*64][N/2+1][2];  INV = true: the reverse
-template <int N, bool INV>
+template <int N, bool INV, bool RAGGED = false>
 __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS)
-    fft1d_fast_kernel(const float* __restrict__ src, float* __restrict__ dst, long long tasks) {
+    fft1d_fast_kernel(const float* __restrict__ src, float* __restrict__ dst, long long tasks, RaggedIn rg) {
+  static_assert(!(RAGGED && INV), "ragged rows: forward only");
   constexpr int NSLOT = Fast1dCfg<N>::NSLOT, WARPS = Fast1dCfg<N>::WARPS;
   constexpr int PC = 2 * N + 4, PR = 2 * N;          // floats per pair: complex side, real side
   constexpr int PIN = INV ? PC : PR, POUT = INV ? PR : PC;
@@ -78,8 +113,27 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
   const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
   // PADIN (forward): every lane copies its own pair to the output pitch, so that the 16-byte reads
   // below are free of bank conflicts (the dense layout puts all lanes on the same four banks)
-  constexpr bool PADIN = !INV && Fast1dCfg<N>::PADIN;
+  constexpr bool PADIN = !INV && (Fast1dCfg<N>::PADIN || RAGGED);
   auto issue = [&](long long task, int slot) {
+    if constexpr (RAGGED) {
+      const float* rows[2];
+      ragged_rows(rg, task * 32 + lane, rows);
+      float* region = slots + slot * SLOT + lane * PC;
+      if (lane == 0) bulk_wait_read();  // the slot's previous result has left
+      __syncwarp();
+      ragged_zero<N>(rg, region, rows);
+      const unsigned mine = ((rows[0] ? 1u : 0u) + (rows[1] ? 1u : 0u)) * (unsigned)rg.w * 4u;
+      const unsigned total = __reduce_add_sync(0xffffffffu, mine);
+      if (lane == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bars + 8 * slot, total);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        if (rows[r]) bulk_g2s(smem_u32(region + r * N + rg.padL), rows[r], (unsigned)rg.w * 4u, bars + 8 * slot);
+      return;
+    }
     if (lane == 0) {
       bulk_wait_read();  // the slot's previous result has left
       fence_async_smem();
@@ -190,9 +244,10 @@ constexpr int coop1d_smem() {
   return 4 * ((32 / (N / 64)) * (2 * N + 4) * 4 + 16);
 }
 
-template <int N, bool INV>
+template <int N, bool INV, bool RAGGED = false>
 __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restrict__ src, float* __restrict__ dst,
-                                                            long long tasks) {
+                                                            long long tasks, RaggedIn rg) {
+  static_assert(!(RAGGED && INV), "ragged rows: forward only");
   constexpr int R = 64, Q = N / R, P = R / Q, LP = 32 / Q, WARPS = 4;
   constexpr int PC = 2 * N + 4, PR = 2 * N, SLOT = LP * PC;
   extern __shared__ __align__(16) float smem1d[];
@@ -207,6 +262,26 @@ __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restr
   lane_factors<Q, INV>(q, lf);
   const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
   auto issue = [&](long long task) {
+    if constexpr (RAGGED) {
+      const float* rows[2] = {nullptr, nullptr};
+      if (lane == 0) bulk_wait_read();  // the slot's previous result has left
+      __syncwarp();
+      if (lane < LP) {
+        ragged_rows(rg, task * LP + l, rows);
+        ragged_zero<N>(rg, region, rows);
+      }
+      const unsigned mine = lane < LP ? ((rows[0] ? 1u : 0u) + (rows[1] ? 1u : 0u)) * (unsigned)rg.w * 4u : 0u;
+      const unsigned total = __reduce_add_sync(0xffffffffu, mine);
+      if (lane == 0) {
+        fence_async_smem();
+        mbar_expect_tx(bar, total);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        if (rows[r]) bulk_g2s(smem_u32(region + r * N + rg.padL), rows[r], (unsigned)rg.w * 4u, bar);
+      return;
+    }
     if (INV && lane < LP) bulk_wait_read();  // this lane's pair has left the slot
     __syncwarp();
     if (lane == 0) {
@@ -306,32 +381,32 @@ __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restr
   bulk_wait_read();
 }
 
-template <int N, bool INV>
-int launch_coop1d(const float* src, float* dst, long long tasks, cudaStream_t s) {
+template <int N, bool INV, bool RAGGED = false>
+int launch_coop1d(const float* src, float* dst, long long tasks, cudaStream_t s, const RaggedIn& rg = RaggedIn{}) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(fft1d_coop_kernel<N, INV>, cudaFuncAttributeMaxDynamicSharedMemorySize, coop1d_smem<N>());
+    cudaFuncSetAttribute(fft1d_coop_kernel<N, INV, RAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, coop1d_smem<N>());
     configured[dev] = true;
   }
   const long long want = (tasks + 3) / 4, cap = (long long)sm_count() * 3;
-  fft1d_coop_kernel<N, INV><<<(int)(want < cap ? want : cap), 128, coop1d_smem<N>(), s>>>(src, dst, tasks);
+  fft1d_coop_kernel<N, INV, RAGGED><<<(int)(want < cap ? want : cap), 128, coop1d_smem<N>(), s>>>(src, dst, tasks, rg);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
-template <int N, bool INV>
-int launch_fast(const float* src, float* dst, long long tasks, cudaStream_t s) {
+template <int N, bool INV, bool RAGGED = false>
+int launch_fast(const float* src, float* dst, long long tasks, cudaStream_t s, const RaggedIn& rg = RaggedIn{}) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaFuncSetAttribute(fft1d_fast_kernel<N, INV>, cudaFuncAttributeMaxDynamicSharedMemorySize, fast1d_smem<N>());
+    cudaFuncSetAttribute(fft1d_fast_kernel<N, INV, RAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, fast1d_smem<N>());
     configured[dev] = true;
   }
   constexpr int W = Fast1dCfg<N>::WARPS;
   const long long want = (tasks + W - 1) / W, cap = (long long)sm_count() * Fast1dCfg<N>::BLOCKS;
-  fft1d_fast_kernel<N, INV><<<(int)(want < cap ? want : cap), W * 32, fast1d_smem<N>(), s>>>(src, dst, tasks);
+  fft1d_fast_kernel<N, INV, RAGGED><<<(int)(want < cap ? want : cap), W * 32, fast1d_smem<N>(), s>>>(src, dst, tasks, rg);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
@@ -357,6 +432,35 @@ int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long task
     case 64: return inverse ? launch_fast<64, true>(src, dst, tasks, s) : launch_fast<64, false>(src, dst, tasks, s);
     case 128: return inverse ? launch_coop1d<128, true>(src, dst, tasks, s) : launch_coop1d<128, false>(src, dst, tasks, s);
     case 256: return inverse ? launch_coop1d<256, true>(src, dst, tasks, s) : launch_coop1d<256, false>(src, dst, tasks, s);
+    default: return kUnsupportedSize;
+  }
+}
+
+// Rows of w floats (element stride 1) inside a zero canvas of N columns: image row y of image b at
+// p + b*sb + y*sy, placed at canvas row y + padU, column padL; rpi canvas rows per image (N for the 2-D
+// row pass, 1 for 1-D signals with h = 1).  Bulk copies need 16-byte units: w, padL, sb, sy multiples of 4
+// floats and p aligned.
+bool fft1d_fast_ragged_supported(int n, const float* p, long long sb, long long sy, int h, int w, int padL, int padU,
+                                 int rpi, const float* cplx) {
+  if (n != 8 && n != 16 && n != 32 && n != 64 && n != 128 && n != 256) return false;
+  if (w < 4 || w % 4 != 0 || padL < 0 || padL % 4 != 0 || padL + w > n || padU < 0 || h < 1 || rpi < 1) return false;
+  if (sb % 4 != 0 || (h > 1 && sy % 4 != 0)) return false;
+  return aligned16(p) && aligned16(cplx);
+}
+
+// transforms the first `tasks` * fft1d_fast_group(n) canvas rows into dst [rows][N/2+1][2] (contiguous)
+int fft1d_fast_ragged(int n, const float* p, long long sb, long long sy, int h, int w, int padL, int padU, int rpi,
+                      float* dst, long long tasks, cudaStream_t s) {
+  if (tasks <= 0) return kSuccess;
+  RaggedIn rg;
+  rg.p = p, rg.sb = sb, rg.sy = sy, rg.h = h, rg.w = w, rg.padL = padL, rg.padU = padU, rg.rpi = rpi;
+  switch (n) {
+    case 8: return launch_fast<8, false, true>(nullptr, dst, tasks, s, rg);
+    case 16: return launch_fast<16, false, true>(nullptr, dst, tasks, s, rg);
+    case 32: return launch_fast<32, false, true>(nullptr, dst, tasks, s, rg);
+    case 64: return launch_fast<64, false, true>(nullptr, dst, tasks, s, rg);
+    case 128: return launch_coop1d<128, false, true>(nullptr, dst, tasks, s, rg);
+    case 256: return launch_coop1d<256, false, true>(nullptr, dst, tasks, s, rg);
     default: return kUnsupportedSize;
   }
 }

@@ -312,6 +312,13 @@ int fft1d_forward(int n, const float* real, int rs0, int rs1, float* cplx, int c
     if (int rc = fft1d_fast(n, false, real, cplx, B / g, s)) return rc;
     if (done == B) return kSuccess;
     real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
+  } else if (B >= 64 && rs1 == 1 && cs2 == 1 && cs1 == 2 && cs0 == n + 2 &&
+             fft1d_fast_ragged_supported(n, real, rs0, 0, 1, n - padL, padL, 0, 1, cplx)) {
+    // a stride between the signals or a left pad (in 16-byte units): same kernels, one bulk copy per signal
+    const int g = fft1d_fast_group(n), done = (B / g) * g;
+    if (int rc = fft1d_fast_ragged(n, real, rs0, 0, 1, n - padL, padL, 0, 1, cplx, B / g, s)) return rc;
+    if (done == B) return kSuccess;
+    real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
   }
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;
@@ -350,6 +357,14 @@ int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, 
       buffer.sz == 1 && buffer.sc == 2 && buffer.sr == n + 2 && (B <= 1 || (in.sb == (long long)n * n && buffer.sb == (long long)n * (n + 2))) &&
       fft1d_fast_supported(n, in.p, n, 1, buffer.p, n + 2, 2, 1, 0)) {
     return fft1d_fast(n, false, in.p, buffer.p, (long long)B * n / fft1d_fast_group(n), s);
+  }
+  // zero-padded images (rows of whole 16-byte units) into the same contiguous buffer: the row pass is still a
+  // batch of B * N 1-D transforms, every canvas row fetched by one bulk copy of its w floats
+  if (n <= 256 && in.sx == 1 && !buffer.blk_planes && buffer.sz == 1 && buffer.sc == 2 && buffer.sr == n + 2 &&
+      (B <= 1 || buffer.sb == (long long)n * (n + 2)) && in.h <= n - padU && padU >= 0 &&
+      fft1d_fast_ragged_supported(n, in.p, in.sb, in.sy, in.h, in.w, padL, padU, n, buffer.p)) {
+    return fft1d_fast_ragged(n, in.p, in.sb, in.sy, in.h, in.w, padL, padU, n, buffer.p,
+                             (long long)B * n / fft1d_fast_group(n), s);
   }
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;

@@ -61,6 +61,12 @@ bool fft1d_fast_supported(int n, const float* real, long long rs0, int rs1, cons
                           int cs2, int padL);
 int fft1d_fast_group(int n);
 int fft1d_fast(int n, bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s);
+// forward transform of rows of w floats inside a zero canvas (padded images of the two-call protocol, strided or
+// left-padded 1-D signals): see fft1d_fast.cu
+bool fft1d_fast_ragged_supported(int n, const float* p, long long sb, long long sy, int h, int w, int padL, int padU,
+                                 int rpi, const float* cplx);
+int fft1d_fast_ragged(int n, const float* p, long long sb, long long sy, int h, int w, int padL, int padU, int rpi,
+                      float* dst, long long tasks, cudaStream_t s);
 int read_device_error_fft1d();
 int clear_device_error_fft1d();
 int read_device_error_256();

@@ -84,6 +84,27 @@ def test_strided_1d():
     assert float(out_big[:, 33:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("n", [8, 16, 32, 64, 128, 256])
+def test_strided_and_left_padded_1d_in_16_byte_units(n):
+    """Signals that are windows of a wider matrix (stride between signals) and a left pad, both in
+    16-byte units, with enough signals for whole warp tasks plus a tail."""
+    b = 64 * 5 + 9
+    rng = np.random.default_rng(n)
+    x = rng.uniform(-1, 1, (b, n)).astype(np.float32)
+    big = torch.zeros((b, n + 12), device="cuda")
+    big[:, 8:8 + n] = dev(x)
+    out = torch.full((b, n // 2 + 1, 2), 7.0, device="cuda")
+    assert fb.fbfft1D(big[:, 8:8 + n], out) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(out), orc.fbfft1d(x)) < FFT_TOL
+    # left pad of 4: the first n - 4 samples, shifted right by 4 inside a zero signal
+    out2 = torch.full((b, n // 2 + 1, 2), 7.0, device="cuda")
+    assert fb.fbfft1D(dev(x), out2, 4) == fb.ErrorCode.Success
+    shifted = np.zeros_like(x)
+    shifted[:, 4:] = x[:, :n - 4]
+    assert orc.rel_l2(host(out2), orc.fbfft1d(shifted)) < FFT_TOL
+    assert fb.device_status() == 0
+
+
 def test_1d_errors():
     with pytest.raises(fb.FbfftError) as e:
         fb.fbfft1D(torch.zeros((2, 512), device="cuda"), torch.zeros((2, 257, 2), device="cuda"))

@@ -37,6 +37,29 @@ def test_two_call_forward_and_inverse(n, b):
     assert orc.rel_l2(host(back), n * n * x.astype(np.float64)) < FFT_TOL
 
 
+@pytest.mark.parametrize("case", [
+    # n, h, w, padL, padU: rows of whole 16-byte units inside the zero canvas (the convolution layers' images)
+    (64, 56, 56, 0, 0), (64, 56, 56, 4, 3), (64, 20, 60, 0, 44), (128, 116, 116, 0, 0), (128, 116, 116, 8, 5),
+    (128, 1, 4, 124, 127), (256, 200, 224, 0, 0), (256, 250, 128, 16, 6)])
+@pytest.mark.parametrize("b", [1, 7])
+def test_two_call_forward_of_zero_padded_images(case, b):
+    """First call on padded images whose rows are whole 16-byte units: every canvas row arrives by one
+    bulk copy, the zeros around it are written on chip, rows outside the image cost no copy."""
+    n, h, w, pl, pu = case
+    rng = np.random.default_rng(sum(case) + b)
+    x = rng.uniform(-1, 1, (b, h, w)).astype(np.float32)
+    buf = torch.full((b, n, n // 2 + 1, 2), 7.0, device="cuda")
+    assert fb.fbfft2D(dev(x), buf, pl, pu) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(buf), orc.fbfft2d_rows(x, n, pl, pu)) < FFT_TOL
+    # an image that is a window of a larger tensor (row and image strides in 16-byte units)
+    big = torch.zeros((b, h + 3, w + 8), device="cuda")
+    big[:, 1:1 + h, 4:4 + w] = dev(x)
+    buf2 = torch.full((b, n, n // 2 + 1, 2), 7.0, device="cuda")
+    assert fb.fbfft2D(big[:, 1:1 + h, 4:4 + w], buf2, pl, pu) == fb.ErrorCode.Success
+    assert torch.equal(buf, buf2)
+    assert fb.device_status() == 0
+
+
 @pytest.mark.parametrize("n", [64, 128, 256])
 def test_two_call_forward_full_contiguous_images(n):
     """Contiguous N x N images without padding: the row pass runs as a batch of 1-D transforms."""
