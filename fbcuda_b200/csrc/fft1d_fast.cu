@@ -15,6 +15,9 @@
 //            leaves through one bulk store.
 //   inverse  the mirror image: one bulk load of 32 * 2*(N+2) floats, Z = A + iB rebuilt with its
 //            Hermitian half in registers, unnormalised inverse FFT, one bulk store of 64*N floats.
+// Rows that are narrower than N or not adjacent in memory (zero-padded images of the two-call row
+// pass, signals with a stride between them, a left pad; all in 16-byte units) take the RAGGED
+// variants of the same kernels: one bulk copy per row, the zeros around it written by the lane.
 // Leftover signals (B mod 64) and every other shape go through the shared-memory line kernels.
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "coop_fft.cuh"
