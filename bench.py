@@ -454,7 +454,13 @@ def run_extras(args, x, spec, n0, hw0):
         ms = time_steps(lambda: fb.fbfft2D(x, buf), 10, 3, 1)
         padded[f"fbfft2D_real_to_buffer_{hwp}x{hwp}_in_{n}"] = {"us": ms * 1e3, "gbs": byts / ms / 1e6,
                                                                "frac_of_measured": byts / ms / 1e6 / peak}
-        del x, buf
+        # last call of the inverse protocol with the crop back to hwp x hwp
+        mid = torch.rand((b, n, n, 2), device="cuda")     # only the first ceil(b / 2) slices are read
+        byts = 8 * n * n * ((b + 1) // 2) + 4 * hwp * hwp * b
+        ms = time_steps(lambda: fb.fbifft2D(mid, x), 10, 3, 1)
+        padded[f"fbifft2D_buffer_to_real_{hwp}x{hwp}_of_{n}"] = {"us": ms * 1e3, "gbs": byts / ms / 1e6,
+                                                                "frac_of_measured": byts / ms / 1e6 / peak}
+        del x, buf, mid
         torch.cuda.empty_cache()
     for n in (32, 128):
         b = GIB // 2 // (4 * n)

@@ -152,10 +152,17 @@ struct ColsInvCfg {
   static constexpr int BLOCKS = N == 64 ? 6 : 3;
 };
 
+// where the N x N result of an image goes: rows padU .. padU + h - 1, columns padL .. padL + w - 1 of it
+// are stored as the h x w image at out + b * sb + y * sy (all in 16-byte units); full images: h = w = N
+struct CropOut {
+  long long sb, sy;
+  int h, w, padL, padU;
+};
+
 template <int N>
 __global__ void __launch_bounds__(ColsInvCfg<N>::T, ColsInvCfg<N>::BLOCKS) cols_inv_kernel(const float* __restrict__ buf,
                                                                                           float* __restrict__ out,
-                                                                                          int B, int G) {
+                                                                                          int B, int G, CropOut crop) {
   using C = ColsInvCfg<N>;
   constexpr int R = C::R, Q = C::Q, P = R / Q, LP = 32 / Q, YB = C::YB, T = C::T, PT = C::PT;
   extern __shared__ __align__(16) float smf[];
@@ -208,8 +215,11 @@ __global__ void __launch_bounds__(ColsInvCfg<N>::T, ColsInvCfg<N>::BLOCKS) cols_
     __syncthreads();
     const bool two = p + G < B;
     for (int r = threadIdx.x; r < YB; r += T) {
-      bulk_s2g(out + (p * N + y0 + r) * (long long)N, smem_u32(tile_a + r * PT), N * 4);
-      if (two) bulk_s2g(out + ((p + G) * N + y0 + r) * (long long)N, smem_u32(tile_b + r * PT), N * 4);
+      const int y = y0 + r - crop.padU;  // row of the cropped image
+      if ((unsigned)y < (unsigned)crop.h) {
+        bulk_s2g(out + p * crop.sb + (long long)y * crop.sy, smem_u32(tile_a + r * PT + crop.padL), crop.w * 4);
+        if (two) bulk_s2g(out + (p + G) * crop.sb + (long long)y * crop.sy, smem_u32(tile_b + r * PT + crop.padL), crop.w * 4);
+      }
     }
     bulk_commit();
     bulk_wait_read();
@@ -218,7 +228,7 @@ __global__ void __launch_bounds__(ColsInvCfg<N>::T, ColsInvCfg<N>::BLOCKS) cols_
 }
 
 template <int N>
-int launch_cols_inv(const float* buf, float* out, int B, cudaStream_t s) {
+int launch_cols_inv(const float* buf, float* out, int B, const CropOut& crop, cudaStream_t s) {
   static bool configured[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -228,7 +238,7 @@ int launch_cols_inv(const float* buf, float* out, int B, cudaStream_t s) {
   }
   const int G = (B + 1) / 2;
   const long long work = (long long)G * (N / ColsInvCfg<N>::YB), cap = (long long)sm_count() * ColsInvCfg<N>::BLOCKS;
-  cols_inv_kernel<N><<<(int)(work < cap ? work : cap), ColsInvCfg<N>::T, ColsInvCfg<N>::SMEM, s>>>(buf, out, B, G);
+  cols_inv_kernel<N><<<(int)(work < cap ? work : cap), ColsInvCfg<N>::T, ColsInvCfg<N>::SMEM, s>>>(buf, out, B, G, crop);
   return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
 }
 
@@ -366,16 +376,20 @@ int fft2d_cols_fast(int n, const CplxView& buffer, const CplxView& dst, int B, c
 }
 
 // contiguous [G][N][N][2] buffer and contiguous [B][N][N] images, 16-byte aligned, no crop
+// contiguous buffer; output images (full or cropped) with rows, strides and pads in 16-byte units
 bool fft2d_cols_inv_fast_supported(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU) {
   if (n != 64 && n != 128) return false;
-  if (buffer.blk_planes || buffer.sz != 1 || padL != 0 || padU != 0) return false;
-  return buffer.sc == 2 && buffer.sr == 2 * n && (B <= 2 || buffer.sb == 2LL * n * n) && out.h == n && out.w == n &&
-         out.sx == 1 && out.sy == n && (B <= 1 || out.sb == (long long)n * n) && aligned16(buffer.p) && aligned16(out.p);
+  if (buffer.blk_planes || buffer.sz != 1 || padL < 0 || padU < 0) return false;
+  if (!(buffer.sc == 2 && buffer.sr == 2 * n && (B <= 2 || buffer.sb == 2LL * n * n) && aligned16(buffer.p))) return false;
+  return out.sx == 1 && out.w >= 4 && out.w % 4 == 0 && padL % 4 == 0 && padL + out.w <= n && out.h >= 1 &&
+         padU + out.h <= n && out.sy % 4 == 0 && (B <= 1 || out.sb % 4 == 0) && aligned16(out.p);
 }
 
-int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, cudaStream_t s) {
-  if (n == 64) return launch_cols_inv<64>(buffer.p, out.p, B, s);
-  return launch_cols_inv<128>(buffer.p, out.p, B, s);
+int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
+  CropOut crop;
+  crop.sb = out.sb, crop.sy = out.sy, crop.h = out.h, crop.w = out.w, crop.padL = padL, crop.padU = padU;
+  if (n == 64) return launch_cols_inv<64>(buffer.p, out.p, B, crop, s);
+  return launch_cols_inv<128>(buffer.p, out.p, B, crop, s);
 }
 
 // contiguous [B][N/2+1][N][2] spectra and contiguous [.][N][N][2] buffer, 16-byte aligned

@@ -454,7 +454,7 @@ int fft2d_large_rows_inverse(int n, const CplxView& src, const CplxView& buffer,
 int fft2d_large_cols_inverse(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU,
                              cudaStream_t s) {
   if (n < 64) return kUnsupportedSize;
-  if (fft2d_cols_inv_fast_supported(n, buffer, out, B, padL, padU)) return fft2d_cols_inv_fast(n, buffer, out, B, s);
+  if (fft2d_cols_inv_fast_supported(n, buffer, out, B, padL, padU)) return fft2d_cols_inv_fast(n, buffer, out, B, padL, padU, s);
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;
     if constexpr (N >= 64) {

@@ -42,7 +42,7 @@ int fft2d_large_rows_forward(int n, const RealView& in, const CplxView& buffer, 
 bool fft2d_cols_fast_supported(int n, const CplxView& buffer, const CplxView& dst, int B);
 int fft2d_cols_fast(int n, const CplxView& buffer, const CplxView& dst, int B, cudaStream_t s);
 bool fft2d_cols_inv_fast_supported(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU);
-int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, cudaStream_t s);
+int fft2d_cols_inv_fast(int n, const CplxView& buffer, const RealView& out, int B, int padL, int padU, cudaStream_t s);
 bool fft2d_rows_inv_fast_supported(int n, const CplxView& src, const CplxView& buffer, int B);
 int fft2d_rows_inv_fast(int n, const CplxView& src, const CplxView& buffer, int B, cudaStream_t s);
 int read_device_error_cols();

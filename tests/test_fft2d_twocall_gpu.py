@@ -60,6 +60,31 @@ def test_two_call_forward_of_zero_padded_images(case, b):
     assert fb.device_status() == 0
 
 
+@pytest.mark.parametrize("case", [
+    # n, h, w, padL, padU: the last call of the inverse protocol crops to images in 16-byte units
+    (64, 56, 56, 0, 0), (64, 56, 56, 4, 3), (64, 9, 60, 0, 55), (128, 116, 116, 0, 0), (128, 116, 116, 8, 5),
+    (128, 1, 4, 124, 127)])
+@pytest.mark.parametrize("b", [1, 2, 7])
+def test_two_call_inverse_crops_in_16_byte_units(case, b):
+    n, h, w, pl, pu = case
+    rng = np.random.default_rng(sum(case) + 31 * b)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)    # a full canvas: the crop keeps a window of it
+    spec = orc.fbfft2d(x, n, 0, 0).astype(np.float32)
+    mid = torch.zeros((b, n, n, 2), device="cuda")
+    assert fb.fbifft2D_c2c(dev(spec), mid) == fb.ErrorCode.Success
+    back = torch.full((b, h, w), 7.0, device="cuda")
+    assert fb.fbifft2D(mid, back, pl, pu) == fb.ErrorCode.Success
+    want = n * n * x.astype(np.float64)[:, pu:pu + h, pl:pl + w]
+    assert orc.rel_l2(host(back), want) < FFT_TOL
+    # the same into a window of a larger tensor: what lies around the window stays untouched
+    big = torch.full((b, h + 2, w + 8), 7.0, device="cuda")
+    assert fb.fbifft2D(mid, big[:, 1:1 + h, 4:4 + w], pl, pu) == fb.ErrorCode.Success
+    assert torch.equal(big[:, 1:1 + h, 4:4 + w], back)
+    big[:, 1:1 + h, 4:4 + w] = 7.0
+    assert float((big - 7.0).abs().max()) == 0.0
+    assert fb.device_status() == 0
+
+
 @pytest.mark.parametrize("n", [64, 128, 256])
 def test_two_call_forward_full_contiguous_images(n):
     """Contiguous N x N images without padding: the row pass runs as a batch of 1-D transforms."""
