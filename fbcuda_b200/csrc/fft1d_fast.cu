@@ -17,7 +17,8 @@
 //            Hermitian half in registers, unnormalised inverse FFT, one bulk store of 64*N floats.
 // Rows that are narrower than N or not adjacent in memory (zero-padded images of the two-call row
 // pass, signals with a stride between them, a left pad; all in 16-byte units) take the RAGGED
-// variants of the same kernels: one bulk copy per row, the zeros around it written by the lane.
+// variants of the same kernels: one bulk copy per row, the zeros around it written by the lane
+// (forward); one bulk store per row of the columns that are kept (inverse).
 // Leftover signals (B mod 64) and every other shape go through the shared-memory line kernels.
 #include "fft2d_small.cuh"  // bulk-copy / mbarrier helpers
 #include "coop_fft.cuh"
@@ -98,7 +99,6 @@ __device__ __forceinline__ void ragged_zero(const RaggedIn& rg, float* region, c
 template <int N, bool INV, bool RAGGED = false>
 __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS)
     fft1d_fast_kernel(const float* __restrict__ src, float* __restrict__ dst, long long tasks, RaggedIn rg) {
-  static_assert(!(RAGGED && INV), "ragged rows: forward only");
   constexpr int NSLOT = Fast1dCfg<N>::NSLOT, WARPS = Fast1dCfg<N>::WARPS;
   constexpr int PC = 2 * N + 4, PR = 2 * N;          // floats per pair: complex side, real side
   constexpr int PIN = INV ? PC : PR, POUT = INV ? PR : PC;
@@ -118,7 +118,11 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
   // below are free of bank conflicts (the dense layout puts all lanes on the same four banks)
   constexpr bool PADIN = !INV && (Fast1dCfg<N>::PADIN || RAGGED);
   auto issue = [&](long long task, int slot) {
-    if constexpr (RAGGED) {
+    if constexpr (RAGGED && INV) {
+      bulk_wait_read();  // this lane's rows of the slot's previous result have left
+      __syncwarp();
+    }
+    if constexpr (RAGGED && !INV) {
       const float* rows[2];
       ragged_rows(rg, task * 32 + lane, rows);
       float* region = slots + slot * SLOT + lane * PC;
@@ -226,13 +230,21 @@ __global__ void __launch_bounds__(Fast1dCfg<N>::WARPS * 32, Fast1dCfg<N>::BLOCKS
     }
     fence_async_smem();
     __syncwarp();
-    if (lane == 0) {
+    if constexpr (RAGGED && INV) {
+      // every lane stores columns padL .. padL + w - 1 of its pair's two rows where the rows live
+      const float* rows[2];
+      ragged_rows(rg, t * 32 + lane, rows);
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        if (rows[r]) bulk_s2g(const_cast<float*>(rows[r]), smem_u32(base + lane * PR + r * N + rg.padL), (unsigned)rg.w * 4u);
+      bulk_commit();
+    } else if (lane == 0) {
       bulk_s2g(dst + t * (32 * POUT), smem_u32(base), 32 * POUT * 4);
       bulk_commit();
     }
     if (NSLOT == 1 && t + nw < tasks) issue(t + nw, 0);
   }
-  if (lane == 0) bulk_wait_read();
+  bulk_wait_read();
 }
 
 // ---- N = 128, 256: a line shared by Q = N/64 lanes (coop_fft.cuh), 32/Q pairs per warp ------------
@@ -250,7 +262,6 @@ constexpr int coop1d_smem() {
 template <int N, bool INV, bool RAGGED = false>
 __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restrict__ src, float* __restrict__ dst,
                                                             long long tasks, RaggedIn rg) {
-  static_assert(!(RAGGED && INV), "ragged rows: forward only");
   constexpr int R = 64, Q = N / R, P = R / Q, LP = 32 / Q, WARPS = 4;
   constexpr int PC = 2 * N + 4, PR = 2 * N, SLOT = LP * PC;
   extern __shared__ __align__(16) float smem1d[];
@@ -265,7 +276,7 @@ __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restr
   lane_factors<Q, INV>(q, lf);
   const long long gw = (long long)blockIdx.x * WARPS + warp, nw = (long long)gridDim.x * WARPS;
   auto issue = [&](long long task) {
-    if constexpr (RAGGED) {
+    if constexpr (RAGGED && !INV) {
       const float* rows[2] = {nullptr, nullptr};
       if (lane == 0) bulk_wait_read();  // the slot's previous result has left
       __syncwarp();
@@ -372,7 +383,15 @@ __global__ void __launch_bounds__(128, 3) fft1d_coop_kernel(const float* __restr
     __syncwarp();
     if (INV) {
       if (lane < LP) {
-        bulk_s2g(dst + (t * LP + l) * PR, smem_u32(region), PR * 4);
+        if constexpr (RAGGED) {
+          const float* rows[2];
+          ragged_rows(rg, t * LP + l, rows);
+#pragma unroll
+          for (int r = 0; r < 2; ++r)
+            if (rows[r]) bulk_s2g(const_cast<float*>(rows[r]), smem_u32(region + r * N + rg.padL), (unsigned)rg.w * 4u);
+        } else {
+          bulk_s2g(dst + (t * LP + l) * PR, smem_u32(region), PR * 4);
+        }
         bulk_commit();
       }
     } else if (lane == 0) {
@@ -464,6 +483,24 @@ int fft1d_fast_ragged(int n, const float* p, long long sb, long long sy, int h, 
     case 64: return launch_fast<64, false, true>(nullptr, dst, tasks, s, rg);
     case 128: return launch_coop1d<128, false, true>(nullptr, dst, tasks, s, rg);
     case 256: return launch_coop1d<256, false, true>(nullptr, dst, tasks, s, rg);
+    default: return kUnsupportedSize;
+  }
+}
+
+// the inverse: src complex [rows][N/2+1][2] (contiguous); columns padL .. padL + w - 1 of every transformed
+// row go to the row's place in the real tensor described as above
+int fft1d_fast_ragged_inverse(int n, const float* src, float* p, long long sb, long long sy, int h, int w, int padL,
+                              int padU, int rpi, long long tasks, cudaStream_t s) {
+  if (tasks <= 0) return kSuccess;
+  RaggedIn rg;
+  rg.p = p, rg.sb = sb, rg.sy = sy, rg.h = h, rg.w = w, rg.padL = padL, rg.padU = padU, rg.rpi = rpi;
+  switch (n) {
+    case 8: return launch_fast<8, true, true>(src, nullptr, tasks, s, rg);
+    case 16: return launch_fast<16, true, true>(src, nullptr, tasks, s, rg);
+    case 32: return launch_fast<32, true, true>(src, nullptr, tasks, s, rg);
+    case 64: return launch_fast<64, true, true>(src, nullptr, tasks, s, rg);
+    case 128: return launch_coop1d<128, true, true>(src, nullptr, tasks, s, rg);
+    case 256: return launch_coop1d<256, true, true>(src, nullptr, tasks, s, rg);
     default: return kUnsupportedSize;
   }
 }

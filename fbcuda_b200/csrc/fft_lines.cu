@@ -337,6 +337,14 @@ int fft1d_inverse(int n, const float* cplx, int cs0, int cs1, int cs2, float* re
     if (int rc = fft1d_fast(n, true, cplx, real, B / g, s)) return rc;
     if (done == B) return kSuccess;
     real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
+  } else if (B >= 64 && rs1 == 1 && cs2 == 1 && cs1 == 2 && cs0 == n + 2 &&
+             fft1d_fast_ragged_supported(n, real, rs0, 0, 1, n - padL, padL, 0, 1, cplx)) {
+    // a stride between the signals or a left pad (in 16-byte units): x = padL .. N - 1 of every result goes to
+    // the start of its row
+    const int g = fft1d_fast_group(n), done = (B / g) * g;
+    if (int rc = fft1d_fast_ragged_inverse(n, cplx, real, rs0, 0, 1, n - padL, padL, 0, 1, B / g, s)) return rc;
+    if (done == B) return kSuccess;
+    real += (long long)done * rs0, cplx += (long long)done * cs0, B -= done;
   }
   return dispatch_size(n, [&](auto nc) {
     constexpr int N = decltype(nc)::value;

@@ -67,6 +67,8 @@ bool fft1d_fast_ragged_supported(int n, const float* p, long long sb, long long 
                                  int rpi, const float* cplx);
 int fft1d_fast_ragged(int n, const float* p, long long sb, long long sy, int h, int w, int padL, int padU, int rpi,
                       float* dst, long long tasks, cudaStream_t s);
+int fft1d_fast_ragged_inverse(int n, const float* src, float* p, long long sb, long long sy, int h, int w, int padL,
+                              int padU, int rpi, long long tasks, cudaStream_t s);
 int read_device_error_fft1d();
 int clear_device_error_fft1d();
 int read_device_error_256();

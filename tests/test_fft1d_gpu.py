@@ -102,6 +102,16 @@ def test_strided_and_left_padded_1d_in_16_byte_units(n):
     shifted = np.zeros_like(x)
     shifted[:, 4:] = x[:, :n - 4]
     assert orc.rel_l2(host(out2), orc.fbfft1d(shifted)) < FFT_TOL
+    # inverse into a window of a wider matrix, and with a left pad (x = 4 .. n - 1 land at the row's start)
+    wide = torch.full((b, n + 12), 7.0, device="cuda")
+    assert fb.fbifft1D(wide[:, 8:8 + n], out) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(wide[:, 8:8 + n]), n * x.astype(np.float64)) < FFT_TOL
+    wide[:, 8:8 + n] = 7.0
+    assert float((wide - 7.0).abs().max()) == 0.0
+    back = torch.full((b, n), 7.0, device="cuda")
+    assert fb.fbifft1D(back, out, 4) == fb.ErrorCode.Success
+    assert orc.rel_l2(host(back[:, :n - 4]), n * x.astype(np.float64)[:, 4:]) < FFT_TOL
+    assert float((back[:, n - 4:] - 7.0).abs().max()) == 0.0
     assert fb.device_status() == 0
 
 
