@@ -301,17 +301,44 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
         a1 = make_float2(0.5f * (u.z + v.z), 0.5f * (u.w - v.w)), b1 = make_float2(0.5f * (u.w + v.w), 0.5f * (v.z - u.z));
       };
       if constexpr (SMALLW) {
-        // only canvas columns 0..15 are non-zero, and no column has a partner in the second half
+        // Only canvas columns 0..15 are non-zero (and no column has a partner in the second half): a
+        // 128-point transform with 16 inputs is 8 independent 16-point transforms,
+        //   X[8 m + s] = sum_n (x[n] w128^(n s)) w16^(n m),  s = 0..7,
+        // four per lane of the line's pair (s = 4 q + i), no exchange between the lanes: half the
+        // instructions of the 64-point transform per lane plus the radix-2 step and its shuffles.
+        static_assert(!SMALLW || (N == 128 && Q == 2), "pruned rows: N = 128");
+        float2 x[16];
 #pragma unroll
-        for (int i = 0; i < R; ++i) a[i] = make_float2(0.f, 0.f);
-        if (q == 0) {
-#pragma unroll
-          for (int p = 0; p < 16; p += 2) {
-            const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
-            float2 b0, b1;
-            take(u, v, a[p], a[p + 1], b0, b1);
-          }
+        for (int p = 0; p < 16; p += 2) {
+          const float4 u = *reinterpret_cast<const float4*>(row1 + p), v = *reinterpret_cast<const float4*>(row2 + p);
+          float2 b0, b1;
+          take(u, v, x[p], x[p + 1], b0, b1);
         }
+        if (q == 1) {  // s = 4 + i: the factor w128^(4 n) = w32^n of the lane
+          static_for<16>([&](auto nc) {
+            constexpr int n = decltype(nc)::value;
+            x[n] = mul_tw<n, 32, false>(x[n]);
+          });
+        }
+        block_sync<T>();  // every lane has read its part of mid: the tile may overwrite it
+        float2* direct = (r == 0) ? vsd : tile + r;
+        float2* mirror = (r == 0) ? vsm : tile + (N - r);
+        static_for<4>([&](auto ic) {
+          constexpr int i = decltype(ic)::value;
+          float2 t[16];
+          static_for<16>([&](auto nc) {
+            constexpr int n = decltype(nc)::value;
+            t[n] = mul_tw<n * i, N, false>(x[n]);
+          });
+          fft_bitrev<16, false, true>(t);
+          static_for<16>([&](auto mc) {
+            constexpr int m = decltype(mc)::value;
+            const int kx = 8 * m + 4 * q + i;
+            const float2 v = t[brev(m, 16)];
+            if (kx <= H) direct[kx * PO] = v;
+            if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
+          });
+        });
       } else if constexpr (Q == 1) {
 #pragma unroll
         for (int p = 0; p < H; p += 2) {
@@ -329,24 +356,26 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           }
         }
       }
-      coop_fft<N, R, Q, false, true>(a, q, lf);
-      block_sync<T>();  // every lane has read its part of mid: the tile may overwrite it
       // Row r > 0 scatters F[r][kx] to tile[kx][r] (kx <= H) and its Hermitian mirror
       // conj(F[r][kx]) to tile[(N-kx)%N][N-r] (kx >= H or kx == 0).  The packed row 0 does
       // the same into the two halves of the scratch row: vsd[kx] = V[kx], vsm[j] = conj(V[(N-j)%N]).
-      float2* direct = (r == 0) ? vsd : tile + r;
-      float2* mirror = (r == 0) ? vsm : tile + (N - r);
-      static_for<R>([&](auto kc) {
-        constexpr int k = decltype(kc)::value;
-        const int kx = Q * k + q;
-        const float2 v = a[brev(k, R)];
-        if (Q * k + Q - 1 <= H || kx <= H) {
-          if (kx <= H) direct[kx * PO] = v;
-        }
-        if (Q * k >= H - (Q - 1) || k == 0) {
-          if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
-        }
-      });
+      if constexpr (!SMALLW) {
+        coop_fft<N, R, Q, false, true>(a, q, lf);
+        block_sync<T>();  // every lane has read its part of mid: the tile may overwrite it
+        float2* direct = (r == 0) ? vsd : tile + r;
+        float2* mirror = (r == 0) ? vsm : tile + (N - r);
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          const int kx = Q * k + q;
+          const float2 v = a[brev(k, R)];
+          if (Q * k + Q - 1 <= H || kx <= H) {
+            if (kx <= H) direct[kx * PO] = v;
+          }
+          if (Q * k >= H - (Q - 1) || k == 0) {
+            if (kx >= H || kx == 0) mirror[((N - kx) & (N - 1)) * PO] = make_float2(v.x, -v.y);
+          }
+        });
+      }
     }
     block_sync<T>();
     // rows ky = 0 and N/2 from the packed row: V = F[0] + i F[N/2]
@@ -392,7 +421,7 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
   constexpr int R = CoopCfg<N>::R, Q = CoopCfg<N>::Q, P = R / Q, LP = 32 / Q;
   constexpr int PM = CoopCfg<N>::PM, PO = CoopCfg<N>::PO;
   constexpr int H = N / 2, T = H * Q;
-  extern __shared__ __align__(16) float2 smem[];
+  extern __shared__ __align__(128) float2 smem[];
   constexpr int REGION = (H + 1) * PO > N * PM ? (H + 1) * PO : N * PM;
   float2* tile = smem;  // [H+1][PO]   spectrum rows as stored: tile[kx][ky]
   float2* mid = smem;   // [N][PM]     aliases the tile (consumed before mid is written)
