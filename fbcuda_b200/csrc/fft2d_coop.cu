@@ -414,7 +414,11 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 // FULL: the output images are contiguous N x N with no crop offset (compile-time strides, no
 // bounds predicates on the stores).  SKIP: small outputs such as weight gradients: a warp none of
 // whose columns is kept by the crop skips its column transforms.
-template <int N, bool FULL = false, bool SKIP = false>
+// NARROW (with SKIP, N = 128): only columns x < 16 are kept (weight gradients).  The row pass then needs 16
+// of the 128 outputs of every line: G[x] = sum_s w128^(s x) T_s[x] with T_s the 16-point inverse transform
+// of the inputs kx = 8 m + s -- four values of s per lane of the line's pair, the two partial sums added
+// through one shuffle per value -- instead of the 64-point transform per lane with its radix-2 step.
+template <int N, bool FULL = false, bool SKIP = false, bool NARROW = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
                                                                                 long long in_sb, RealView out, int B,
                                                                                 int padL, int padU, long long blk_planes) {
@@ -467,7 +471,58 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       tile[kx * PO + H] = make_float2(p.x + h.y, p.y - h.x);
     }
     block_sync<T>();
-    {
+    if constexpr (NARROW) {
+      static_assert(!NARROW || (N == 128 && Q == 2 && SKIP && !FULL), "narrow outputs: N = 128 weight gradients");
+      const int r = item;
+      const float2* c1 = tile + r;                                  // tile[kx][r]
+      const float2* c2 = tile + ((r == 0) ? H : N - r);             // tile[N-kx][(N-r)%N]
+      float2 g[16];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) g[x] = make_float2(0.f, 0.f);
+      static_for<4>([&](auto ic) {
+        constexpr int i = decltype(ic)::value;
+        const int sft = 4 * q + i;
+        float2 t[16];
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+          const int kx = 8 * m + sft;
+          if (kx <= H) {
+            t[m] = c1[kx * PO];
+          } else {
+            const float2 u = c2[(N - kx) * PO];
+            t[m] = make_float2(u.x, -u.y);
+          }
+        }
+        fft_bitrev<16, true, true>(t);
+        static_for<16>([&](auto xc) {
+          constexpr int x = decltype(xc)::value;
+          const float2 v = mul_tw<i * x, N, true>(t[brev(x, 16)]);
+          g[x].x += v.x, g[x].y += v.y;
+        });
+      });
+      if (q == 1) {  // the lane's factor w128^(4 x) = w32^x
+        static_for<16>([&](auto xc) {
+          constexpr int x = decltype(xc)::value;
+          g[x] = mul_tw<x, 32, true>(g[x]);
+        });
+      }
+#pragma unroll
+      for (int x = 0; x < 16; ++x) {
+        g[x].x += __shfl_xor_sync(0xffffffffu, g[x].x, LP);
+        g[x].y += __shfl_xor_sync(0xffffffffu, g[x].y, LP);
+      }
+      block_sync<T>();  // the tile is consumed: mid may overwrite it
+      // columns x >= 16 (and their partners x + H) are not kept: Z_x[ky] = G_x[ky], Z_x[N-ky] = conj(G_x[ky])
+      float2* row1 = mid + r * PM;
+      float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int x = 2 * j + q;
+        const float2 v = q ? g[2 * j + 1] : g[2 * j];
+        row1[x] = v;
+        row2[x] = make_float2(v.x, -v.y);
+      }
+    } else {
       // ---- pass B^-1: row item along kx = jl + P*q + R*m.
       // F[ky][kx] = tile[kx][ky] for kx <= H, else conj(tile[N-kx][(N-ky)%N]).
       const int r = item;
@@ -486,16 +541,13 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           }
         }
       }
-    }
-    block_sync<T>();  // the tile is consumed: mid may overwrite it
-    coop_fft<N, R, Q, true>(a, q, lf);
-    {
+      block_sync<T>();  // the tile is consumed: mid may overwrite it
+      coop_fft<N, R, Q, true>(a, q, lf);
       // lane holds G[ky][x] at x = Q*k + q; columns x and x+H share a complex line:
       // Z_p[ky] = G_p[ky] + i G_{p+H}[ky], Z_p[N-ky] = conj(G_p[ky]) + i conj(G_{p+H}[ky]).
       // x + H = Q*(k + R/2) + q sits in the same lane.
       // Row 0 holds the packed pair (G[0], G[H]) = (re, im); it stores the same two combinations
       // into rows 0 and H, and pass A^-1 undoes them after loading.
-      const int r = item;
       float2* row1 = mid + r * PM;
       float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
       static_for<R / 2>([&](auto kc) {
@@ -641,6 +693,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   // (measured: the predicate-free stores gain at N = 128, 0.57 -> 0.78 of the copy bandwidth, and lose at N = 64)
   if (N == 128 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0) {
     fft2d_coop_inv_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  } else if (N == 128 && out.w + padL <= 16) {
+    // weight gradients: only the first 16 columns are kept, the row pass computes nothing else
+    if constexpr (N == 128) {
+      static bool narrow_configured[64];
+      if (dev >= 0 && dev < 64 && !narrow_configured[dev]) {
+        cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+        narrow_configured[dev] = true;
+      }
+      fft2d_coop_inv_kernel<N, false, true, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+    }
   } else if (N == 128 && (out.w + padL) * 2 <= N) {
     // at most half of the column pairs survive the crop (measured on 13x13 weight gradients: 297 -> 227 us)
     fft2d_coop_inv_kernel<N, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);

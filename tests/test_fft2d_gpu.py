@@ -212,3 +212,19 @@ def test_zero_padded_images_with_rows_of_whole_16_byte_units(case, b):
     spec = gpu_fft2d(x, n, pl, pu)
     assert orc.rel_l2(spec, orc.fbfft2d(x, n, pl, pu)) < FFT_TOL
     assert fb.device_status() == 0
+
+
+@pytest.mark.parametrize("case", [(13, 13, 0, 0), (5, 9, 3, 2), (16, 16, 0, 0), (1, 1, 15, 127), (128, 3, 13, 0), (7, 16, 0, 100)])
+@pytest.mark.parametrize("b", [1, 5, 700])
+def test_n128_inverse_cropped_to_the_first_16_columns(case, b):
+    """N = 128 inverse of which only columns below 16 are kept (weight gradients): the row pass
+    computes 16 of its 128 outputs per line."""
+    n = 128
+    h, w, pl, pu = case
+    rng = np.random.default_rng(b + 3 * h + w + pl)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    spec = orc.fbfft2d(x, n, 0, 0).astype(np.float32)
+    back = gpu_ifft2d(spec, n, h, w, pl, pu, fill=7.0)
+    want = n * n * x.astype(np.float64)[:, pu:pu + h, pl:pl + w]
+    assert orc.rel_l2(back, want) < FFT_TOL
+    assert fb.device_status() == 0
