@@ -606,6 +606,119 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
   }
 }
 
+// ------------------------------------------------------------------ convolution weights, N = 128, 4 planes a block
+// Images of at most 16 x 16 at the canvas' origin into the contraction's 4-bin blocks.  In that layout the
+// 32-byte piece (kx, 4 consecutive ky) of plane p sits between the same pieces of planes p - 1 and p + 1, so
+// a block that transforms one plane writes isolated 32-byte sectors `planes * 32` bytes apart.  Here a block
+// of 8 warps takes 4 adjacent planes and stores whole 128-byte lines:
+//   rows     X1[y][kx] = sum_x img[y][x] w^(kx x), kx = 0..64, by direct sums (thread = kx and half of the rows;
+//            the powers of w^kx by repeated multiplication);
+//   columns  for a slab of 13 values of kx: X[kx][ky] = sum_y X1[y][kx] w^(ky y), a 128-point transform of 16
+//            inputs = 8 independent 16-point transforms X[8 m + s], two per lane of the 4 lanes of a line
+//            (s = 2 q + i), parked as slab[plane][kx][ky];
+//   stores   the 8 lanes (plane, half) of a piece (kx, ky quad) write its 128 bytes of the 4 planes together.
+constexpr int WG = 4, WKX = 13, WSLABS = 5, WPITCH = 130, WX1P = 66, WTHREADS = 256;
+constexpr int kWeightsSmem = WG * 256 * 4 + 128 * 8 + WG * 16 * WX1P * 8 + WG * WKX * WPITCH * 8;
+
+__global__ void __launch_bounds__(WTHREADS, 2) weights128_blocked_kernel(RealView in, float* __restrict__ out, int groups,
+                                                                         long long blk_planes) {
+  constexpr int N = 128, H = 64;
+  extern __shared__ __align__(16) unsigned char wsm[];
+  float* img = reinterpret_cast<float*>(wsm);                            // [WG][16][16]
+  float2* stw = reinterpret_cast<float2*>(img + WG * 256);               // [128] roots of unity
+  float2* x1 = stw + N;                                                  // [WG][16][WX1P]
+  float2* slab = x1 + WG * 16 * WX1P;                                    // [WG][WKX][WPITCH]
+  const int tid = threadIdx.x;
+  for (int i = tid; i < N; i += WTHREADS) {
+    float sn, cs;
+    sincospif(-2.0f * (float)i / (float)N, &sn, &cs);
+    stw[i] = make_float2(cs, sn);
+  }
+  for (int g = blockIdx.x; g < groups; g += gridDim.x) {
+    __syncthreads();  // the previous group's stores have read the slab; stw is written
+    for (int i = tid; i < WG * 256; i += WTHREADS) {
+      const int pl = i >> 8, y = (i >> 4) & 15, x = i & 15;
+      img[i] = (y < in.h && x < in.w) ? in.p[(long long)(WG * g + pl) * in.sb + (long long)y * in.sy + (long long)x * in.sx] : 0.f;
+    }
+    __syncthreads();
+    {
+      // rows: thread (kx = tid % 64, rows 4 (tid / 64) .. + 3) of every plane; kx = 64 (w = -1) by the first 64 threads
+      const int kx = tid & 63, y0 = (tid >> 6) * 4;
+      const float2 w1 = stw[kx];
+      float2 acc[WG][4];
+#pragma unroll
+      for (int pl = 0; pl < WG; ++pl)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[pl][j] = make_float2(0.f, 0.f);
+      float2 w = make_float2(1.f, 0.f);
+#pragma unroll
+      for (int x = 0; x < 16; ++x) {
+#pragma unroll
+        for (int pl = 0; pl < WG; ++pl)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float v = img[pl * 256 + (y0 + j) * 16 + x];
+            acc[pl][j].x += v * w.x, acc[pl][j].y += v * w.y;
+          }
+        w = make_float2(w.x * w1.x - w.y * w1.y, w.x * w1.y + w.y * w1.x);
+      }
+#pragma unroll
+      for (int pl = 0; pl < WG; ++pl)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x1[(pl * 16 + y0 + j) * WX1P + kx] = acc[pl][j];
+      if (tid < WG * 16) {
+        const float* row = img + tid * 16;  // (plane, y) = tid
+        float sum = 0.f;
+#pragma unroll
+        for (int x = 0; x < 16; ++x) sum += (x & 1) ? -row[x] : row[x];
+        x1[tid * WX1P + H] = make_float2(sum, 0.f);
+      }
+    }
+    __syncthreads();
+    for (int sl = 0; sl < WSLABS; ++sl) {
+      const int kx0 = sl * WKX;
+      {
+        // columns: line task = (plane, kx of the slab), 4 lanes a line
+        const int task = tid >> 2, q = tid & 3;
+        if (task < WG * WKX) {
+          const int pl = task / WKX, kxl = task % WKX;
+          float2 x[16];
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            const float2 v = x1[(pl * 16 + n) * WX1P + kx0 + kxl];
+            const float2 f = stw[(2 * q * n) & (N - 1)];  // the lane's factor w128^(2 q n)
+            x[n] = make_float2(v.x * f.x - v.y * f.y, v.x * f.y + v.y * f.x);
+          }
+          float2* line = slab + (pl * WKX + kxl) * WPITCH;
+          static_for<2>([&](auto ic) {
+            constexpr int i = decltype(ic)::value;
+            float2 t[16];
+            static_for<16>([&](auto nc) {
+              constexpr int n = decltype(nc)::value;
+              t[n] = mul_tw<n * i, N, false>(x[n]);
+            });
+            fft_bitrev<16, false, true>(t);
+            static_for<16>([&](auto mc) {
+              constexpr int m = decltype(mc)::value;
+              line[8 * m + 2 * q + i] = t[brev(m, 16)];
+            });
+          });
+        }
+      }
+      __syncthreads();
+      // stores: piece (kx, ky quad) of the 4 planes = 128 contiguous bytes, 8 lanes (plane, half)
+      for (int e = tid; e < WKX * 32 * 8; e += WTHREADS) {
+        const int sub = e & 7, ln = e >> 3, pl = sub >> 1, half = sub & 1;
+        const int kxl = ln >> 5, quad = ln & 31;
+        const float4 v = *reinterpret_cast<const float4*>(slab + (pl * WKX + kxl) * WPITCH + quad * 4 + half * 2);
+        const long long piece = (long long)(kx0 + kxl) * 32 + quad;
+        *reinterpret_cast<float4*>(out + (piece * blk_planes + WG * g + pl) * 8 + half * 4) = v;
+      }
+      __syncthreads();
+    }
+  }
+}
+
 template <int N>
 constexpr int fwd_smem() {
   constexpr int mid = N * CoopCfg<N>::PM, tile = (N / 2 + 1) * CoopCfg<N>::PO;
@@ -637,6 +750,17 @@ int launch_fwd(const RealView& in, const CplxView& out, int B, int padL, int pad
   const bool in_bulk = in.sx == 1 && in.sy == in.w && (B <= 1 || in.sb == (long long)in.h * in.w) && aligned16(in.p) &&
                        in.h <= N && in.w <= N && (long long)in.h * in.w * 4 + 32 <= fwd_smem<N>() - 16;
   if constexpr (N == 128) {
+    if (out.blk_planes && in.h <= 16 && in.w <= 16 && padL == 0 && padU == 0 && B % WG == 0 && B == out.blk_planes) {
+      // convolution weights into the contraction's blocks: 4 adjacent planes a block, whole 128-byte lines
+      static bool weights_configured[64];
+      if (dev >= 0 && dev < 64 && !weights_configured[dev]) {
+        cudaFuncSetAttribute(weights128_blocked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWeightsSmem);
+        weights_configured[dev] = true;
+      }
+      const int groups = B / WG, wcap = sm_count() * 2;
+      weights128_blocked_kernel<<<groups < wcap ? groups : wcap, WTHREADS, kWeightsSmem, s>>>(in, out.p, groups, out.blk_planes);
+      return cudaPeekAtLastError() == cudaSuccess ? kSuccess : kCudaError;
+    }
     if (in.h <= 16 && in.w + padL <= 16 && padL >= 0 && padU >= 0 && in.h + padU <= N) {
       // small images in the canvas' first 16 columns (convolution weights): direct column pass
       const int smem = fwd_smem<N>() + 1024 + N * 8 + 16;

@@ -84,7 +84,9 @@ def test_layer_at_benchmark_batch_through_both_call_chains(name):
 @pytest.mark.parametrize("case", [
     # n, batch shard, C, O, image, kernel, pad: the shards data-parallel runs on 4 and 8 GPUs leave
     (64, 8, 128, 128, 56, 3, 1), (128, 4, 96, 96, 128, 13, 0), (32, 5, 40, 200, 27, 5, 0), (16, 1, 16, 16, 12, 3, 1),
-    (32, 3, 130, 24, 20, 5, 2), (64, 7, 33, 65, 30, 7, 0), (16, 8, 256, 4, 14, 3, 0)])
+    (32, 3, 130, 24, 20, 5, 2), (64, 7, 33, 65, 30, 7, 0), (16, 8, 256, 4, 14, 3, 0),
+    # FFT-128 weights of 16 x 16 and 1 x 1 (the 4-planes-per-block weight transform, plane counts 260 and 272)
+    (128, 2, 20, 13, 30, 16, 0), (128, 3, 16, 17, 20, 1, 0)])
 def test_small_batch_shards_take_the_fp32_streaming_contraction(case):
     """At most 8 images: updateOutput / updateGradInput contract against 8 or fewer columns and
     accGradParameters sums 8 or fewer terms; plane counts that are no multiple of the 128-row and
