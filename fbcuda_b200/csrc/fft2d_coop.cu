@@ -471,8 +471,45 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       tile[kx * PO + H] = make_float2(p.x + h.y, p.y - h.x);
     }
     block_sync<T>();
-    if constexpr (NARROW) {
-      static_assert(!NARROW || (N == 128 && Q == 2 && SKIP && !FULL), "narrow outputs: N = 128 weight gradients");
+    if constexpr (NARROW && N == 64) {
+      // N = 64, only columns x < 8 are kept: G[x] = sum_s w64^(s x) T_s[x], T_s the 8-point inverse transform of
+      // the inputs kx = 8 m + s (a lane holds a whole line)
+      static_assert(!(NARROW && N == 64) || (Q == 1 && !FULL), "narrow outputs at N = 64");
+      const int r = item;
+      const float2* c1 = tile + r;
+      const float2* c2 = tile + ((r == 0) ? H : N - r);
+      float2 g[8];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) g[x] = make_float2(0.f, 0.f);
+      static_for<8>([&](auto sc) {
+        constexpr int sft = decltype(sc)::value;
+        float2 t[8];
+        static_for<8>([&](auto mc) {
+          constexpr int kx = 8 * decltype(mc)::value + sft;
+          if constexpr (kx <= H) {
+            t[decltype(mc)::value] = c1[kx * PO];
+          } else {
+            const float2 u = c2[(N - kx) * PO];
+            t[decltype(mc)::value] = make_float2(u.x, -u.y);
+          }
+        });
+        fft_bitrev<8, true, true>(t);
+        static_for<8>([&](auto xc) {
+          constexpr int x = decltype(xc)::value;
+          const float2 v = mul_tw<sft * x, N, true>(t[brev(x, 8)]);
+          g[x].x += v.x, g[x].y += v.y;
+        });
+      });
+      block_sync<T>();  // the tile is consumed: mid may overwrite it
+      float2* row1 = mid + r * PM;
+      float2* row2 = mid + ((r == 0) ? H : N - r) * PM;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        row1[x] = g[x];
+        row2[x] = make_float2(g[x].x, -g[x].y);
+      }
+    } else if constexpr (NARROW) {
+      static_assert(!NARROW || N == 64 || (N == 128 && Q == 2 && SKIP && !FULL), "narrow outputs: N = 128 weight gradients");
       const int r = item;
       const float2* c1 = tile + r;                                  // tile[kx][r]
       const float2* c2 = tile + ((r == 0) ? H : N - r);             // tile[N-kx][(N-r)%N]
@@ -559,7 +596,35 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       });
     }
     block_sync<T>();
-    {
+    if constexpr (NARROW && N == 64) {
+      // ---- pass A^-1 for the 8 kept columns: 4 lanes a column (16 points each), ky = jl + 4 q4 + 16 m
+      const int col = lane & 7, q4 = lane >> 3;
+      float2 lf4[4];
+      lane_factors<4, true>(q4, lf4);
+      float2 c[16];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < 4; ++jl) c[m * 4 + jl] = mid[(jl + 4 * q4 + 16 * m) * PM + col];
+      }
+      if (q4 == 0) {
+        // ky = 0 sits at c[0] and ky = H at c[8] of the q4 = 0 lanes (see the general path below)
+        const float2 A = c[0], Bv = c[8];
+        c[0] = make_float2(0.5f * (A.x + Bv.x), 0.5f * (A.y + Bv.y));
+        c[8] = make_float2(0.5f * (A.y - Bv.y), 0.5f * (Bv.x - A.x));
+      }
+      block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
+      if (b + gridDim.x < B) fetch(b + gridDim.x);
+      coop_fft<N, 16, 4, true>(c, q4, lf4);
+      const unsigned x0 = (unsigned)(col - padL);
+      if (x0 < (unsigned)out.w) {
+        float* p0 = out.p + (long long)b * out.sb + (long long)x0 * out.sx + (long long)(q4 - padU) * out.sy;
+        static_for<16>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          if ((unsigned)(4 * k + q4 - padU) < (unsigned)out.h) p0[(long long)(4 * k) * out.sy] = c[brev(k, 16)].x;
+        });
+      }
+    } else {
       // ---- pass A^-1: column pair item along ky = jl + P*q + R*m
 #pragma unroll
       for (int m = 0; m < Q; ++m) {
@@ -817,6 +882,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   // (measured: the predicate-free stores gain at N = 128, 0.57 -> 0.78 of the copy bandwidth, and lose at N = 64)
   if (N == 128 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0) {
     fft2d_coop_inv_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  } else if (N == 64 && out.w + padL <= 8) {
+    // weight gradients at N = 64: only the first 8 columns are kept
+    if constexpr (N == 64) {
+      static bool narrow64_configured[64];
+      if (dev >= 0 && dev < 64 && !narrow64_configured[dev]) {
+        cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+        narrow64_configured[dev] = true;
+      }
+      fft2d_coop_inv_kernel<N, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+    }
   } else if (N == 128 && out.w + padL <= 16) {
     // weight gradients: only the first 16 columns are kept, the row pass computes nothing else
     if constexpr (N == 128) {

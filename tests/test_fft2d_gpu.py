@@ -214,13 +214,14 @@ def test_zero_padded_images_with_rows_of_whole_16_byte_units(case, b):
     assert fb.device_status() == 0
 
 
-@pytest.mark.parametrize("case", [(13, 13, 0, 0), (5, 9, 3, 2), (16, 16, 0, 0), (1, 1, 15, 127), (128, 3, 13, 0), (7, 16, 0, 100)])
+@pytest.mark.parametrize("case", [(128, 13, 13, 0, 0), (128, 5, 9, 3, 2), (128, 16, 16, 0, 0), (128, 1, 1, 15, 127),
+                                  (128, 128, 3, 13, 0), (128, 7, 16, 0, 100), (64, 3, 3, 0, 0), (64, 7, 7, 0, 0),
+                                  (64, 5, 8, 0, 3), (64, 2, 3, 5, 60), (64, 64, 1, 7, 0)])
 @pytest.mark.parametrize("b", [1, 5, 700])
-def test_n128_inverse_cropped_to_the_first_16_columns(case, b):
-    """N = 128 inverse of which only columns below 16 are kept (weight gradients): the row pass
-    computes 16 of its 128 outputs per line."""
-    n = 128
-    h, w, pl, pu = case
+def test_inverse_cropped_to_the_first_columns(case, b):
+    """N = 128 / 64 inverse of which only columns below 16 / 8 are kept (weight gradients): the row pass
+    computes only those outputs of every line."""
+    n, h, w, pl, pu = case
     rng = np.random.default_rng(b + 3 * h + w + pl)
     x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
     spec = orc.fbfft2d(x, n, 0, 0).astype(np.float32)
