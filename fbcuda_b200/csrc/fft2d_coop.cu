@@ -624,6 +624,35 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
           if ((unsigned)(4 * k + q4 - padU) < (unsigned)out.h) p0[(long long)(4 * k) * out.sy] = c[brev(k, 16)].x;
         });
       }
+    } else if constexpr (NARROW && N == 128) {
+      // ---- pass A^-1 for the 16 kept columns: 8 lanes a column (16 points each), ky = jl + 2 q8 + 16 m;
+      // every warp takes 4 columns instead of the first warp all 16 with 64 points a lane
+      const int col = warp * 4 + (lane & 3), q8 = lane >> 2;
+      float2 lf8[8];
+      lane_factors<8, true>(q8, lf8);
+      float2 c[16];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+#pragma unroll
+        for (int jl = 0; jl < 2; ++jl) c[m * 2 + jl] = mid[(jl + 2 * q8 + 16 * m) * PM + col];
+      }
+      if (q8 == 0) {
+        // ky = 0 sits at c[0] and ky = H at c[8] of the q8 = 0 lanes (see the general path below)
+        const float2 A = c[0], Bv = c[8];
+        c[0] = make_float2(0.5f * (A.x + Bv.x), 0.5f * (A.y + Bv.y));
+        c[8] = make_float2(0.5f * (A.y - Bv.y), 0.5f * (Bv.x - A.x));
+      }
+      block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
+      if (b + gridDim.x < B) fetch(b + gridDim.x);
+      coop_fft<N, 16, 8, true>(c, q8, lf8);
+      const unsigned x0 = (unsigned)(col - padL);
+      if (x0 < (unsigned)out.w) {
+        float* p0 = out.p + (long long)b * out.sb + (long long)x0 * out.sx + (long long)(q8 - padU) * out.sy;
+        static_for<16>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          if ((unsigned)(8 * k + q8 - padU) < (unsigned)out.h) p0[(long long)(8 * k) * out.sy] = c[brev(k, 16)].x;
+        });
+      }
     } else {
       // ---- pass A^-1: column pair item along ky = jl + P*q + R*m
 #pragma unroll
