@@ -418,7 +418,11 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
 // of the 128 outputs of every line: G[x] = sum_s w128^(s x) T_s[x] with T_s the 16-point inverse transform
 // of the inputs kx = 8 m + s -- four values of s per lane of the line's pair, the two partial sums added
 // through one shuffle per value -- instead of the 64-point transform per lane with its radix-2 step.
-template <int N, bool FULL = false, bool SKIP = false, bool NARROW = false>
+// STAGE: output images with rows, crop offsets and strides in 16-byte units.  The rows of the result are
+// parked in the shared memory the spectrum came through and leave by one bulk store per kept row (the
+// crop is the store's start column and length) instead of 4-byte stores with bounds tests from every
+// lane; the next spectrum is fetched after the stores have read the rows.
+template <int N, bool FULL = false, bool SKIP = false, bool NARROW = false, bool STAGE = false>
 __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCKS) fft2d_coop_inv_kernel(const float* __restrict__ in,
                                                                                 long long in_sb, RealView out, int B,
                                                                                 int padL, int padU, long long blk_planes) {
@@ -668,7 +672,9 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
         a[R / 2] = make_float2(0.5f * (A.y - Bv.y), 0.5f * (Bv.x - A.x));
       }
       block_sync<T>();  // mid is consumed: fetch the next spectrum behind the last transform
-      if (b + gridDim.x < B) fetch(b + gridDim.x);
+      if constexpr (!STAGE) {
+        if (b + gridDim.x < B) fetch(b + gridDim.x);
+      }
       const unsigned x0 = (unsigned)(item - padL), x1 = (unsigned)(item + H - padL);
       const bool ok0 = x0 < (unsigned)out.w, ok1 = x1 < (unsigned)out.w;
       if constexpr (SKIP) {
@@ -676,7 +682,25 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
       }
       coop_fft<N, R, Q, true>(a, q, lf);
       float* dst = out.p + (long long)b * out.sb;
-      if constexpr (FULL) {
+      if constexpr (STAGE) {
+        static_assert(!STAGE || (!FULL && !SKIP && !NARROW), "staged rows: the general crop");
+        constexpr int PS = N + 4;  // floats per parked row
+        float* rows = reinterpret_cast<float*>(smem);
+        static_for<R>([&](auto kc) {
+          constexpr int k = decltype(kc)::value;
+          const float2 t = a[brev(k, R)];
+          rows[(Q * k + q) * PS + item] = t.x;
+          rows[(Q * k + q) * PS + item + H] = t.y;
+        });
+        fence_async_smem();
+        block_sync<T>();
+        for (int y = threadIdx.x; y < out.h; y += T)
+          bulk_s2g(dst + (long long)y * out.sy, smem_u32(rows + (y + padU) * PS + padL), (unsigned)out.w * 4u);
+        bulk_commit();
+        bulk_wait_read();
+        block_sync<T>();
+        if (b + gridDim.x < B) fetch(b + gridDim.x);
+      } else if constexpr (FULL) {
         float* p0 = dst + item + q * N;
         static_for<R>([&](auto kc) {
           constexpr int k = decltype(kc)::value;
@@ -909,6 +933,7 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   }
   const int cap = sm_count() * CoopCfg<N>::BLOCKS_PER_SM;
   // (measured: the predicate-free stores gain at N = 128, 0.57 -> 0.78 of the copy bandwidth, and lose at N = 64)
+  // (measured: full 128 x 128 outputs keep their direct stores, 0.76 against 0.71 of the copy bandwidth with parked rows)
   if (N == 128 && out.sx == 1 && out.sy == N && out.h == N && out.w == N && padL == 0 && padU == 0) {
     fft2d_coop_inv_kernel<N, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   } else if (N == 64 && out.w + padL <= 8) {
@@ -934,6 +959,15 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
   } else if (N == 128 && (out.w + padL) * 2 <= N) {
     // at most half of the column pairs survive the crop (measured on 13x13 weight gradients: 297 -> 227 us)
     fft2d_coop_inv_kernel<N, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
+  } else if (out.sx == 1 && out.w >= 4 && out.w % 4 == 0 && padL % 4 == 0 && out.sy % 4 == 0 && (B <= 1 || out.sb % 4 == 0) &&
+             aligned16(out.p) && padL + out.w <= N && padU + out.h <= N && !(N == 128 && (out.w + padL) * 2 <= N)) {
+    // cropped images in 16-byte units: rows parked in shared memory, one bulk store per kept row
+    static bool stage_configured[64];
+    if (dev >= 0 && dev < 64 && !stage_configured[dev]) {
+      cudaFuncSetAttribute(fft2d_coop_inv_kernel<N, false, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, inv_smem<N>());
+      stage_configured[dev] = true;
+    }
+    fft2d_coop_inv_kernel<N, false, false, false, true><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   } else {
     fft2d_coop_inv_kernel<N><<<B < cap ? B : cap, (N / 2) * CoopCfg<N>::Q, inv_smem<N>(), s>>>(in.p, in.sb, out, B, padL, padU, in.blk_planes);
   }
