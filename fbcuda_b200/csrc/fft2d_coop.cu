@@ -389,11 +389,20 @@ __global__ void __launch_bounds__((N / 2) * CoopCfg<N>::Q, CoopCfg<N>::MIN_BLOCK
     float* dst = out + (long long)b * out_sb;
     if (blk_planes) {
       // 4-bin blocks (contraction operands): 32-byte pieces, planes adjacent; two lanes per piece
-      constexpr int QR = N / 4;
-      for (int i = threadIdx.x; i < (H + 1) * QR * 2; i += T) {
-        const int half = i & 1, piece = i >> 1;
-        const float4 v = *reinterpret_cast<const float4*>(tile + (piece / QR) * PO + (piece % QR) * 4 + half * 2);
-        *reinterpret_cast<float4*>(out + ((long long)piece * blk_planes + b) * 8 + half * 4) = v;
+      // (thread t keeps its half of the ky quad (t / 2) % QR and walks kx in steps of T / (2 QR): both
+      // addresses advance by constants, and four reads are in flight before the first store)
+      constexpr int QR = N / 4, KSTEP = T / (2 * QR), ROUNDS = (H + 1 + KSTEP - 1) / KSTEP;
+      static_assert(T % (2 * QR) == 0, "a block covers whole stored rows per round");
+      const int half = threadIdx.x & 1, quad = (threadIdx.x >> 1) % QR, kx0 = threadIdx.x / (2 * QR);
+      const float2* src = tile + kx0 * PO + quad * 4 + half * 2;
+      float* dstp = out + ((long long)(kx0 * QR + quad) * blk_planes + b) * 8 + half * 4;
+      const long long dstep = (long long)KSTEP * QR * blk_planes * 8;
+#pragma unroll 4
+      for (int rd = 0; rd < ROUNDS; ++rd) {
+        if (kx0 + rd * KSTEP <= H) {
+          const float4 v = *reinterpret_cast<const float4*>(src + rd * KSTEP * PO);
+          *reinterpret_cast<float4*>(dstp + rd * dstep) = v;
+        }
       }
     } else {
       for (int kx = threadIdx.x; kx <= H; kx += T) bulk_s2g(dst + (long long)kx * (2 * N), smem_u32(tile + kx * PO), N * 8);
