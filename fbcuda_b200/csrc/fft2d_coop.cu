@@ -761,38 +761,48 @@ __global__ void __launch_bounds__(WTHREADS, 2) weights128_blocked_kernel(RealVie
     sincospif(-2.0f * (float)i / (float)N, &sn, &cs);
     stw[i] = make_float2(cs, sn);
   }
+  // the group's 4 images travel through registers: the next group's loads are in flight during this group's work
+  static_assert(WG * 256 == 4 * WTHREADS, "four image values a thread");
+  auto load_images = [&](int g, float (&v)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = tid + j * WTHREADS, pl = i >> 8, y = (i >> 4) & 15, x = i & 15;
+      v[j] = (g < groups && y < in.h && x < in.w)
+                 ? __ldg(in.p + (long long)(WG * g + pl) * in.sb + (long long)y * in.sy + (long long)x * in.sx)
+                 : 0.f;
+    }
+  };
+  float pending[4];
+  load_images(blockIdx.x, pending);
   for (int g = blockIdx.x; g < groups; g += gridDim.x) {
     __syncthreads();  // the previous group's stores have read the slab; stw is written
-    for (int i = tid; i < WG * 256; i += WTHREADS) {
-      const int pl = i >> 8, y = (i >> 4) & 15, x = i & 15;
-      img[i] = (y < in.h && x < in.w) ? in.p[(long long)(WG * g + pl) * in.sb + (long long)y * in.sy + (long long)x * in.sx] : 0.f;
-    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) img[tid + j * WTHREADS] = pending[j];
+    load_images(g + gridDim.x, pending);
     __syncthreads();
     {
       // rows: thread (kx = tid % 64, rows 4 (tid / 64) .. + 3) of every plane; kx = 64 (w = -1) by the first 64 threads
       const int kx = tid & 63, y0 = (tid >> 6) * 4;
       const float2 w1 = stw[kx];
-      float2 acc[WG][4];
+      float2 wx[16];  // w^(kx x), x = 0..15, by repeated multiplication
+      wx[0] = make_float2(1.f, 0.f);
 #pragma unroll
-      for (int pl = 0; pl < WG; ++pl)
+      for (int x = 1; x < 16; ++x) wx[x] = make_float2(wx[x - 1].x * w1.x - wx[x - 1].y * w1.y, wx[x - 1].x * w1.y + wx[x - 1].y * w1.x);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[pl][j] = make_float2(0.f, 0.f);
-      float2 w = make_float2(1.f, 0.f);
+      for (int pl = 0; pl < WG; ++pl) {
 #pragma unroll
-      for (int x = 0; x < 16; ++x) {
+        for (int j = 0; j < 4; ++j) {
+          const float4* row = reinterpret_cast<const float4*>(img + pl * 256 + (y0 + j) * 16);  // the same for all kx: a broadcast
+          float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int pl = 0; pl < WG; ++pl)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float v = img[pl * 256 + (y0 + j) * 16 + x];
-            acc[pl][j].x += v * w.x, acc[pl][j].y += v * w.y;
+          for (int x4 = 0; x4 < 4; ++x4) {
+            const float4 v = row[x4];
+            acc.x += v.x * wx[4 * x4].x + v.y * wx[4 * x4 + 1].x + v.z * wx[4 * x4 + 2].x + v.w * wx[4 * x4 + 3].x;
+            acc.y += v.x * wx[4 * x4].y + v.y * wx[4 * x4 + 1].y + v.z * wx[4 * x4 + 2].y + v.w * wx[4 * x4 + 3].y;
           }
-        w = make_float2(w.x * w1.x - w.y * w1.y, w.x * w1.y + w.y * w1.x);
+          x1[(pl * 16 + y0 + j) * WX1P + kx] = acc;
+        }
       }
-#pragma unroll
-      for (int pl = 0; pl < WG; ++pl)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) x1[(pl * 16 + y0 + j) * WX1P + kx] = acc[pl][j];
       if (tid < WG * 16) {
         const float* row = img + tid * 16;  // (plane, y) = tid
         float sum = 0.f;
