@@ -340,7 +340,10 @@ int cgemm_small(const float* a, long long a_rs, long long a_ks, bool conjA, cons
     const long long total = (long long)g.m_tiles * (X / 4);
     if (total > 0x7fffffffLL) return -1;
     g.total_tiles = (int)total;
-    const long long cap = (long long)(NB == 8 ? FewCfg<8>::MINB : FewCfg<4>::MINB) * sm_count();
+    // persistent blocks fill their SMs' shared memory: a caller that runs collectives beside the contraction
+    // keeps some SMs free for them (set_contraction_reserved_sms), as the tensor-core kernel does
+    const int sms = sm_count() - contraction_reserved_sms();
+    const long long cap = (long long)(NB == 8 ? FewCfg<8>::MINB : FewCfg<4>::MINB) * (sms > 1 ? sms : 1);
     const int grid = (int)(total < cap ? total : cap);
     if (NB == 4) {
       cgemm_fewcols_kernel<4><<<grid, FewCfg<4>::THREADS, FewCfg<4>::SMEM, s>>>(ma, mb, g);
