@@ -127,6 +127,33 @@ def test_small_batch_shards_take_the_fp32_streaming_contraction(case):
         assert orc.rel_l2(host(got), host(other).astype(np.float64)) < CONV_TOL
 
 
+def test_reserved_sms_do_not_change_the_results_of_small_shards():
+    """SMs kept free for collectives shrink the grids of the persistent contractions (tensor-core and
+    FP32 streaming kernels alike): same bits out."""
+    n, b, c, o, hw, k, pad = 64, 8, 64, 48, 40, 3, 1
+    rng = np.random.default_rng(77)
+    x = dev(rng.normal(size=(b, c, hw, hw)).astype(np.float32))
+    w = dev((rng.normal(size=(o, c, k, k)) / 24.0).astype(np.float32))
+    go = dev(rng.normal(size=(b, o, hw, hw)).astype(np.float32))
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    results = []
+    try:
+        for reserved in (0, 32, 128):
+            fb.set_contraction_reserved_sms(reserved)
+            out, gi, gw = torch.empty_like(go), torch.empty_like(x), torch.empty_like(w)
+            fb.conv_update_output(n, x, w, out, ws, inPad=(pad, pad))
+            fb.conv_update_grad_input(n, gi, w, go, ws, inPad=(pad, pad))
+            fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=(pad, pad))
+            torch.cuda.synchronize()
+            results.append((out, gi, gw))
+    finally:
+        fb.set_contraction_reserved_sms(0)
+    for other in results[1:]:
+        for a, b2 in zip(results[0], other):
+            assert torch.equal(a, b2)
+    assert fb.device_status() == 0
+
+
 @pytest.mark.parametrize("name", ["fft64", "fft128"])
 def test_layer_phase_flags_reassemble_the_passes(name):
     """STOP_AFTER_TRANSFORMS, STOP_AFTER_CONTRACTION and START_FROM_SPECTRUM cut every pass into
