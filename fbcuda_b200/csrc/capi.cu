@@ -102,14 +102,14 @@ const char* fbfft_b200_last_error(void) { return g_last_error; }
 int fbfft_b200_device_status(void) {
   const int a = read_device_error(), b = read_device_error_coop(), c = read_device_error_tc(), d = read_device_error_tma(),
             e = read_device_error_fft1d(), f = read_device_error_256(), g = read_device_error_cols(),
-            h = read_device_error_peak(), i = read_device_error_small();
-  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : (g != 0 ? g : (h != 0 ? h : i)))))));
+            h = read_device_error_peak(), i = read_device_error_small(), j = read_device_error_n8();
+  return a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (e != 0 ? e : (f != 0 ? f : (g != 0 ? g : (h != 0 ? h : (i != 0 ? i : j))))))));
 }
 
 int fbfft_b200_clear_device_status(void) {
   const int r = clear_device_error() | clear_device_error_coop() | clear_device_error_tc() | clear_device_error_tma() |
                 clear_device_error_fft1d() | clear_device_error_256() | clear_device_error_cols() |
-                clear_device_error_peak() | clear_device_error_small();
+                clear_device_error_peak() | clear_device_error_small() | clear_device_error_n8();
   if (cudaDeviceSynchronize() != cudaSuccess || r != 0) return fail(kCudaError, "clear_device_status: cannot reset the status words");
   return kSuccess;
 }

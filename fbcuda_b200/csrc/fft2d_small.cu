@@ -409,6 +409,16 @@ int launch_inv(const CplxView& in, const RealView& out, int B, int padL, int pad
 int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, int padL, int padU, cudaStream_t s) {
   if (B <= 0) return kSuccess;
   if (out.blk_planes && out.blk_bins != 4) return kUnsupportedDimension;  // forward transforms write 4-bin blocks
+  if (n == 8 && fft2d_n8_supported(in, out, B, padL, padU)) {
+    // whole groups of 32 full images: one thread per image; the rest below
+    const int done = (B / 32) * 32;
+    if (int rc = fft2d_n8(false, in.p, out.p, B / 32, s)) return rc;
+    if (done == B) return kSuccess;
+    RealView i2 = in;
+    CplxView o2 = out;
+    i2.p += (long long)done * in.sb, o2.p += (long long)done * out.sb;
+    return launch_fwd<8>(i2, o2, B - done, padL, padU, s);
+  }
   switch (n) {
     case 8:
       return launch_fwd<8>(in, out, B, padL, padU, s);
@@ -424,6 +434,15 @@ int fft2d_small_forward(int n, const RealView& in, const CplxView& out, int B, i
 int fft2d_small_inverse(int n, const CplxView& in, const RealView& out, int B, int padL, int padU, cudaStream_t s) {
   if (B <= 0) return kSuccess;
   if (in.blk_planes && in.blk_bins != n) return kUnsupportedDimension;  // inverse transforms read row blocks
+  if (n == 8 && fft2d_n8_supported(out, in, B, padL, padU)) {
+    const int done = (B / 32) * 32;
+    if (int rc = fft2d_n8(true, in.p, out.p, B / 32, s)) return rc;
+    if (done == B) return kSuccess;
+    CplxView i2 = in;
+    RealView o2 = out;
+    i2.p += (long long)done * in.sb, o2.p += (long long)done * out.sb;
+    return launch_inv<8>(i2, o2, B - done, padL, padU, s);
+  }
   switch (n) {
     case 8:
       return launch_inv<8>(in, out, B, padL, padU, s);

@@ -69,6 +69,11 @@ int fft1d_fast_ragged(int n, const float* p, long long sb, long long sy, int h, 
                       float* dst, long long tasks, cudaStream_t s);
 int fft1d_fast_ragged_inverse(int n, const float* src, float* p, long long sb, long long sy, int h, int w, int padL,
                               int padU, int rpi, long long tasks, cudaStream_t s);
+// N = 8 on contiguous full images, one thread per image (fft2d_n8.cu): whole groups of 32 images
+bool fft2d_n8_supported(const RealView& real, const CplxView& cplx, int B, int padL, int padU);
+int fft2d_n8(bool inverse, const float* src, float* dst, long long tasks, cudaStream_t s);
+int read_device_error_n8();
+int clear_device_error_n8();
 int read_device_error_fft1d();
 int clear_device_error_fft1d();
 int read_device_error_256();

@@ -229,3 +229,19 @@ def test_inverse_cropped_to_the_first_columns(case, b):
     want = n * n * x.astype(np.float64)[:, pu:pu + h, pl:pl + w]
     assert orc.rel_l2(back, want) < FFT_TOL
     assert fb.device_status() == 0
+
+
+@pytest.mark.parametrize("b", [32, 229, 5000])
+def test_n8_full_images_one_thread_per_image(b):
+    """N = 8 on contiguous full 8 x 8 images: whole groups of 32 images take the one-thread-per-image
+    kernel, the tail the general one; both directions against the oracle."""
+    n = 8
+    rng = np.random.default_rng(8 + b)
+    x = rng.uniform(-1, 1, (b, n, n)).astype(np.float32)
+    spec = gpu_fft2d(x, n)
+    want = orc.fbfft2d(x, n, 0, 0)
+    per = np.linalg.norm((spec - want).reshape(b, -1), axis=1) / np.linalg.norm(want.reshape(b, -1), axis=1)
+    assert per.max() < 10 * FFT_TOL, int(per.argmax())
+    back = gpu_ifft2d(want.astype(np.float32), n, n, n)
+    assert orc.rel_l2(back, n * n * x.astype(np.float64)) < FFT_TOL
+    assert fb.device_status() == 0
