@@ -605,16 +605,25 @@ def conv_block(name, args, world, rank, comm, with_cpu=True):
             fb.conv_acc_grad_parameters(n, x, gw, go, ws, inPad=ip,
                                         flags=api.REUSE_INPUT_SPECTRUM | api.REUSE_OUTPUT_SPECTRUM)
 
+    # shards of at most 8 images on every rank: the weight-gradient spectrum is kept plane by plane between the
+    # contraction and the sum, so that the reduce-scatter is one collective over contiguous shards
+    small_shards = world > 1 and -(-bg // world) <= 8
+
+    def layout_flag(mode):
+        return api.RESULT_PLANE_MAJOR if (small_shards and mode == api.DP_FREQUENCY_REDUCE_SCATTER) else 0
+
     def make_step_dp(mode, collective=True):
         # the weight-gradient contraction runs first, in a workspace of its own; its sum over the
         # ranks, inverse transform (and gather) run on a second stream under the other two passes
+        lay = layout_flag(mode) if collective else 0
+
         def step():
             cur = torch.cuda.current_stream()
-            fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.STOP_AFTER_CONTRACTION)
+            fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.STOP_AFTER_CONTRACTION | lay)
             side.wait_stream(cur)
             with torch.cuda.stream(side):
                 if collective:
-                    fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM)
+                    fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM | lay)
                 else:
                     fb.conv_acc_grad_parameters(n, x, gw, go, ws2, inPad=ip, flags=api.START_FROM_SPECTRUM)
             fb.conv_update_output(n, x, w, out, ws, inPad=ip)
@@ -719,7 +728,7 @@ def conv_block(name, args, world, rank, comm, with_cpu=True):
         # the sum over the ranks with what follows it (inverse, gather), alone on the stream
         for mname, mode in modes.items():
             fn = lambda mode=mode: fb.conv_acc_grad_parameters_dp(comm, mode, n, x, gw, go, ws, inPad=ip,
-                                                                  flags=api.START_FROM_SPECTRUM)
+                                                                  flags=api.START_FROM_SPECTRUM | layout_flag(mode))
             barrier_sync(world)
             phases[f"sum_and_inverse_{mname}_us"] = time_event_us(fn, reps=5, warm=2)
     block["phases_rank0"] = phases

@@ -368,6 +368,7 @@ STOP_AFTER_CONTRACTION = 8
 START_FROM_SPECTRUM = 16
 ACCUMULATE_RESULT = 32
 STOP_AFTER_TRANSFORMS = 64
+RESULT_PLANE_MAJOR = 128
 REGION_INPUT, REGION_OUTPUT, REGION_WEIGHT, REGION_RESULT = 0, 1, 2, 3
 
 

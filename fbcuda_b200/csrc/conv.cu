@@ -116,9 +116,13 @@ bool use_blocked(int n, long long C, long long O) {
 int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk, long long a_planes, bool conjA,
              const float* b, long long b_pn, long long b_pk, long long b_planes, bool conjB, float* d, long long d_pm,
              long long d_pn, long long d_planes, int M, int N, int K, float inv_norm, cudaStream_t s,
-             bool accumulate = false) {
+             bool accumulate = false, bool d_plane_major = false) {
   const long long X = bins_of(n);
   if (blocked) {
+    // result: row blocks of n bins with the planes adjacent inside a block, or (d_plane_major) plane by plane
+    const long long dm = d_plane_major ? d_pm * X : d_pm * n, dn = d_plane_major ? d_pn * X : d_pn * n;
+    const long long dbs = d_plane_major ? 16 : d_planes * n;
+    const int dqb = d_plane_major ? 16 : n;
     // operands in 4-bin blocks (plane stride 4 complex), result in blocks of one stored row (n bins).
     // The MMA tile is 128 rows of m by 16 / 32 / 64 columns of n: the two operands swap roles
     // (complex products commute) when that pads less, e.g. 64 planes against a batch of 128.
@@ -130,17 +134,17 @@ int contract(int n, bool blocked, const float* a, long long a_pm, long long a_pk
     // a shard of at most 8 images leaves a contraction with 8 columns or 8 terms: no tile of the
     // tensor-core kernel fits that, the FP32 kernels stream the large operand (or the result) once
     if (contraction_mode() == 0 &&
-        cgemm_small_supported(a, b, d, d_pm * n, d_pn * n, d_planes * n, n, 4, 4, M, N, K, (int)X, accumulate)) {
-      const int rc = cgemm_small(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K,
-                                 (int)X, inv_norm, s, a_planes * 4, b_planes * 4, d_planes * n, n);
+        cgemm_small_supported(a, b, d, dm, dn, dbs, dqb, 4, 4, M, N, K, (int)X, accumulate)) {
+      const int rc = cgemm_small(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, dm, dn, M, N, K,
+                                 (int)X, inv_norm, s, a_planes * 4, b_planes * 4, dbs, dqb);
       if (rc != -1) return rc;  // -1: a tensor map could not be encoded, the general kernel takes over
     }
     if (padded(N, M) < padded(M, N)) {
-      return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, d_pn * n, d_pm * n, N, M, K, (int)X,
-                      inv_norm, accumulate, s, b_planes * 4, a_planes * 4, d_planes * n, 4, 4, n);
+      return cgemm_tc(b, b_pn * 4, b_pk * 4, conjB, a, a_pm * 4, a_pk * 4, conjA, d, dn, dm, N, M, K, (int)X,
+                      inv_norm, accumulate, s, b_planes * 4, a_planes * 4, dbs, 4, 4, dqb);
     }
-    return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, d_pm * n, d_pn * n, M, N, K, (int)X,
-                    inv_norm, accumulate, s, a_planes * 4, b_planes * 4, d_planes * n, 4, 4, n);
+    return cgemm_tc(a, a_pm * 4, a_pk * 4, conjA, b, b_pn * 4, b_pk * 4, conjB, d, dm, dn, M, N, K, (int)X,
+                    inv_norm, accumulate, s, a_planes * 4, b_planes * 4, dbs, 4, 4, dqb);
   }
   // natural layout: D[m][n] = sum_k opA(A[m][k]) opB(B[n][k]) = cgemm_bins with A' = A (rows m),
   // B' = B^T: C[i=m][j=n] = sum_k opA(A[i][k]) * opB'(B'[k][j]), B'[k][j] = B[j][k] -> "conj-transposed" flag
@@ -341,12 +345,12 @@ int fbfft_b200_conv_acc_grad_parameters(int fft_size, const float* in, const int
       // res[o][c] = scale / N^2 * sum_b conj(out[b][o]) in[b][c]      (m = o, n = c, k = b)
       rc = contract(n, blk, ws + r.out_off, 1, O, (long long)B * O, true, ws + r.in_off, 1, C, (long long)B * C, false,
                     ws + r.res_off, C, 1, (long long)O * C, O, C, B, scale / ((float)n * (float)n), s,
-                    (flags & FBFFT_CONV_ACCUMULATE_RESULT) != 0);
+                    (flags & FBFFT_CONV_ACCUMULATE_RESULT) != 0, (flags & FBFFT_CONV_RESULT_PLANE_MAJOR) != 0);
       if (rc) return rc;
     }
   }
   if (flags & FBFFT_CONV_STOP_AFTER_CONTRACTION) return kSuccess;
-  return inverse(n, ws + r.res_off, tw, 0, 0, blk, s);
+  return inverse(n, ws + r.res_off, tw, 0, 0, blk && !(flags & FBFFT_CONV_RESULT_PLANE_MAJOR), s);
 }
 
 // accGradParameters over batch shards on several GPUs: every rank contracts its own shard, the
@@ -397,7 +401,9 @@ int fbfft_b200_conv_acc_grad_parameters_dp(fbfft_b200_comm* comm, int mode, int 
   const size_t gw_count = (size_t)planes * tw.size[2] * tw.size[3];
   const Regions r = regions(n, B, C, O);
   float* res = static_cast<float*>(workspace) + r.res_off;
-  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0;
+  // the result region: row blocks, or plane by plane when the caller asked for that (or the layer has no blocks)
+  const bool blk = use_blocked(n, C, O) && (reinterpret_cast<uintptr_t>(workspace) & 31u) == 0 &&
+                   !(flags & FBFFT_CONV_RESULT_PLANE_MAJOR);
   if (mode == FBFFT_DP_SPATIAL_ALLREDUCE) {
     if (!gw_dense) {
       set_last_error("conv_acc_grad_parameters_dp: the spatial all-reduce needs a contiguous grad_weight");

@@ -251,7 +251,15 @@ enum {
   FBFFT_CONV_ACCUMULATE_RESULT = 32,
   /* run the forward transforms that are not marked REUSE, then return: a caller that holds the
    * weights fixed over several calls transforms them once this way */
-  FBFFT_CONV_STOP_AFTER_TRANSFORMS = 64
+  FBFFT_CONV_STOP_AFTER_TRANSFORMS = 64,
+  /* accGradParameters (and its data-parallel form; no counterpart in the reference): the result region holds
+   * the frequency-domain weight gradient plane by plane, [O*C][N/2+1][N] complex values, instead of in the
+   * row blocks the contraction otherwise writes.  Both halves of a STOP_AFTER_CONTRACTION /
+   * START_FROM_SPECTRUM pair, and every rank of a data-parallel sum, must agree on it.  Data-parallel callers
+   * set it when every rank's batch shard is small (at most 8 images: the contraction then writes whole lines
+   * in either layout): each rank's share of the planes is one contiguous piece, and the reduce-scatter of
+   * FBFFT_DP_FREQUENCY_REDUCE_SCATTER is a single collective instead of one per stored row. */
+  FBFFT_CONV_RESULT_PLANE_MAJOR = 128
 };
 enum {
   FBFFT_CONV_REGION_INPUT = 0,

@@ -231,6 +231,50 @@ def test_data_parallel_entry_point_with_a_one_rank_communicator(mode):
         comm.destroy()
 
 
+@pytest.mark.parametrize("case", [(32, 6, 16, 24, 27, 5, 0), (64, 20, 32, 16, 40, 3, 1), (128, 3, 16, 20, 40, 13, 0),
+                                  (16, 40, 16, 16, 12, 3, 1)])
+def test_plane_major_result_region(case):
+    """RESULT_PLANE_MAJOR: the weight-gradient spectrum plane by plane between contraction and inverse
+    (shards of at most 8 images: the FP32 streaming kernel; larger ones: the tensor-core kernel), in one
+    call, split in two, and through the data-parallel entry point with a one-rank communicator."""
+    n, b, c, o, hw, k, pad = case
+    rng = np.random.default_rng(sum(case))
+    oh = hw + 2 * pad - k + 1
+    x = rng.normal(size=(b, c, hw, hw)).astype(np.float32)
+    go = rng.normal(size=(b, o, oh, oh)).astype(np.float32)
+    want = orc.fftconv_acc_grad_parameters(x, go, n, k, k, pad)
+    xd, god = dev(x), dev(go)
+    ws = torch.empty(fb.conv_workspace_bytes(n, b, c, o) // 4, device="cuda")
+    ip = (pad, pad)
+    gw = torch.full((o, c, k, k), 7.0, device="cuda")
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, inPad=ip, flags=api.RESULT_PLANE_MAJOR)
+    torch.cuda.synchronize()
+    assert orc.rel_l2(host(gw), want) < CONV_TOL
+    gw.fill_(7.0)
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, inPad=ip, flags=api.RESULT_PLANE_MAJOR | api.STOP_AFTER_CONTRACTION)
+    # the region is [O*C][N/2+1][N] complex: plane (1, 2) can be read off directly
+    off, _ = fb.conv_workspace_region(n, b, c, o, api.REGION_RESULT)
+    bins = (n // 2 + 1) * n
+    plane = host(ws[off // 4 + (1 * c + 2) * bins * 2: off // 4 + (1 * c + 2 + 1) * bins * 2]).reshape(n // 2 + 1, n, 2)
+    fb.conv_acc_grad_parameters(n, xd, gw, god, ws, inPad=ip, flags=api.RESULT_PLANE_MAJOR | api.START_FROM_SPECTRUM)
+    torch.cuda.synchronize()
+    assert orc.rel_l2(host(gw), want) < CONV_TOL
+    # ... and is the spectrum whose inverse, cropped, is that plane of the gradient
+    back = torch.empty((1, k, k), device="cuda")
+    fb.fft2d_c2r(n, dev(plane[None]), back)
+    assert orc.rel_l2(host(back)[0], want[1, 2]) < CONV_TOL
+    comm = fb.Communicator(fb.comm_unique_id(), 0, 1, timeout_ms=30000)
+    try:
+        gw.fill_(7.0)
+        fb.conv_acc_grad_parameters_dp(comm, api.DP_FREQUENCY_REDUCE_SCATTER, n, xd, gw, god, ws, inPad=ip,
+                                       flags=api.RESULT_PLANE_MAJOR)
+        torch.cuda.synchronize()
+        assert orc.rel_l2(host(gw), want) < CONV_TOL
+    finally:
+        comm.destroy()
+    assert fb.device_status() == 0
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -266,6 +310,12 @@ def _dp_rank(rank, world, port, out_dir):
             fb.conv_acc_grad_parameters_dp(comm, mode, n, xs, gw, gs, ws, inPad=(pad, pad))
             torch.cuda.synchronize()
             errs.append(orc.rel_l2(host(gw), want))
+        # the reduce-scatter over a plane-major result region (one collective over contiguous shards)
+        gw = torch.full((o, c, k, k), 7.0, device="cuda")
+        fb.conv_acc_grad_parameters_dp(comm, api.DP_FREQUENCY_REDUCE_SCATTER, n, xs, gw, gs, ws, inPad=(pad, pad),
+                                       flags=api.RESULT_PLANE_MAJOR)
+        torch.cuda.synchronize()
+        errs.append(orc.rel_l2(host(gw), want))
     torch.cuda.synchronize()
     comm.destroy()
     with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
@@ -282,7 +332,7 @@ def test_data_parallel_entry_point_on_two_gpus(tmp_path):
     mp.spawn(_dp_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for r in range(world):
         errs = [float(e) for e in open(tmp_path / f"r{r}.txt").read().split()]
-        assert len(errs) == 9 and max(errs) < CONV_TOL, errs
+        assert len(errs) == 12 and max(errs) < CONV_TOL, errs
 
 
 def test_bounded_wait_runs_out_and_the_status_clears():
