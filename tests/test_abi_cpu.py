@@ -119,3 +119,21 @@ def test_communicator_entry_points_refuse_bad_arguments_on_the_host():
     p = ctypes.c_void_p(256)
     rc = L.fbfft_b200_conv_acc_grad_parameters_dp(None, 0, 8, p, i4, i4, 0, 0, p, i4, i4, p, i4, i4, 0, 0, 1.0, p, 1 << 20, 0, None)
     assert rc == bad and "communicator" in fb.last_error()
+
+
+def test_flag_constants_of_the_python_binding_match_the_header():
+    """Every FBFFT_CONV_* / FBFFT_DP_* enumerator of include/fbfft_b200.h that the Python binding names has
+    the header's value (the binding passes plain integers through ctypes)."""
+    import os
+    import re
+    from fbcuda_b200 import api
+    header = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "fbfft_b200.h")).read()
+    values = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(FBFFT_[A-Z0-9_]+)\s*=\s*(\d+)", header)}
+    pairs = {"FBFFT_CONV_REUSE_INPUT_SPECTRUM": api.REUSE_INPUT_SPECTRUM, "FBFFT_CONV_REUSE_OUTPUT_SPECTRUM": api.REUSE_OUTPUT_SPECTRUM,
+             "FBFFT_CONV_REUSE_WEIGHT_SPECTRUM": api.REUSE_WEIGHT_SPECTRUM, "FBFFT_CONV_STOP_AFTER_CONTRACTION": api.STOP_AFTER_CONTRACTION,
+             "FBFFT_CONV_START_FROM_SPECTRUM": api.START_FROM_SPECTRUM, "FBFFT_CONV_ACCUMULATE_RESULT": api.ACCUMULATE_RESULT,
+             "FBFFT_CONV_STOP_AFTER_TRANSFORMS": api.STOP_AFTER_TRANSFORMS, "FBFFT_CONV_RESULT_PLANE_MAJOR": api.RESULT_PLANE_MAJOR,
+             "FBFFT_DP_FREQUENCY_ALLREDUCE": api.DP_FREQUENCY_ALLREDUCE, "FBFFT_DP_FREQUENCY_REDUCE_SCATTER": api.DP_FREQUENCY_REDUCE_SCATTER,
+             "FBFFT_DP_SPATIAL_ALLREDUCE": api.DP_SPATIAL_ALLREDUCE}
+    for name, value in pairs.items():
+        assert values[name] == value, name
